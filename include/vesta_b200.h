@@ -1,0 +1,69 @@
+/* C ABI of libvesta_b200.so: the run-time under vesta_gpu_b200.launch.
+ *
+ * The reference reaches NVRTC and the CUDA driver through the Python packages cuda-bindings
+ * and nvidia-cuda-nvrtc (vesta/launch.py:5-7). Each entry point below stands for the calls the
+ * reference makes at the cited lines, behind plain pointers and sizes, so that any host
+ * language with a C FFI can drive the decode-step kernel. Every function returns 0 on success
+ * and a non-zero CUDA / NVRTC status otherwise; vesta_last_error() then describes the failure.
+ * libcuda and libnvrtc are opened lazily, so the library loads on a machine with no GPU.
+ */
+#ifndef VESTA_B200_H
+#define VESTA_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ABI version of this header. */
+int vesta_rt_version(void);
+
+/* Text of the last failure on the calling thread (never NULL). */
+const char* vesta_last_error(void);
+
+/* Optional: path of the libnvrtc to open (default: the system libnvrtc.so.12). */
+int vesta_set_nvrtc_path(const char* path);
+
+/* vesta/launch.py:17-27 compile_cubin: nvrtcCreateProgram, nvrtcCompileProgram,
+ * nvrtcGetProgramLog, nvrtcGetCUBIN. arch e.g. "sm_100a". On return *cubin / *log are
+ * malloc'ed (release with vesta_free); *log holds the compiler log also on failure. */
+int vesta_nvrtc_compile(const char* src, const char* arch, const char* const* opts, int n_opts,
+                        void** cubin, size_t* cubin_size, char** log);
+void vesta_free(void* p);
+
+/* vesta/launch.py:32 cuInit; makes sure a context is current on the calling thread
+ * (the primary context of `device` is retained and set if none is). */
+int vesta_init(int device);
+
+/* vesta/launch.py:35-36 cuModuleLoadData / cuModuleGetFunction. */
+int vesta_module_load(const void* cubin, void** module);
+int vesta_module_unload(void* module);
+int vesta_module_get_function(void* module, const char* name, void** function);
+
+/* vesta/launch.py:38-40 cuFuncSetAttribute(MAX_DYNAMIC_SHARED_SIZE_BYTES) and
+ * cuOccupancyMaxActiveBlocksPerMultiprocessor. */
+int vesta_func_set_max_dynamic_smem(void* function, int bytes);
+int vesta_occupancy(void* function, int block_threads, size_t dynamic_smem, int* blocks_per_sm);
+
+/* vesta/launch.py:68-70 cuLaunchCooperativeKernel: 1-D grid and block, on `stream`
+ * (a CUstream, 0 for the default stream). args: one pointer per kernel parameter. */
+int vesta_launch_cooperative(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
+                             void* stream, void** args);
+
+/* Plain (non-cooperative) launch, used for the one-time weight packing kernel. */
+int vesta_launch(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
+                 void* stream, void** args);
+
+/* vesta/launch.py:57-70 bind + launch: the argument list is fixed once (every kernel parameter
+ * is a device pointer), after which a step costs one call. vesta_step_run launches `steps`
+ * decode steps back to back on `stream` without returning to the caller in between. */
+int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
+                    int n_args, const unsigned long long* device_pointers, void** bound);
+int vesta_step_run(void* bound, void* stream, int steps);
+void vesta_step_release(void* bound);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,100 @@
+"""The decode-step program on the GPU: Hugging Face style weights as residue, lowered to one
+persistent kernel per step.
+
+    m = VestaGPT2(hf, dtype='f16', batch=8, tmax=1024)
+    m.reset(); m.x.copy_(tok); m.t.fill_(p); m.step()     # one decode step
+    m.logits(), m.next()                                    # views, no sync
+
+Same surface as the reference binding (vesta/gpt2.py:18-55): `gpt2_weights`, and `VestaGPT2`
+with `W, B, tmax, keys, vals, x, t, low, k, weight_bytes, reset, step, logits, next, kv_bytes`.
+With feedback on, each step writes its chosen token into x and advances t, so generation is
+back-to-back launches with nothing from the host in between. The sizes (layers, width, heads,
+MLP width, vocabulary) are read from the weights instead of being fixed to GPT-2 small
+(vesta/gpt2.py:16), so an XL-shaped model runs through the same code.
+"""
+import torch
+
+from . import PROGRAMS
+from .launch import Kernel, TORCH_DT
+from .lower import lower
+from .program_text import decode_program
+from .shapes import Shape
+
+E_HEAD = 64
+
+
+def gpt2_weights(hf):
+    """state_dict under Hugging Face names -> residues of the step program, per-layer tensors stacked on l"""
+    sd = hf.state_dict()
+    L = 0
+    while f'transformer.h.{L}.ln_1.weight' in sd:
+        L += 1
+    st = lambda n: torch.stack([sd[f'transformer.h.{l}.{n}'] for l in range(L)])
+    return dict(wte=sd['transformer.wte.weight'], wpe=sd['transformer.wpe.weight'],
+                ln1w=st('ln_1.weight'), ln1b=st('ln_1.bias'), qkvw=st('attn.c_attn.weight'), qkvb=st('attn.c_attn.bias'),
+                ow=st('attn.c_proj.weight'), ob=st('attn.c_proj.bias'), ln2w=st('ln_2.weight'), ln2b=st('ln_2.bias'),
+                fcw=st('mlp.c_fc.weight'), fcb=st('mlp.c_fc.bias'), pw=st('mlp.c_proj.weight'), pb=st('mlp.c_proj.bias'),
+                lnfw=sd['transformer.ln_f.weight'], lnfb=sd['transformer.ln_f.bias'])
+
+
+def shape_of(W, heads=None):
+    N, D = W['wte'].shape
+    L, _, F = W['fcw'].shape
+    H = heads or D // E_HEAD
+    return Shape('model', L=L, D=D, H=H, E=D // H, F=F, N=N, C=W['wpe'].shape[0])
+
+
+class VestaGPT2:
+    def __init__(self, hf, dtype='f16', batch=1, tmax=1024, feedback=True, program=None, timing=False,
+                 blocks_per_sm=None, per_sequence_t=False, device=None):
+        """program: path of a .vst file; default: the step program for the sizes of the weights
+        (identical to programs/gpt2.vst for GPT-2 small). per_sequence_t: every sequence keeps its
+        own position t[b] (ragged batches); default one position for the whole batch as in the
+        reference."""
+        tdt = TORCH_DT[dtype]
+        dev = torch.device('cuda', torch.cuda.current_device() if device is None else device)
+        self.device = dev
+        self.W = {k: v.detach().to(dev, tdt).contiguous() for k, v in gpt2_weights(hf).items()}
+        self.shape = shape_of(self.W)
+        sh = self.shape
+        self.B, self.tmax = batch, tmax
+        self.keys = torch.zeros(batch, sh.L, tmax, sh.H, sh.E, device=dev, dtype=tdt)
+        self.vals = torch.zeros_like(self.keys)
+        self.x = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.t = torch.zeros(batch if per_sequence_t else 1, dtype=torch.int32, device=dev)
+        R = {'x': self.x, 't': self.t, **self.W, 'keys': self.keys, 'vals': self.vals}
+        names = {torch.int32: 'i32', torch.float16: 'f16', torch.float32: 'f32'}
+        spec = {n: (((batch,) if per_sequence_t else ()), 'i32') if n == 't' else (tuple(v.shape), names[v.dtype])
+                for n, v in R.items()}
+        if program is None:
+            text = decode_program(sh)
+        else:
+            text = open(program, encoding='utf-8').read()
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        per_token = ('x', 'keys', 'vals') + (('t',) if per_sequence_t else ())
+        self.low = lower(text, spec, axis_max={'s': tmax}, batch=batch, per_token=per_token,
+                         outputs=('logit', 'next'), feedback={'x': 'next', 't': 1} if feedback else None,
+                         timing=timing, grid=sms)
+        self.k = Kernel(self.low, device=dev.index, blocks_per_sm=blocks_per_sm)
+        self.k.bind(R)
+        self.weight_bytes = sum(v.numel() * v.element_size() for n, v in self.W.items() if n != 'wpe') \
+            + sh.D * self.W['wpe'].element_size()
+
+    def reset(self):
+        self.keys.zero_(); self.vals.zero_(); self.t.zero_()
+
+    def step(self, steps=1):
+        self.k.launch(steps)
+
+    def logits(self):
+        return self.k.view('logit')
+
+    def next(self):
+        return self.k.view('next')
+
+    def kv_bytes(self, n_ctx):
+        sh = self.shape
+        return 2 * sh.L * self.B * n_ctx * sh.D * self.keys.element_size()
+
+
+DEFAULT_PROGRAM = PROGRAMS / 'gpt2.vst'

@@ -1,0 +1,432 @@
+"""Placement of a decode-step program on the 148 SMs of a B200 and assembly of the CUDA source
+of ONE persistent cooperative kernel (plus a one-time weight-packing kernel).
+
+    lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False) -> Lowered
+
+Same call and the same Lowered fields as the reference compiler (vesta/lower.py:1294-1329,
+69-79), so vesta.gpt2-style callers and Kernel.view() work unchanged. What happens inside is
+different by design: instead of deriving scalar CUDA C statement by statement, this pass
+
+  1. recognises the program: every statement is matched, in order, against the statement
+     patterns of the decode-step family (embed; per layer LN -> QKV -> KV emit -> scores ->
+     softmax -> PV -> projection + residual -> LN -> FC -> tanh-GELU -> projection + residual;
+     then LN -> tied-embedding logits -> argmax with lowest-id ties). Names, sizes and
+     constants are read from the program; anything that does not match raises
+     NotImplementedError (there is no generic or CPU fallback by design);
+  2. places the five contractions on the CTAs of a one-CTA-per-SM grid (NARROW: whole fold, a few
+     output tiles per CTA; WIDE: a slice of the fold for many output tiles, combined by atomics),
+     balancing the bytes every CTA streams per step, and lays each CTA's share of the fp16 weights
+     out as one contiguous stream of mma-ordered 16x16 tiles (Lowered.place, consumed by the
+     packing kernel and the step kernel);
+  3. prepends the sizes, placement constants and the kernel signatures to the hand-written
+     sm_100a kernel text in csrc/step_kernel.cuh.
+"""
+import math
+from dataclasses import dataclass, field, fields, is_dataclass
+from pathlib import Path
+
+import numpy as np
+
+from . import syntax as sx
+
+KERNEL_TEXT = Path(__file__).resolve().parent / 'csrc' / 'step_kernel.cuh'
+
+CTYPE = {'f32': 'float', 'f16': 'unsigned short', 'i32': 'int'}
+NW = 8                 # consumer warps per CTA (one more warp streams the weights)
+CHUNK_TILES = 32       # 16 KB ring slots
+WN_MAX = 4             # widest NARROW placement
+PT_STRIDE = 16
+SMEM_LIMIT = 227 * 1024
+DEFAULT_SMS = 148      # B200
+
+
+@dataclass
+class Lowered:
+    src: str
+    params: list             # (name, dtype, emitted) in kernel argument order
+    scratch: dict            # host-visible name -> (offset, axes, static shape)
+    scratch_floats: int
+    shared_bytes: int        # dynamic shared memory per block
+    barriers_per_launch: int
+    plan: list = field(default_factory=list)     # (statement, placement) for reading
+    sites: list = field(default_factory=list)    # timing: what each TS slot measures
+    counters: int = 2                            # length of the bar array
+    # additions of this backend
+    block: int = (NW + 1) * 32                   # threads per CTA
+    grid: int = DEFAULT_SMS                      # CTAs the placement was made for (one per SM)
+    place: np.ndarray = None                     # int32 [grid, PT_STRIDE] placement records
+    packed_bytes: int = 0                        # size of the packed weight copy
+    pack_params: list = field(default_factory=list)   # residues the packing kernel reads
+    dims: dict = field(default_factory=dict)     # sizes and constants read from the program
+    roles: dict = field(default_factory=dict)    # role -> residue name
+
+
+# ------------------------------------------------------------------ recognition
+class Mismatch(Exception):
+    pass
+
+
+def _unify(pat, node, env):
+    """structural match of a pattern tree against a program tree; `$name` binds"""
+    if isinstance(pat, str):
+        if pat.startswith('$'):
+            if pat in env and env[pat] != node:
+                raise Mismatch(f'{pat} is {env[pat]!r}, found {node!r}')
+            env[pat] = node
+            return
+        if pat != node:
+            raise Mismatch(f'expected {pat!r}, found {node!r}')
+        return
+    if isinstance(pat, sx.Name) and pat.id.startswith('$'):
+        if isinstance(node, sx.Name):
+            return _unify(pat.id, node.id, env)
+        if isinstance(node, sx.Num):
+            return _unify(pat.id, node.value, env)
+        raise Mismatch(f'{pat.id} cannot stand for {type(node).__name__}')
+    if isinstance(pat, tuple):
+        if not isinstance(node, tuple) or len(pat) != len(node):
+            raise Mismatch('different number of indices or statements')
+        for p, n in zip(pat, node):
+            _unify(p, n, env)
+        return
+    if is_dataclass(pat):
+        if type(pat) is not type(node):
+            raise Mismatch(f'expected {type(pat).__name__}, found {type(node).__name__}')
+        for f in fields(pat):
+            _unify(getattr(pat, f.name), getattr(node, f.name), env)
+        return
+    if pat != node:
+        raise Mismatch(f'expected {pat!r}, found {node!r}')
+
+
+def _pattern(text):
+    stmts = sx.parse(text, wild=True)
+    assert len(stmts) == 1, text
+    return stmts[0]
+
+
+# statements of the layer body, in order; Q numbers refer to the questions of the reference
+# (QUESTIONS.md:15-88, vesta/programs/gpt2.vst:37-72)
+LAYER_PATTERNS = [
+    ('LN1 mean', '$m1 = fold sum $d: $z[$d] / $D'),
+    ('LN1 variance', '$v1 = fold sum $d: ($z[$d] - $m1) * ($z[$d] - $m1) / $D'),
+    ('LN1', '$a[$d] = ($z[$d] - $m1) / sqrt($v1 + $eps) * $ln1w[$l, $d] + $ln1b[$l, $d]'),
+    ('QKV', '$qkv[$j] = (fold sum $d: $a[$d] * $qkvw[$l, $d, $j]) + $qkvb[$l, $j]'),
+    ('query view', '$q[$h, $e] = $qkv[$h * $E + $e]'),
+    ('K emit', 'residue $keys[$l, $t, $h, $e] <- $qkv[$D + $h * $E + $e]'),
+    ('V emit', 'residue $vals[$l, $t, $h, $e] <- $qkv[$D2 + $h * $E + $e]'),
+    ('scores', '$sc[$h, $s] = (fold sum $e: $q[$h, $e] * $keys[$l, $s, $h, $e]) / $scale'),
+    ('softmax max', '$mx[$h] = fold max $s: $sc[$h, $s]'),
+    ('softmax exp', '$ex[$h, $s] = exp($sc[$h, $s] - $mx[$h])'),
+    ('softmax weights', '$w[$h, $s] = $ex[$h, $s] / (fold sum $s: $ex[$h, $s])'),
+    ('PV', '$o[$h, $e] = fold sum $s: $w[$h, $s] * $vals[$l, $s, $h, $e]'),
+    ('attn-proj', '$oo[$d] = fold sum $h: (fold sum $e: $o[$h, $e] * $ow[$l, $h * $E + $e, $d])'),
+    ('residual 1', '$z1[$d] = $z[$d] + $oo[$d] + $ob[$l, $d]'),
+    ('LN2 mean', '$m2 = fold sum $d: $z1[$d] / $D'),
+    ('LN2 variance', '$v2 = fold sum $d: ($z1[$d] - $m2) * ($z1[$d] - $m2) / $D'),
+    ('LN2', '$b[$d] = ($z1[$d] - $m2) / sqrt($v2 + $eps) * $ln2w[$l, $d] + $ln2b[$l, $d]'),
+    ('FC', '$u[$f] = (fold sum $d: $b[$d] * $fcw[$l, $d, $f]) + $fcb[$l, $f]'),
+    ('GELU', '$g[$f] = $ga * $u[$f] * ($one + tanh($gb * ($u[$f] + $gc * $u[$f] * $u[$f] * $u[$f])))'),
+    ('MLP-proj + residual 2', '$z2[$d] = $z1[$d] + (fold sum $f: $g[$f] * $pw[$l, $f, $d]) + $pb[$l, $d]'),
+]
+HEAD_PATTERNS = [
+    ('LNf mean', '$m3 = fold sum $d: $zL[$d] / $D'),
+    ('LNf variance', '$v3 = fold sum $d: ($zL[$d] - $m3) * ($zL[$d] - $m3) / $D'),
+    ('LNf', '$c[$d] = ($zL[$d] - $m3) / sqrt($v3 + $eps) * $lnfw[$d] + $lnfb[$d]'),
+    ('logits', '$logit[$n] = fold sum $d: $c[$d] * $wte[$n, $d]'),
+    ('best', '$best = fold max $n: $logit[$n]'),
+    ('next', '$next = fold min $n: fork $logit[$n] == $best ? $n : $N'),
+]
+EMBED_PATTERN = ('embed', '$z0[$d] = $wte[$x, $d] + $wpe[$t, $d]')
+
+
+def _show(node):
+    return getattr(node, 'name', type(node).__name__)
+
+
+def recognise(text):
+    """program text -> (env of bindings, axis extents, received residues {name: axes})"""
+    stmts = sx.parse(text)
+    axes, recv, rest = {}, {}, []
+    for s in stmts:
+        if isinstance(s, sx.AxisDef):
+            axes[s.name] = s.extent
+        elif isinstance(s, sx.Receive):
+            recv[s.name] = s.axes
+        else:
+            rest.append(s)
+    env = {}
+
+    def need(label, pat_text, node):
+        try:
+            _unify(_pattern(pat_text), node, env)
+        except Mismatch as err:
+            raise NotImplementedError(
+                f'statement {_show(node)!r} is not the {label} statement of a decode step: {err}') from None
+
+    if len(rest) != 2 + len(HEAD_PATTERNS) or not isinstance(rest[1], sx.StepFold):
+        raise NotImplementedError('not a decode-step program: expected embed, one `fold step` over the layers, '
+                                  f'then {len(HEAD_PATTERNS)} head statements')
+    need(*EMBED_PATTERN, rest[0])
+    step = rest[1]
+    try:
+        _unify(sx.StepFold('$zL', ('$d',), '$l', sx.Name('$z0'), '$z', step.body, sx.Name('$z2')), step, env)
+    except Mismatch as err:
+        raise NotImplementedError(f'layer loop: {err}') from None
+    if len(step.body) != len(LAYER_PATTERNS):
+        raise NotImplementedError(f'layer body has {len(step.body)} statements, a decode step has {len(LAYER_PATTERNS)}')
+    for (label, pat), node in zip(LAYER_PATTERNS, step.body):
+        need(label, pat, node)
+    for (label, pat), node in zip(HEAD_PATTERNS, rest[2:]):
+        need(label, pat, node)
+
+    ext = {}
+    for name, e in axes.items():
+        if isinstance(e, sx.Num):
+            ext[name] = int(e.value)
+        elif e == sx.Bin('+', sx.Name(env['$t']), sx.Num(1)):
+            ext[name] = None                      # run-time extent: positions seen so far
+        else:
+            raise NotImplementedError(f'axis {name}: extent must be a number or {env["$t"]} + 1')
+    return env, ext, recv
+
+
+def _dims(env, ext):
+    g = lambda k: ext[env[k]]
+    D, H, E, F, N, J, L = g('$d'), g('$h'), g('$e'), g('$f'), g('$n'), g('$j'), g('$l')
+    checks = [
+        (ext[env['$s']] is None, 'the position axis must have the run-time extent t + 1'),
+        (env['$D'] == D, 'LayerNorm divides by the width'),
+        (H * E == D, 'heads x head width must equal the width'),
+        (env['$E'] == E, 'head views must use the head width'),
+        (J == 3 * D and env['$D2'] == 2 * D, 'QKV must be three width-sized parts'),
+        (env['$N'] == N, 'the argmax default must be the vocabulary size'),
+        (env['$one'] == 1, 'GELU form'),
+        (D % 16 == 0 and F % 16 == 0 and E % 8 == 0, 'width and MLP width must be multiples of 16, head width of 8'),
+        (E == 64, 'this kernel holds one 128-byte K/V row per 8 lanes: head width 64'),
+    ]
+    for ok, why in checks:
+        if not ok:
+            raise NotImplementedError(f'program outside the supported family: {why}')
+    return dict(D=D, H=H, E=E, F=F, N=N, J=J, L=L, eps=float(env['$eps']), scale=float(env['$scale']),
+                gelu=(float(env['$ga']), float(env['$gb']), float(env['$gc'])))
+
+
+ROLE_KEYS = ('x', 't', 'wte', 'wpe', 'ln1w', 'ln1b', 'qkvw', 'qkvb', 'ow', 'ob', 'ln2w', 'ln2b',
+             'fcw', 'fcb', 'pw', 'pb', 'lnfw', 'lnfb', 'keys', 'vals')
+
+
+# ------------------------------------------------------------------ placement
+def _spread(total, loads, cap):
+    """hand out `total` equal units one at a time to the least loaded CTA (at most cap each);
+    -> counts per CTA. loads is updated by the caller's unit weight afterwards."""
+    counts = [0] * len(loads)
+    cur = list(loads)
+    for _ in range(total):
+        c = min((i for i in range(len(cur)) if counts[i] < cap), key=lambda i: (cur[i], i), default=None)
+        if c is None:
+            raise NotImplementedError('placement: too many output tiles for this grid')
+        counts[c] += 1
+        cur[c] += 1.0
+    return counts
+
+
+def place_step(dims, grid):
+    """-> (int32 [grid, PT_STRIDE] placement records, tiles per CTA stream, plan notes)"""
+    D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
+    KT_D, KT_F, JT_D, JT_J, JT_N = D // 16, F // 16, D // 16, 3 * D // 16, (N + 15) // 16
+    G = grid
+    # FC / MLP-proj: every f tile costs 2*KT_D tiles of stream; at most WN_MAX per CTA
+    fc = _spread(KT_F, [0.0] * G, WN_MAX)
+    load = [2.0 * KT_D * n for n in fc]
+    # QKV: every output tile costs KT_D tiles of stream
+    cnt = [0] * G
+    for _ in range(JT_J):
+        c = min((i for i in range(G) if cnt[i] < WN_MAX), key=lambda i: (load[i], i))
+        cnt[c] += 1
+        load[c] += KT_D
+    qkv = cnt
+    # attn-proj: groups of 8 output tiles x slices of the fold, one unit per CTA
+    groups = math.ceil(JT_D / 8)
+    splits = max(1, min(KT_D, G // groups))
+    nk = math.ceil(KT_D / splits)
+    units = [(jg, k0) for jg in range(groups) for k0 in range(0, KT_D, nk)]
+    if len(units) > G:
+        raise NotImplementedError('placement: projection units exceed the grid')
+    proj = [None] * G
+    order = sorted(range(G), key=lambda i: (load[i], i))
+    for (jg, k0), c in zip(units, order):
+        j0, nj = jg * 8, min(8, JT_D - jg * 8)
+        kk = min(nk, KT_D - k0)
+        proj[c] = (j0, nj, k0, kk)
+        load[c] += nj * kk
+    # logits: output tiles over the whole fold; balance the whole step (layers x per-layer load + logits)
+    step_load = [L * v for v in load]
+    cnt = [0] * G
+    for _ in range(JT_N):
+        c = min(range(G), key=lambda i: (step_load[i], i))
+        cnt[c] += 1
+        step_load[c] += KT_D
+    logit = cnt
+
+    rec = np.zeros((G, PT_STRIDE), np.int32)
+    base = 0
+    fj = qj = lj = 0
+    for c in range(G):
+        pj0, pnj, pk0, pnk = proj[c] or (0, 0, 0, 0)
+        layer = qkv[c] * KT_D + pnj * pnk + fc[c] * KT_D + JT_D * fc[c]
+        rec[c, :12] = (base, layer, qj, qkv[c], pj0, pnj, pk0, pnk, fj, fc[c], lj, logit[c])
+        qj += qkv[c]; fj += fc[c]; lj += logit[c]
+        base += L * layer + logit[c] * KT_D
+    assert qj == JT_J and fj == KT_F and lj == JT_N
+    if base >= 2 ** 31:
+        raise NotImplementedError('packed weights exceed the 32-bit tile index')
+    per = rec[:, 1].astype(np.int64) * L + rec[:, 11].astype(np.int64) * KT_D
+    notes = dict(tiles_total=int(base), tiles_min=int(per.min()), tiles_max=int(per.max()),
+                 tiles_mean=float(per.mean()), proj_units=len(units), proj_nk=nk)
+    return rec, int(base), notes
+
+
+# ------------------------------------------------------------------ assembly
+def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
+          grid=DEFAULT_SMS, act_lo=None):
+    """See the module docstring. `res`: name -> (shape, dtype) as the kernel sees them (batched
+    where per-token; scalars have shape ()). `axis_max`: bound of the run-time position axis,
+    e.g. {'s': tmax}. `grid`: CTAs to place for (one per SM). 't' may be listed in per_token, in
+    which case every sequence has its own position (shape (batch,))."""
+    env, ext, recv = recognise(text)
+    dims = _dims(env, ext)
+    D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
+    B = int(batch)
+    roles = {k: env['$' + k] for k in ROLE_KEYS}
+    for role, name in roles.items():
+        if name not in res:
+            raise NameError(f'residue {name} not supplied')
+        if name not in recv:
+            raise NameError(f'{name} is used but never received')
+    extra = [n for n in res if n not in roles.values()]
+    if extra:
+        raise ValueError(f'residues the program does not receive: {extra}')
+    s_axis = env['$s']
+    if s_axis not in axis_max:
+        raise ValueError(f'axis_max must bound the run-time axis {s_axis}')
+    tmax = int(axis_max[s_axis])
+    per_token = set(per_token)
+    t_name, x_name = roles['t'], roles['x']
+    t_per_token = t_name in per_token
+
+    def want(role, shape, dt):
+        got_shape, got_dt = res[roles[role]]
+        if tuple(got_shape) != tuple(shape) or got_dt != dt:
+            raise ValueError(f'residue {roles[role]}: expected {tuple(shape)} {dt}, got {tuple(got_shape)} {got_dt}')
+
+    wdt = res[roles['wte']][1]
+    if wdt != 'f16':
+        raise NotImplementedError('weights and the KV cache must be fp16 (f16); fp32 storage is not placed by this backend')
+    want('x', (B,), 'i32')
+    want('t', (B,) if t_per_token else (), 'i32')
+    cpos = int(res[roles['wpe']][0][0])
+    want('wte', (N, D), 'f16'); want('wpe', (cpos, D), 'f16')
+    for r, shp in (('ln1w', (L, D)), ('ln1b', (L, D)), ('qkvw', (L, D, 3 * D)), ('qkvb', (L, 3 * D)), ('ow', (L, D, D)),
+                   ('ob', (L, D)), ('ln2w', (L, D)), ('ln2b', (L, D)), ('fcw', (L, D, F)), ('fcb', (L, F)),
+                   ('pw', (L, F, D)), ('pb', (L, D)), ('lnfw', (D,)), ('lnfb', (D,))):
+        want(r, shp, 'f16')
+    want('keys', (B, L, tmax, H, E), 'f16'); want('vals', (B, L, tmax, H, E), 'f16')
+    for r in ('x', 'keys', 'vals'):
+        if roles[r] not in per_token:
+            raise NotImplementedError(f'{roles[r]} must be a per-token residue')
+    fb = dict(feedback or {})
+    if fb and not (fb.get(x_name) == env['$next'] and isinstance(fb.get(t_name), int) and len(fb) == 2):
+        raise NotImplementedError(f'feedback must be {{{x_name!r}: {env["$next"]!r}, {t_name!r}: <int>}}')
+    for o in outputs:
+        if o not in (env['$logit'], env['$next']):
+            raise NotImplementedError(f'output {o}: only {env["$logit"]} and {env["$next"]} are kept for the host')
+
+    NB = (B + 7) // 8
+    if NB > 4:
+        raise NotImplementedError('batch above 32 rows per launch is not placed yet')
+    if act_lo is None:
+        act_lo = NB <= 2
+    rec, tiles, notes = place_step(dims, grid)
+
+    # global scratch (floats): host-visible values first, then the kernel's own vectors
+    def up(v, a=64):
+        return (v + a - 1) // a * a
+    off_logit, off_next = 0, up(B * N)
+    off_z = up(off_next + B)
+    off_q = off_z + 3 * up(B * D)
+    off_o = off_q + up(B * D)
+    off_best = off_o + up(B * D)
+    scratch_floats = off_best + up(2 * B)
+    scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
+
+    KT_D = D // 16
+    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + NW * WN_MAX * NB * 128 * 4
+             + NW * (E + 2) * 4 + B * 8 * NW + 64 + 16)
+    nslot = (SMEM_LIMIT - fixed - 1024) // (CHUNK_TILES * 512 + 16)
+    if nslot < 2:
+        raise NotImplementedError('model too wide for the shared-memory budget at this batch')
+    nslot = min(nslot, 16)
+    shared = fixed + nslot * (CHUNK_TILES * 512 + 16) + 512
+
+    def f32(v):
+        return repr(float(np.float32(v))) + 'f'
+    scale = dims['scale']
+    defs = dict(V_NW=NW, V_B=B, V_NB=NB, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
+                V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
+                V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
+                V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
+                V_TIMING=int(bool(timing)), V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
+                V_OFF_O=off_o, V_OFF_BEST=off_best)
+    head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
+
+    emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
+    params, sig = [], []
+    for name, (shape, dt) in res.items():
+        em = name in emitted
+        params.append((name, dt, em))
+        sig.append(f'{"" if em else "const "}{CTYPE[dt]}* __restrict__ R_{name}')
+    R = {k: 'R_' + v for k, v in roles.items()}
+    step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
+                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
+    fill = [f'a.x = {R["x"]}; a.t = {R["t"]};']
+    for k in ('wte', 'wpe', 'ln1w', 'ln1b', 'qkvb', 'ob', 'ln2w', 'ln2b', 'fcb', 'pb', 'lnfw', 'lnfb'):
+        fill.append(f'a.{k} = {R[k]};')
+    fill.append(f'a.keys = {R["keys"]}; a.vals = {R["vals"]};')
+    if fb:
+        fill.append(f'a.x_out = {R["x"]}; a.t_out = {R["t"]};')
+    else:
+        fill.append('a.x_out = 0; a.t_out = 0;')
+    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT;')
+    pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
+    pack_params = [roles[k] for k in pack_roles]
+    pack_sig = ', '.join([f'const unsigned short* __restrict__ R_{roles[k]}' for k in pack_roles]
+                         + ['unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
+    pack_fill = ' '.join(f'p.{k} = R_{roles[k]};' for k in pack_roles) + ' p.WP = WP; p.PT = PT;'
+    tail = (f'\nextern "C" __global__ void __launch_bounds__(NTHREADS, 1) vesta_step({step_sig}) {{\n'
+            f'    Args a; {" ".join(fill)}\n    step_body(a);\n}}\n'
+            f'\nextern "C" __global__ void vesta_pack({pack_sig}) {{\n'
+            f'    PackArgs p; {pack_fill}\n    pack_body(p);\n}}\n')
+    src = head + KERNEL_TEXT.read_text(encoding='utf-8') + tail
+
+    q = env
+    plan = [
+        (f'{q["$z0"]} (embed)', 'grid-stride, then barrier'),
+        (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', 'every CTA recomputes, one warp per row, into mma operand tiles'),
+        (f'{q["$qkv"]} + emits', f'NARROW: whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA; bias, q, K/V emit in the epilogue'),
+        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)', 'one CTA per (sequence, head), online softmax in registers'),
+        (f'{q["$oo"]}, {q["$z1"]}', f'WIDE: {notes["proj_units"]} units of 8 output tiles x {notes["proj_nk"]} fold tiles, fp32 atomics'),
+        (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', 'every CTA recomputes'),
+        (f'{q["$u"]}, {q["$g"]}', f'NARROW: {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
+        (f'{q["$z2"]}', 'WIDE over the CTA\'s own f tiles, fp32 atomics'),
+        (f'{q["$m3"]}, {q["$v3"]}, {q["$c"]} (LNf)', 'every CTA recomputes'),
+        (f'{q["$logit"]}', f'WIDE over the whole fold, {min(rec[:, 11])}-{max(rec[:, 11])} vocabulary tiles per CTA'),
+        (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes'),
+    ]
+    sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
+        + ['logits', 'finish']
+    low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
+                  barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=16 + max(grid, 1024),
+                  block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
+                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes), roles=roles)
+    return low
