@@ -44,11 +44,11 @@ typedef unsigned short u16;
 #define WN_MAX 4                      // widest NARROW placement (output tiles per CTA)
 #define LNV ((V_D + 127) / 128)       // float4 per lane to hold one row of width D
 
-// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [16 + cta] barrier flags
+// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter, cleared by the last CTA of every step
 #define BAR_STATUS 0
 #define BAR_DONE 1
 #define BAR_ABORT 2
-#define BAR_FLAGS 16
+#define BAR_COUNT 32
 
 // every wait gives up after WAIT_NS nanoseconds (a step takes well under a millisecond)
 #define WAIT_NS 500000000ull
@@ -153,8 +153,11 @@ __device__ __forceinline__ u32 wide_tiles(int nj, int nk) { return (u32)(nj * nk
 #define SM_ACT (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)
 #define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)
 #define SM_RED (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)
-#define SM_MISC (SM_RED + NW * WN_MAX * V_NB * 128 * 4)
-#define SM_MISC_BYTES (NW * (V_E + 2) * 4 + V_B * 8 * NW + 64)
+#define SM_PRM (SM_RED + NW * WN_MAX * V_NB * 128 * 4)
+#define PRM_TILE_HALVES (WN_MAX * 16)
+#define SM_PRM_BYTES ((3 * V_D + PRM_TILE_HALVES) * 2)
+#define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
+#define SM_MISC_BYTES (NW * (V_E + 2) * 4 + V_B * 8 * NW + V_B * 4 + 64)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
 #define SM_TOTAL (SM_BARS + 2 * V_NSLOT * 8)
 
@@ -165,6 +168,9 @@ struct Ctx {
     u32 chunk;         // stream chunks consumed so far (same value in every consumer warp and the producer)
     int cta, ncta, tid, warp, lane;
     bool dead;         // a bounded wait expired somewhere: skip waits from now on
+#if V_TIMING
+    long long wait_clocks; u32 slow_waits;
+#endif
 };
 
 __device__ __forceinline__ u32 full_bar(const Ctx& c, u32 slot) { return smem_u32(c.smem + SM_BARS) + slot * 8; }
@@ -179,6 +185,11 @@ __device__ __noinline__ void give_up(Ctx& c, u32 where) {
 __device__ __forceinline__ void wait_mbar(Ctx& c, u32 bar, u32 parity, u32 where) {
     if (c.dead) return;
     if (mbar_try(bar, parity)) return;
+#if V_TIMING
+    c.slow_waits++;
+    const long long k0_ = clock64();
+    struct Acc_ { Ctx& c; long long k0; __device__ ~Acc_() { c.wait_clocks += clock64() - k0; } } acc_{c, k0_};
+#endif
     const u64 t0 = now_ns();
     u32 spins = 0;
     while (!mbar_try(bar, parity)) {
@@ -189,29 +200,52 @@ __device__ __forceinline__ void wait_mbar(Ctx& c, u32 bar, u32 parity, u32 where
     }
 }
 
-// Grid barrier for the consumer warps of all CTAs: every CTA publishes its generation in its own
-// flag word; warp 0 of every CTA polls all flags. One write and one round of reads, no atomics.
-__device__ __forceinline__ void grid_sync(Ctx& c) {
+// Grid barrier for the consumer warps of all CTAs, in two halves so that loads that do not depend
+// on other CTAs (the next phase's parameters) can be issued in between. One monotonic counter:
+// every CTA adds 1 (release), thread 0 of every CTA polls it until it reaches generation x CTAs.
+// Measured on B200 with 148 CTAs arriving together: 2400 cycles (1.3 us) per barrier, of which the
+// release fence is ~530 and the add ~270. Every variant tried was slower: one flag word per CTA
+// polled by all (6100 cycles: 148 x 148 polling loads delay the flag stores), 4 or 16 counters on
+// separate lines (4600), two levels of 16 (4000), an arrival counter plus a "go" word (3600).
+__device__ __forceinline__ void phase_end(Ctx& c) {
     cons_sync();
-    c.gen++;
-    if (c.warp == 0) {
-        if (c.lane == 0) st_release(c.bar + BAR_FLAGS + c.cta, c.gen);
-        if (!c.dead) {
+    c.gen += (u32)c.ncta;
+    if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(c.bar + BAR_COUNT) : "memory");
+}
+__device__ __forceinline__ void phase_wait(Ctx& c) {
+    if (c.tid == 0 && !c.dead) {
+        if ((int)(ld_acquire(c.bar + BAR_COUNT) - c.gen) < 0) {
             const u64 t0 = now_ns();
-            for (int i = c.lane; i < c.ncta; i += 32) {
-                u32 spins = 0;
-                while ((int)(ld_acquire(c.bar + BAR_FLAGS + i) - c.gen) < 0) {
-                    if ((++spins & 63u) == 0) {
-                        if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; break; }
-                        if (now_ns() - t0 > WAIT_NS) { give_up(c, 0x100u); break; }
-                    }
+            u32 spins = 0;
+            while ((int)(ld_acquire(c.bar + BAR_COUNT) - c.gen) < 0) {
+                if ((++spins & 63u) == 0) {
+                    if (ld_relaxed(c.bar + BAR_ABORT)) break;
+                    if (now_ns() - t0 > WAIT_NS) { give_up(c, 0x100u); break; }
                 }
-                if (c.dead) break;
             }
         }
     }
     cons_sync();
     if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
+}
+
+// 16-byte asynchronous copies global -> shared for the small per-phase parameters
+__device__ __forceinline__ void cp16(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// Parameters of the next phase into shared memory: LayerNorm gain and shift, the bias added when a
+// combined vector is initialised (all three V_D halves), and the bias of this CTA's NARROW tiles.
+__device__ __noinline__ void fetch_params(Ctx& c, const u16* gw, const u16* gb, const u16* ib, const u16* tb, int tiles) {
+    u16* prm = reinterpret_cast<u16*>(c.smem + SM_PRM);
+    const int per = V_D / 8;                       // 16-byte pieces per vector
+    for (int i = c.tid; i < 3 * per; i += NCONS) {
+        const int v = i / per, q = i % per;
+        const u16* src = v == 0 ? gw : (v == 1 ? gb : ib);
+        if (src) cp16(prm + v * V_D + q * 8, src + q * 8);
+    }
+    if (tb && c.tid < tiles * 2) cp16(prm + 3 * V_D + c.tid * 8, tb + c.tid * 8);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -239,7 +273,7 @@ __device__ __forceinline__ void produce_wide(Ctx& c, const unsigned char* src, i
     }
 }
 
-__device__ void producer(Ctx& c, const Place& P, const unsigned char* __restrict__ WP) {
+__device__ __noinline__ void producer(Ctx& c, const Place& P, const unsigned char* __restrict__ WP) {
     const unsigned char* base = WP + (size_t)P.base * FRAG_BYTES;
     for (int l = 0; l < V_L; l++) {
         const unsigned char* s = base + (size_t)l * P.layer * FRAG_BYTES;
@@ -393,8 +427,20 @@ __device__ __forceinline__ void act_store4(unsigned char* act, int b, int k, flo
     base[(t + 1) * 4 + 2 + reg] = l1;
 }
 
-// LayerNorm of the rows of z (global, fp32, [V_B][V_D]) into the operand tiles. One warp per row.
-__device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, const u16* __restrict__ gw, const u16* __restrict__ gb, unsigned char* act) {
+__device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, float v) {
+    const u16 hi = f2h(v), lo = f2h(v - h2f(hi));
+    const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1, half = kk & 1;
+    u16* base = reinterpret_cast<u16*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4 + t) * 16);
+    base[reg * 2 + half] = hi;
+    base[(2 + reg) * 2 + half] = lo;
+}
+
+// LayerNorm of the rows of z (global, fp32, [V_B][V_D]) into the operand tiles, one warp per row;
+// gain and shift come from the parameter block in shared memory. The same pass starts the vector
+// the following projection is combined into: init[b][d] += z[b][d] + bias[d], every CTA adding
+// its share of the elements (init was zeroed a phase earlier).
+__device__ __noinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act) {
+    const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
     for (int b = c.warp; b < V_B; b += NW) {
         float4 v[LNV];
         float s = 0.f;
@@ -423,27 +469,46 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, c
         for (int i = 0; i < LNV; i++) {
             const int d = (i * 32 + c.lane) * 4;
             if (d < V_D) {
-                const uint2 w = __ldg(reinterpret_cast<const uint2*>(gw + d));
-                const uint2 bb = __ldg(reinterpret_cast<const uint2*>(gb + d));
+                const uint2 w = *reinterpret_cast<const uint2*>(prm + d);
+                const uint2 bb = *reinterpret_cast<const uint2*>(prm + V_D + d);
                 float4 o;
                 o.x = (v[i].x - mean) * rs * h_lo(w.x) + h_lo(bb.x);
                 o.y = (v[i].y - mean) * rs * h_hi(w.x) + h_hi(bb.x);
                 o.z = (v[i].z - mean) * rs * h_lo(w.y) + h_lo(bb.y);
                 o.w = (v[i].w - mean) * rs * h_hi(w.y) + h_hi(bb.y);
                 act_store4(act, b, d, o);
+                if (init && ((i * 32 + c.lane) % c.ncta) == c.cta) {
+                    const uint2 ib = *reinterpret_cast<const uint2*>(prm + 2 * V_D + d);
+                    float* dst = init + (size_t)b * V_D + d;
+                    red_add(dst, v[i].x + h_lo(ib.x)); red_add(dst + 1, v[i].y + h_hi(ib.x));
+                    red_add(dst + 2, v[i].z + h_lo(ib.y)); red_add(dst + 3, v[i].w + h_hi(ib.y));
+                }
             }
         }
     }
     cons_sync();
 }
 
-// rows [k0*16, (k0+nk)*16) of x (global fp32 [V_B][V_D]) into operand tiles 0..nk-1
-__device__ __forceinline__ void slice_to_act(Ctx& c, const float* __restrict__ x, int k0, int nk, unsigned char* act) {
-    const int per_row = nk * 4;                     // float4 per row
-    for (int i = c.tid; i < V_B * per_row; i += NCONS) {
-        const int b = i / per_row, q = i % per_row;
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)b * V_D + k0 * 16 + q * 4));
-        act_store4(act, b, q * 4, v);
+// Attention output for the fold range [k0*16, (k0+nk)*16) of the projection, merged from the
+// per-chunk partial results (m, sum, unnormalised o[V_E]) of the attention phase, into operand
+// tiles 0..nk-1.
+#define PART_STRIDE (V_E + 2)
+__device__ __noinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act) {
+    const int cols = nk * 16;
+    for (int i = c.tid; i < V_B * cols; i += NCONS) {
+        const int b = i / cols, kk = i % cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
+        const float* p = part + (size_t)((b * V_H + h) * V_NCH) * PART_STRIDE;
+        float m[V_NCH], M = -3.0e38f;
+#pragma unroll
+        for (int ch = 0; ch < V_NCH; ch++) { m[ch] = __ldcg(p + ch * PART_STRIDE); M = fmaxf(M, m[ch]); }
+        float num = 0.f, den = 0.f;
+#pragma unroll
+        for (int ch = 0; ch < V_NCH; ch++) {
+            const float w = expf(m[ch] - M);
+            den += w * __ldcg(p + ch * PART_STRIDE + 1);
+            num += w * __ldcg(p + ch * PART_STRIDE + 2 + e);
+        }
+        act_store1(act, b, kk, num / den);
     }
     cons_sync();
 }
@@ -457,8 +522,9 @@ __device__ __forceinline__ void dot8(const uint4& kv, const float (&q)[8], float
 }
 
 #define ATT_UNROLL 4
-__device__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
-                               float* __restrict__ obuf, int b, int h, int l, int n) {
+// positions [s_lo, s_hi) of one (sequence, head); result: (running max, sum, unnormalised o[V_E]) at out
+__device__ __noinline__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
+                               float* __restrict__ out, int b, int h, int l, int s_lo, int n) {
     // 8 lanes per position (16 B each of the 128 B row), 4 positions per warp per round
     const int li = c.lane & 7, grp = c.warp * 4 + (c.lane >> 3);
     const int NG = NW * 4;
@@ -473,7 +539,7 @@ __device__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* 
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] = 0.f;
     // the trip count is the same for every lane of the warp (the shuffles below need all 32 lanes)
-    for (int base = 0; base < n; base += NG * ATT_UNROLL) {
+    for (int base = s_lo; base < n; base += NG * ATT_UNROLL) {
         const int s0 = base + grp;
         uint4 kk[ATT_UNROLL], vv[ATT_UNROLL];
 #pragma unroll
@@ -541,7 +607,8 @@ __device__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* 
             dd += ms[w * (V_E + 2) + 1] * sc;
             num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
         }
-        obuf[(size_t)b * V_D + h * V_E + c.tid] = num / dd;
+        out[2 + c.tid] = num;
+        if (c.tid == 0) { out[0] = M; out[1] = dd; }
     }
     cons_sync();
 }
@@ -561,7 +628,8 @@ struct Args {
 __device__ __forceinline__ int pos_of(const Args& a, int b) { return a.t[b * V_TSTRIDE]; }
 
 #if V_TIMING
-#define TICK(k) do { if (c.cta == 0 && c.tid == 0) { u64 now_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now_)); a.TS[k] += now_ - tlast_; tlast_ = now_; } } while (0)
+// thread 0 of CTA V_TIMING-1 sums clock64 deltas per site in shared memory (cheap) and adds them to TS at the end
+#define TICK(k) do { if (c.cta == V_TIMING - 1 && c.tid == 0) { const long long now_ = clock64(); ts_[k] += now_ - tlast_; tlast_ = now_; } } while (0)
 #else
 #define TICK(k) do { } while (0)
 #endif
@@ -570,18 +638,26 @@ __device__ void step_body(const Args& a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Ctx c;
     c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false;
+#if V_TIMING
+    c.wait_clocks = 0; c.slow_waits = 0;
+#endif
     c.cta = blockIdx.x; c.ncta = gridDim.x; c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
 #if V_TIMING
-    u64 tlast_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tlast_));
+    __shared__ long long ts_[16];
+    if (threadIdx.x == 0) for (int i = 0; i < 16; i++) ts_[i] = 0;
+    long long tlast_ = clock64();
+    const u64 t_begin_ = now_ns();
 #endif
 
     // inputs outside their ranges would index outside the caches and tables: refuse the step
     // (every CTA sees the same values and takes the same branch)
+    int* s_pos = reinterpret_cast<int*>(smem + SM_MISC + NW * (V_E + 2) * 4 + V_B * 8 * NW + 16);
     {
         bool bad = false;
         for (int b = 0; b < V_B; b++) {
             const int tb = pos_of(a, b), xb = a.x[b];
             bad |= (tb < 0) | (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
+            if (c.tid == 0) s_pos[b] = tb;
         }
         if (bad) {
             if (c.cta == 0 && c.tid == 0) atomicCAS(a.bar + BAR_STATUS, 0u, 0x900u);
@@ -600,36 +676,50 @@ __device__ void step_body(const Args& a) {
 
     const Place P = load_place(a.PT, c.cta);
     if (c.warp == NW) {
-        if (c.lane == 0) producer(c, P, a.WP);
+        if (c.lane == 0) {
+            producer(c, P, a.WP);
+#if V_TIMING
+            if (c.cta == V_TIMING - 1) { a.TS[18] += (u64)c.wait_clocks; a.TS[19] += c.slow_waits; a.TS[20] += c.chunk; }
+#endif
+        }
         return;
     }
 
-    c.gen = ld_relaxed(a.bar + BAR_FLAGS + c.cta);
+    c.gen = 0;      // the barrier counter is zero at launch: the last CTA of every step clears it
     unsigned char* act = smem + SM_ACT;
     unsigned char* gact = smem + SM_GACT;
     float* red = reinterpret_cast<float*>(smem + SM_RED);
+    const u16* prm = reinterpret_cast<const u16*>(smem + SM_PRM);
     float* Z = a.S + V_OFF_Z;
     float* qbuf = a.S + V_OFF_Q;
-    float* obuf = a.S + V_OFF_O;
+    float* part = a.S + V_OFF_PART;
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
+    const size_t ZS = (size_t)V_B * V_D;
 
-    // Q1: z0 = wte[x] + wpe[t]
+    // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
         const int b = i / V_D, d = i % V_D;
-        Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)pos_of(a, b) * V_D + d]);
+        Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)s_pos[b] * V_D + d]);
+        Z[ZS + i] = 0.f;
     }
     TICK(0);
-    grid_sync(c);
+    phase_end(c);
+    fetch_params(c, a.ln1w, a.ln1b, a.ob, a.qkvb + P.qkv_j0 * 16, P.qkv_nj);
+    phase_wait(c);
     TICK(1);
 
     for (int l = 0; l < V_L; l++) {
-        float* zin = Z + (size_t)((2 * l) % 3) * V_B * V_D;
-        float* z1 = Z + (size_t)((2 * l + 1) % 3) * V_B * V_D;
-        float* z2 = Z + (size_t)((2 * l + 2) % 3) * V_B * V_D;
+        float* zin = Z + (size_t)((2 * l) % 3) * ZS;
+        float* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
+        float* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
 
-        // ---- LN1 + QKV (+bias), q to scratch, K and V rounded to fp16 into the cache at t
-        for (int i = gtid; i < V_B * V_D; i += gthreads) { z1[i] = 0.f; z2[i] = 0.f; }
-        ln_to_act(c, zin, a.ln1w + (size_t)l * V_D, a.ln1b + (size_t)l * V_D, act);
+        // ---- LN1 + QKV (+bias): q to scratch, K and V rounded to fp16 into the cache at t.
+        //      The same pass starts z1 = z + ob (the projection adds into it two phases later)
+        //      and clears z2, which nobody reads any more.
+        for (int i = gtid; i < V_B * V_D; i += gthreads) z2[i] = 0.f;
+        cp_wait();
+        cons_sync();
+        ln_to_act(c, zin, z1, act);
         {
             float acc[WN_MAX][V_NB][4];
             narrow_gemm(c, KT_D, P.qkv_nj, act, acc);
@@ -640,31 +730,34 @@ __device__ void step_body(const Args& a) {
                 narrow_coord(o, jj, j_in, b);
                 if (b < V_B) {
                     const int j = (P.qkv_j0 + jj) * 16 + j_in;
-                    const float v = red[o] + h2f(a.qkvb[(size_t)l * 3 * V_D + j]);
+                    const float v = red[o] + h2f(prm[3 * V_D + jj * 16 + j_in]);
                     if (j < V_D) qbuf[(size_t)b * V_D + j] = v;
                     else {
-                        const size_t at = ((size_t)(b * V_L + l) * V_TMAX + pos_of(a, b)) * V_D + (j % V_D);
+                        const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (j % V_D);
                         if (j < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
                     }
                 }
             }
         }
         TICK(2);
-        grid_sync(c);
+        phase_end(c);
+        phase_wait(c);
         TICK(3);
 
-        // ---- attention, one (sequence, head) at a time
-        for (int it = c.cta; it < V_B * V_H; it += c.ncta) {
-            const int b = it / V_H, h = it % V_H;
-            attention_item(c, a.keys, a.vals, qbuf, obuf, b, h, l, pos_of(a, b) + 1);
+        // ---- attention: one (sequence, head, chunk of positions) at a time, partial results to scratch
+        for (int it = c.cta; it < V_B * V_H * V_NCH; it += c.ncta) {
+            const int ch = it % V_NCH, bh = it / V_NCH, b = bh / V_H, h = bh % V_H;
+            const int n = s_pos[b] + 1, cs = (n + V_NCH - 1) / V_NCH;
+            attention_item(c, a.keys, a.vals, qbuf, part + (size_t)it * PART_STRIDE, b, h, l, ch * cs, min(n, (ch + 1) * cs));
         }
         TICK(4);
-        grid_sync(c);
+        phase_end(c);
+        phase_wait(c);
         TICK(5);
 
-        // ---- attn-proj: z1 = z + o . ow + ob, partial sums over this CTA's fold range
+        // ---- attn-proj: z1 += o . ow, partial sums over this CTA's fold range
         if (P.proj_nj) {
-            slice_to_act(c, obuf, P.proj_k0, P.proj_nk, act);
+            merge_to_act(c, part, P.proj_k0, P.proj_nk, act);
             float acc[V_NB][4];
             wide_gemm(c, P.proj_nk, P.proj_nj, act, 0, acc);
             if (c.warp < P.proj_nj) {
@@ -674,23 +767,29 @@ __device__ void step_body(const Args& a) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const int j = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                        if (b < V_B) {
-                            float v = acc[nb][i];
-                            if (P.proj_k0 == 0) v += __ldcg(zin + (size_t)b * V_D + j) + h2f(a.ob[(size_t)l * V_D + j]);
-                            red_add(z1 + (size_t)b * V_D + j, v);
-                        }
+                        if (b < V_B) red_add(z1 + (size_t)b * V_D + j, acc[nb][i]);
                     }
             }
         }
         TICK(6);
-        grid_sync(c);
+        phase_end(c);
+        fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
+                     a.fcb + (size_t)l * V_F + P.fc_j0 * 16, P.fc_nj);
+        phase_wait(c);
         TICK(7);
 
-        // ---- LN2 + FC + GELU on this CTA's slice of f, then its partial of the MLP projection
-        ln_to_act(c, z1, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, act);
+        // ---- LN2 + FC + GELU on this CTA's slice of f, then its partial of the MLP projection.
+        //      The LN pass starts z2 = z1 + pb; zin is free from here on and is cleared for the
+        //      next layer's projection.
+        for (int i = gtid; i < V_B * V_D; i += gthreads) zin[i] = 0.f;
+        cp_wait();
+        cons_sync();
+        ln_to_act(c, z1, z2, act);
+        TICK(12);
         {
             float acc[WN_MAX][V_NB][4];
             narrow_gemm(c, KT_D, P.fc_nj, act, acc);
+            TICK(13);
             narrow_reduce(c, P.fc_nj, acc);
             // g = gelu(u + fcb) -> operand tiles of the projection: fold index = jj*16 + j_in
             const int total = P.fc_nj * V_NB * 128;
@@ -699,17 +798,13 @@ __device__ void step_body(const Args& a) {
                 narrow_coord(o, jj, j_in, b);
                 float g = 0.f;
                 if (b < V_B) {
-                    const float u = red[o] + h2f(a.fcb[(size_t)l * V_F + (P.fc_j0 + jj) * 16 + j_in]);
+                    const float u = red[o] + h2f(prm[3 * V_D + jj * 16 + j_in]);
                     g = V_GELU_A * u * (1.0f + tanhf(V_GELU_B * (u + V_GELU_C * u * u * u)));
                 }
-                // single element store: halves of the head and remainder words
-                const u16 hi = f2h(g), lo = f2h(g - h2f(hi));
-                const int reg = j_in >> 3, t = (j_in & 7) >> 1, half = j_in & 1;
-                u16* base = reinterpret_cast<u16*>(gact + ((size_t)(jj * V_NB + (b >> 3)) * 32 + (b & 7) * 4 + t) * 16);
-                base[reg * 2 + half] = hi;
-                base[(2 + reg) * 2 + half] = lo;
+                act_store1(gact, b, jj * 16 + j_in, g);
             }
             cons_sync();
+            TICK(14);
         }
         for (int jg = 0; jg < JT_D; jg += 8) {
             const int width = min(8, JT_D - jg);
@@ -722,22 +817,26 @@ __device__ void step_body(const Args& a) {
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
                         const int j = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                        if (b < V_B) {
-                            float v = acc[nb][i];
-                            if (P.fc_j0 == 0) v += __ldcg(z1 + (size_t)b * V_D + j) + h2f(a.pb[(size_t)l * V_D + j]);
-                            red_add(z2 + (size_t)b * V_D + j, v);
-                        }
+                        if (b < V_B) red_add(z2 + (size_t)b * V_D + j, acc[nb][i]);
                     }
             }
         }
         TICK(8);
-        grid_sync(c);
+        phase_end(c);
+        if (l + 1 < V_L)
+            fetch_params(c, a.ln1w + (size_t)(l + 1) * V_D, a.ln1b + (size_t)(l + 1) * V_D, a.ob + (size_t)(l + 1) * V_D,
+                         a.qkvb + (size_t)(l + 1) * 3 * V_D + P.qkv_j0 * 16, P.qkv_nj);
+        else
+            fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
+        phase_wait(c);
         TICK(9);
     }
 
     // ---- LN_f + logits + argmax
-    float* zf = Z + (size_t)((2 * V_L) % 3) * V_B * V_D;
-    ln_to_act(c, zf, a.lnfw, a.lnfb, act);
+    float* zf = Z + (size_t)((2 * V_L) % 3) * ZS;
+    cp_wait();
+    cons_sync();
+    ln_to_act(c, zf, (float*)0, act);
     u64 best[V_NB][2];
 #pragma unroll
     for (int nb = 0; nb < V_NB; nb++) { best[nb][0] = 0; best[nb][1] = 0; }
@@ -802,10 +901,19 @@ __device__ void step_body(const Args& a) {
 #if V_FEEDBACK
             for (int b = 0; b < (V_TSTRIDE ? V_B : 1); b++) a.t_out[b] += V_TSTEP;
 #endif
+            atomicExch(a.bar + BAR_COUNT, 0u);     // every CTA is past its last barrier
             atomicExch(a.bar + BAR_DONE, 0u);
         }
     }
     TICK(11);
+#if V_TIMING
+    if (c.cta == V_TIMING - 1 && c.tid == 0) {
+        for (int i = 0; i < 16; i++) a.TS[i] += (u64)ts_[i];
+        a.TS[16] += (u64)c.wait_clocks; a.TS[17] += c.slow_waits;
+        a.TS[21] += now_ns() - t_begin_;        // nanoseconds of this CTA's launch, to convert clocks
+        a.TS[22] += (u64)(clock64() - (tlast_ - 0)) * 0 + 1;   // launches
+    }
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------

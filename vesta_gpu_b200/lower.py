@@ -355,14 +355,16 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     off_logit, off_next = 0, up(B * N)
     off_z = up(off_next + B)
     off_q = off_z + 3 * up(B * D)
-    off_o = off_q + up(B * D)
-    off_best = off_o + up(B * D)
+    # position chunks per (sequence, head) in the attention phase: fewest rounds of the grid per position
+    nch = min(range(1, 17), key=lambda k: (math.ceil(B * H * k / grid) / k, k))
+    off_part = off_q + up(B * D)
+    off_best = off_part + up(B * H * nch * (E + 2))
     scratch_floats = off_best + up(2 * B)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     KT_D = D // 16
-    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + NW * WN_MAX * NB * 128 * 4
-             + NW * (E + 2) * 4 + B * 8 * NW + 64 + 16)
+    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + NW * WN_MAX * NB * 128 * 4 + (3 * D + WN_MAX * 16) * 2 + 16
+             + NW * (E + 2) * 4 + B * 8 * NW + B * 4 + 64 + 16)
     nslot = (SMEM_LIMIT - fixed - 1024) // (CHUNK_TILES * 512 + 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget at this batch')
@@ -376,8 +378,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
-                V_TIMING=int(bool(timing)), V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_OFF_O=off_o, V_OFF_BEST=off_best)
+                V_TIMING=int(timing), V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
+                V_MAXGRID=grid, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch)
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
@@ -414,7 +416,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         (f'{q["$z0"]} (embed)', 'grid-stride, then barrier'),
         (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', 'every CTA recomputes, one warp per row, into mma operand tiles'),
         (f'{q["$qkv"]} + emits', f'NARROW: whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA; bias, q, K/V emit in the epilogue'),
-        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)', 'one CTA per (sequence, head), online softmax in registers'),
+        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)', f'one CTA per (sequence, head, 1/{nch} of the positions), online softmax in registers, merged by the projection'),
         (f'{q["$oo"]}, {q["$z1"]}', f'WIDE: {notes["proj_units"]} units of 8 output tiles x {notes["proj_nk"]} fold tiles, fp32 atomics'),
         (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', 'every CTA recomputes'),
         (f'{q["$u"]}, {q["$g"]}', f'NARROW: {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
@@ -424,9 +426,11 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes'),
     ]
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
-        + ['logits', 'finish']
+        + ['logits', 'finish', 'mlp: LN2', 'mlp: FC', 'mlp: GELU', '-',
+           'consumer stream wait (clocks)', 'consumer waits not ready', 'producer wait (clocks)', 'producer waits not ready',
+           'chunks', 'launch ns', 'launches']
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
-                  barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=16 + max(grid, 1024),
+                  barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
                   dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes), roles=roles)
     return low
