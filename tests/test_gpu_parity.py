@@ -1,0 +1,231 @@
+"""Parity of the CUDA path with the reference interpreter (through the golden fixtures) and with
+the CPU oracle, on a B200. Everything goes through the public API, i.e. through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import load, fixture_inputs, teacher_tokens, close, TIGHT, MARGIN
+
+pytestmark = pytest.mark.gpu
+
+
+def model(sh, seed, init, batch, tmax, **kw):
+    from vesta_gpu_b200.synth import SynthGPT2
+    from vesta_gpu_b200.gpt2 import VestaGPT2
+    hf = SynthGPT2(sh, seed, init)
+    return VestaGPT2(hf, batch=batch, tmax=tmax, **kw), hf
+
+
+def run_fixture(name, seqs=None):
+    """teacher-forced decode of the fixture's sequences as one batch; every step's token and every
+    kept step's logits against the reference interpreter's"""
+    g = load(name)
+    sh, seed, init, prompts, gen, keep, stride = fixture_inputs(g)
+    seqs = list(range(prompts.shape[0])) if seqs is None else seqs
+    P = prompts.shape[1]
+    steps = P + gen
+    m, _ = model(sh, seed, init, len(seqs), steps)
+    m.reset()
+    feed = np.stack([teacher_tokens(g, i, P) for i in seqs])           # [B, steps]
+    feed_d = torch.from_numpy(feed).cuda()
+    worst, bad = 0.0, []
+    for t in range(steps):
+        m.x.copy_(feed_d[:, t])
+        m.step()
+        nxt = m.next().cpu().numpy().astype(np.int64)
+        lg = m.logits()[:, ::stride].cpu().numpy() if t in keep else None
+        for r, i in enumerate(seqs):
+            if g[f'margins_{i}'][t] > MARGIN and nxt[r] != g[f'tokens_{i}'][t]:
+                bad.append((i, t, int(nxt[r]), int(g[f'tokens_{i}'][t])))
+            if lg is not None:
+                ref = g[f'logits_{i}'][keep.index(t)]
+                assert close(lg[r], ref), (name, i, t)
+                worst = max(worst, float(np.abs(lg[r] - ref).max()))
+    m.k.check()
+    assert not bad, bad[:5]
+    assert worst < TIGHT, worst
+    assert int(m.t.cpu()[0]) == steps
+    return worst
+
+
+def test_tiny_fixture():
+    run_fixture('tiny_b3')
+
+
+def test_tiny3_fixture_vocab_not_multiple_of_16():
+    run_fixture('tiny3_b2')
+
+
+def test_gpt2_small_rich_init():
+    run_fixture('gpt2_rich_b1')
+
+
+def test_gpt2_small_batch1_config():
+    """128-token prompt + 256 greedy steps, batch 1"""
+    run_fixture('gpt2_cfg2', seqs=[0])
+
+
+def test_gpt2_small_batch8_config():
+    """eight sequences, 128 + 256 positions"""
+    run_fixture('gpt2_cfg2')
+
+
+def test_gpt2_xl_shape():
+    run_fixture('gpt2_xl_b1')
+
+
+def test_free_running_feedback_matches_reference_tokens():
+    """feedback on, no host write between generated steps: the stream equals the reference's up to the
+    first step whose margin is below the bar"""
+    g = load('gpt2_cfg2')
+    sh, seed, init, prompts, gen, keep, stride = fixture_inputs(g)
+    B, P = prompts.shape
+    m, _ = model(sh, seed, init, B, P + gen)
+    m.reset()
+    pd = torch.from_numpy(prompts).cuda()
+    for t in range(P):
+        m.x.copy_(pd[:, t]); m.step()
+    toks = [m.x.clone()]
+    for _ in range(gen - 1):
+        m.step(); toks.append(m.x.clone())
+    got = torch.stack(toks, 1).cpu().numpy()
+    m.k.check()
+    for i in range(B):
+        ref = g[f'tokens_{i}'][P - 1:P - 1 + gen]
+        sure = g[f'margins_{i}'][P - 1:P - 1 + gen] > MARGIN
+        stop = gen if sure.all() else int(np.argmin(sure))
+        assert np.array_equal(got[i, :stop + 0], ref[:stop]), i
+
+
+@pytest.mark.parametrize('batch', [1, 2, 5, 8])
+def test_against_oracle_other_batches(batch):
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import make_prompts
+    steps = 9
+    m, hf = model(TINY3, 11, 'rich', batch, steps)
+    W = O.upcast(hf.weights)
+    feed = make_prompts(TINY3, batch, steps, seed=batch)
+    caches = [O.new_cache(TINY3, steps) for _ in range(batch)]
+    m.reset()
+    for t in range(steps):
+        m.x.copy_(torch.from_numpy(feed[:, t].copy()).cuda()); m.step()
+        lg = m.logits().cpu().numpy(); nx = m.next().cpu().numpy()
+        for i in range(batch):
+            ref, rn = O.step(TINY3, W, caches[i][0], caches[i][1], int(feed[i, t]), t)
+            assert np.abs(lg[i] - ref).max() < TIGHT
+            if O.margin(ref) > MARGIN:
+                assert int(nx[i]) == rn
+    # the cache holds the fp16-rounded K and V of every position (gpt2.vst:48-49); allow one fp16 step
+    k = m.keys.cpu().numpy().astype(np.float32)
+    for i in range(batch):
+        ref = caches[i][0].astype(np.float32)
+        assert np.abs(k[i, :, :steps] - ref).max() <= 2e-3
+    m.k.check()
+
+
+def test_per_sequence_positions_ragged_starts():
+    """every sequence at its own position: sequence b starts b*2 steps late"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY
+    from vesta_gpu_b200.synth import make_prompts
+    B, steps = 4, 12
+    m, hf = model(TINY, 3, 'rich', B, steps, per_sequence_t=True, feedback=False)
+    W = O.upcast(hf.weights)
+    feed = make_prompts(TINY, B, steps, seed=9)
+    caches = [O.new_cache(TINY, steps) for _ in range(B)]
+    m.reset()
+    for s in range(steps):
+        pos = np.array([max(0, s - 2 * b) for b in range(B)], np.int32)
+        live = [s >= 2 * b for b in range(B)]
+        x = np.array([feed[b, pos[b]] for b in range(B)], np.int32)
+        m.x.copy_(torch.from_numpy(x).cuda()); m.t.copy_(torch.from_numpy(pos).cuda())
+        m.step()
+        lg = m.logits().cpu().numpy()
+        for b in range(B):
+            if live[b]:
+                ref, _ = O.step(TINY, W, caches[b][0], caches[b][1], int(x[b]), int(pos[b]))
+                assert np.abs(lg[b] - ref).max() < TIGHT, (s, b)
+    m.k.check()
+
+
+def test_batch_rows_are_independent_at_full_size():
+    """the same prompt in all 8 rows gives the same tokens in every row, equal to the batch-1 run"""
+    from vesta_gpu_b200.shapes import GPT2_SMALL
+    from vesta_gpu_b200.synth import make_prompts
+    P, G = 16, 24
+    prompt = make_prompts(GPT2_SMALL, 1, P, seed=5)[0]
+    outs = {}
+    for B in (1, 8):
+        m, _ = model(GPT2_SMALL, 0, 'baseline', B, P + G)
+        m.reset()
+        for t in range(P):
+            m.x.fill_(int(prompt[t])); m.step()
+        first = m.logits().clone()
+        toks = [m.x.clone()]
+        for _ in range(G - 1):
+            m.step(); toks.append(m.x.clone())
+        outs[B] = (torch.stack(toks, 1).cpu().numpy(), first.cpu().numpy())
+        m.k.check()
+        del m
+    t8, l8 = outs[8]
+    assert all(np.array_equal(t8[0], t8[r]) for r in range(8))
+    assert np.abs(l8 - l8[0:1]).max() < 1e-4
+    assert np.abs(l8[0] - outs[1][1][0]).max() < 1e-4
+    assert np.array_equal(t8[0], outs[1][0][0])
+
+
+def test_multi_step_launch_and_reset():
+    from vesta_gpu_b200.shapes import TINY
+    m, _ = model(TINY, 3, 'rich', 3, 32)
+    def run(chunked):
+        m.reset(); m.x.copy_(torch.tensor([1, 2, 3], dtype=torch.int32))
+        if chunked:
+            m.step(20)
+        else:
+            for _ in range(20):
+                m.step()
+        return m.x.cpu().numpy().copy(), m.logits().cpu().numpy().copy(), int(m.t.cpu()[0])
+    a, b = run(False), run(True)
+    assert np.array_equal(a[0], b[0]) and a[2] == b[2] == 20
+    assert np.abs(a[1] - b[1]).max() < 1e-4
+    m.k.check()
+
+
+def test_out_of_range_inputs_are_refused_not_executed():
+    from vesta_gpu_b200.shapes import TINY
+    m, _ = model(TINY, 3, 'rich', 2, 8)
+    m.reset(); m.x.fill_(3); m.step()
+    before = m.logits().clone()
+    m.t.fill_(8)                                  # position == tmax: outside the cache
+    m.step()
+    assert 'out of range' in str(m.k.status())
+    assert torch.equal(before, m.logits())        # nothing ran
+    with pytest.raises(RuntimeError):
+        m.k.check()
+    m.k.bar.zero_(); m.t.fill_(1); m.x.fill_(TINY.N)      # token id == vocabulary size
+    m.step()
+    assert 'out of range' in str(m.k.status())
+    m.k.bar.zero_(); m.x.fill_(3); m.step()
+    assert m.k.status() == 0
+
+
+def test_kernel_api_mirrors_reference():
+    """vesta/launch.py:29-73: attributes, view(), bind() assertions"""
+    from vesta_gpu_b200.shapes import TINY
+    from vesta_gpu_b200.launch import Kernel
+    m, _ = model(TINY, 3, 'rich', 2, 8)
+    k = m.k
+    for attr in ('mod', 'fn', 'smem', 'sms', 'grid', 'block', 'lowered', 'S', 'bar', 'TS', 'args', 'keep'):
+        assert hasattr(k, attr), attr
+    assert k.grid == k.sms == torch.cuda.get_device_properties(0).multi_processor_count
+    assert k.view('logit').shape == (2, TINY.N) and k.view('next').shape == (2,)
+    assert k.view('next').dtype == torch.float32
+    R = dict(k.keep)
+    R['wte'] = R['wte'].t().contiguous().t()      # same values, not contiguous
+    with pytest.raises(AssertionError):
+        k.bind(R)
+    R['wte'] = k.keep['wte'].float()
+    with pytest.raises(AssertionError):
+        k.bind(R)
+    assert m.weight_bytes == TINY.weight_bytes() and m.kv_bytes(5) == 2 * TINY.L * 2 * 5 * TINY.D * 2

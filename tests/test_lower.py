@@ -1,0 +1,149 @@
+"""Recognition and placement (vesta_gpu_b200/lower.py), on the CPU."""
+import numpy as np
+import pytest
+
+from vesta_gpu_b200 import lower as lw
+from vesta_gpu_b200.build import lower_for, residue_spec
+from vesta_gpu_b200.program_text import decode_program
+from vesta_gpu_b200.shapes import GPT2_SMALL, GPT2_XL, TINY, TINY3
+
+
+def stream_tiles(rec, dims, cta):
+    """tiles of one CTA's stream as (kind, layer, j tile, k tile), in stream order: the index
+    arithmetic of pack_narrow / pack_wide in csrc/step_kernel.cuh restated"""
+    D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
+    KT_D, JT_D = D // 16, D // 16
+    base, layer, qj0, qnj, pj0, pnj, pk0, pnk, fj0, fnj, lj0, lnj = [int(v) for v in rec[cta][:12]]
+
+    def narrow(kind, l, j0, nj, kt):
+        return [(kind, l, j0 + i % nj, i // nj) for i in range(nj * kt)]
+
+    def wide(kind, l, j0, nj, k0, nk):
+        out = []
+        for i in range(nj * nk):
+            grp = i // (8 * nk)
+            width = min(8, nj - grp * 8)
+            r = i - grp * 8 * nk
+            out.append((kind, l, j0 + grp * 8 + r % width, k0 + r // width))
+        return out
+    tiles = []
+    for l in range(L):
+        seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
+            + narrow('fc', l, fj0, fnj, KT_D) + wide('p2', l, 0, JT_D, fj0, fnj)
+        assert len(seg) == layer
+        tiles += seg
+    tiles += wide('logit', 0, lj0, lnj, 0, KT_D)
+    return base, tiles
+
+
+@pytest.mark.parametrize('sh,batch,grid', [(GPT2_SMALL, 1, 148), (GPT2_SMALL, 8, 148), (TINY, 3, 148), (TINY3, 2, 148),
+                                           (GPT2_XL, 1, 148), (GPT2_SMALL, 8, 132), (TINY, 1, 7)])
+def test_every_weight_tile_exactly_once(sh, batch, grid):
+    low = lower_for(sh, batch, 64, grid=grid)
+    dims = low.dims
+    D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
+    want = {'qkv': (3 * D // 16, D // 16), 'proj': (D // 16, D // 16), 'fc': (F // 16, D // 16),
+            'p2': (D // 16, F // 16), 'logit': ((N + 15) // 16, D // 16)}
+    seen = {k: np.zeros((L if k != 'logit' else 1,) + v, np.int32) for k, v in want.items()}
+    cursor = 0
+    for c in range(grid):
+        base, tiles = stream_tiles(low.place, dims, c)
+        assert base == cursor                       # streams are laid end to end
+        cursor += len(tiles)
+        for kind, l, j, k in tiles:
+            seen[kind][l, j, k] += 1
+    assert cursor * 512 == low.packed_bytes
+    for k, v in seen.items():
+        assert v.min() == 1 and v.max() == 1, k
+    # every output tile of the projection has exactly one CTA that starts at fold tile 0, NARROW widths fit
+    assert low.place[:, 3].max() <= lw.WN_MAX and low.place[:, 9].max() <= lw.WN_MAX
+
+
+def test_streams_are_balanced():
+    low = lower_for(GPT2_SMALL, 8, 384)
+    n = low.dims['notes']
+    assert n['tiles_max'] / n['tiles_mean'] < 1.01
+    low = lower_for(GPT2_XL, 1, 384)
+    n = low.dims['notes']
+    assert n['tiles_max'] / n['tiles_mean'] < 1.05      # 48 layers of coarse per-layer units
+
+
+def test_lowered_fields_match_reference_contract():
+    """vesta/lower.py:69-79: src, params, scratch, scratch_floats, shared_bytes, barriers_per_launch, plan, sites, counters"""
+    low = lower_for(GPT2_SMALL, 8, 384)
+    names = [p[0] for p in low.params]
+    assert names == ['x', 't', 'wte', 'wpe', 'ln1w', 'ln1b', 'qkvw', 'qkvb', 'ow', 'ob', 'ln2w', 'ln2b', 'fcw', 'fcb',
+                     'pw', 'pb', 'lnfw', 'lnfb', 'keys', 'vals']
+    emitted = {p[0] for p in low.params if p[2]}
+    assert emitted == {'x', 't', 'keys', 'vals'}
+    off, axes, shape = low.scratch['logit']
+    assert shape == (8, 50257) and off == 0
+    off2, _, shape2 = low.scratch['next']
+    assert shape2 == (8,) and off2 >= 8 * 50257 and low.scratch_floats > off2 + 8
+    assert low.shared_bytes <= 227 * 1024
+    assert low.barriers_per_launch == 1 + 4 * 12          # the reference needs 113 at batch 8
+    assert 'vesta_step' in low.src and 'vesta_pack' in low.src and low.counters >= 64
+    assert len(low.plan) >= 8 and all(len(p) == 2 for p in low.plan)
+    no_fb = lower_for(GPT2_SMALL, 1, 64, feedback=False)
+    assert {p[0] for p in no_fb.params if p[2]} == {'keys', 'vals'}
+
+
+def test_constants_read_from_the_program():
+    low = lower_for(GPT2_XL, 1, 64)
+    d = low.dims
+    assert (d['L'], d['D'], d['H'], d['F'], d['N']) == (48, 1600, 25, 6400, 50257)
+    assert d['eps'] == 1e-5 and d['scale'] == 8.0 and d['gelu'] == (0.5, 0.7978845608028654, 0.044715)
+    text = decode_program(TINY, eps=0.001)
+    spec = residue_spec(TINY, 1, 16)
+    low = lw.lower(text, spec, {'s': 16}, batch=1, per_token=('x', 'keys', 'vals'), outputs=('logit', 'next'))
+    assert low.dims['eps'] == 0.001 and '#define V_EPS 0.001' in low.src
+
+
+def mutate(text, old, new):
+    assert old in text
+    return text.replace(old, new, 1)
+
+
+@pytest.mark.parametrize('old,new', [
+    ('tanh(', 'exp('),                                   # another activation
+    ('/ 8', '* 8'),                                      # scores multiplied instead of divided
+    ('z1[d] = z[d] + oo[d] + ob[l, d]', 'z1[d] = oo[d] + ob[l, d]'),      # no residual
+    ('fold max s: sc[h, s]', 'fold min s: sc[h, s]'),
+    ('next = fold min n:', 'next = fold max n:'),        # ties to the highest id
+    ('axis j = 384', 'axis j = 400'),                    # QKV not three widths
+    ('    q[h, e] = qkv[h * 64 + e]\n', ''),             # a statement missing
+])
+def test_programs_outside_the_family_are_refused(old, new):
+    text = mutate(decode_program(TINY), old, new)
+    with pytest.raises(NotImplementedError):
+        lw.lower(text, residue_spec(TINY, 1, 16), {'s': 16}, batch=1, per_token=('x', 'keys', 'vals'))
+
+
+def test_residue_checks():
+    text = decode_program(TINY)
+    spec = residue_spec(TINY, 2, 16)
+    with pytest.raises(ValueError):
+        lw.lower(text, dict(spec, wte=((TINY.N, TINY.D + 16), 'f16')), {'s': 16}, batch=2, per_token=('x', 'keys', 'vals'))
+    with pytest.raises(NameError):
+        lw.lower(text, {k: v for k, v in spec.items() if k != 'pb'}, {'s': 16}, batch=2, per_token=('x', 'keys', 'vals'))
+    with pytest.raises(NotImplementedError):
+        lw.lower(text, dict(spec, wte=((TINY.N, TINY.D), 'f32')), {'s': 16}, batch=2, per_token=('x', 'keys', 'vals'))
+    with pytest.raises(ValueError):
+        lw.lower(text, spec, {}, batch=2, per_token=('x', 'keys', 'vals'))
+    with pytest.raises(NotImplementedError):
+        lw.lower(text, spec, {'s': 16}, batch=2, per_token=('x', 'keys', 'vals'), feedback={'x': 'best', 't': 1})
+
+
+def test_renamed_program_is_recognised():
+    """names are read from the program, not assumed"""
+    text = decode_program(TINY).replace('qkv', 'proj3').replace('zL', 'out_state').replace('sc[', 'score[').replace('sc[h, s]', 'score[h, s]')
+    spec = residue_spec(TINY, 1, 16)
+    spec = {k.replace('qkv', 'proj3'): v for k, v in spec.items()}
+    low = lw.lower(text, spec, {'s': 16}, batch=1, per_token=('x', 'keys', 'vals'), outputs=('logit', 'next'))
+    assert low.roles['qkvw'] == 'proj3w' and 'R_proj3w' in low.src
+
+
+def test_per_sequence_positions():
+    low = lower_for(TINY, 4, 32, per_sequence_t=True)
+    assert '#define V_TSTRIDE 1' in low.src
+    assert dict((p[0], p[1]) for p in low.params)['t'] == 'i32'
