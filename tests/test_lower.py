@@ -21,10 +21,10 @@ def stream_tiles(rec, dims, cta):
     def wide(kind, l, j0, nj, k0, nk):
         out = []
         for i in range(nj * nk):
-            grp = i // (8 * nk)
-            width = min(8, nj - grp * 8)
-            r = i - grp * 8 * nk
-            out.append((kind, l, j0 + grp * 8 + r % width, k0 + r // width))
+            grp = i // (lw.WG * nk)
+            width = min(lw.WG, nj - grp * lw.WG)
+            r = i - grp * lw.WG * nk
+            out.append((kind, l, j0 + grp * lw.WG + r % width, k0 + r // width))
         return out
     tiles = []
     for l in range(L):

@@ -1,8 +1,8 @@
 // One persistent cooperative kernel per decode step, written for sm_100a (B200, 148 SMs).
 //
 // This text is the body that vesta_gpu_b200/lower.py places behind a block of #defines (model
-// sizes, placement constants, scratch offsets, parameter names) and a generated kernel signature.
-// It compiles with NVRTC (no headers) and with nvcc.
+// sizes, placement constants, scratch offsets) and a generated kernel signature. It compiles with
+// NVRTC (no headers) and with nvcc.
 //
 // Execution model
 //   * grid = one CTA per SM, block = NW consumer warps + 1 producer warp.
@@ -18,16 +18,17 @@
 //   * NARROW placement: a CTA owns a few output tiles over the whole fold; its warps split the fold
 //     and combine through shared memory; the epilogue sees complete sums (bias, GELU, KV emit).
 //     WIDE placement: a CTA owns a range of the fold for many output tiles; each warp owns output
-//     tiles; sums that span CTAs are combined with fp32 atomics into a zeroed vector.
+//     tiles; sums that span CTAs are combined with fp32 atomics into a vector zeroed a phase earlier.
 //   * Per layer: [LN1 + QKV + KV emit] | [attention] | [attn-proj + residual] | [LN2 + FC + GELU +
 //     MLP-proj + residual], grid barriers between them; then LN_f + logits + argmax + feedback,
 //     finished by the last CTA to arrive (no barrier).
+//   * The whole step is ONE loop over phases with one GEMM site, one LayerNorm site and one barrier
+//     site, and the big loops are kept rolled: measured on B200, a step kernel of 100 KB of code
+//     ran instruction-fetch bound (88 % instruction-cache hit rate, ~90 cycles per 128 B of code,
+//     every layer re-fetching the kernel), several times slower than its memory traffic allowed.
 //   * Every wait (grid barrier, mbarrier) is bounded; on expiry the kernel records where in bar[]
 //     and every later wait falls through, so the launch always ends.
 
-// ---------------------------------------------------------------------------------------------
-// small helpers
-// ---------------------------------------------------------------------------------------------
 typedef unsigned int u32;
 typedef unsigned long long u64;
 typedef unsigned short u16;
@@ -36,15 +37,13 @@ typedef unsigned short u16;
 #define NCONS (NW * 32)
 #define NTHREADS (NCONS + 32)
 #define KT_D (V_D / 16)
-#define KT_F (V_F / 16)
 #define JT_D (V_D / 16)
-#define JT_J (3 * V_D / 16)
-#define JT_N ((V_N + 15) / 16)
 #define FRAG_BYTES 512
 #define WN_MAX 4                      // widest NARROW placement (output tiles per CTA)
-#define LNV ((V_D + 127) / 128)       // float4 per lane to hold one row of width D
+#define WG NW                         // output tiles per WIDE group: one per consumer warp
+#define G4 (V_D / 4)                  // float4 groups per activation row
 
-// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter, cleared by the last CTA of every step
+// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter
 #define BAR_STATUS 0
 #define BAR_DONE 1
 #define BAR_ABORT 2
@@ -53,51 +52,39 @@ typedef unsigned short u16;
 // every wait gives up after WAIT_NS nanoseconds (a step takes well under a millisecond)
 #define WAIT_NS 500000000ull
 __device__ __forceinline__ u64 now_ns() { u64 t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
 __device__ __forceinline__ u32 smem_u32(const void* p) { return (u32)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ u32 pack_h2(float lo, float hi) {
-    u32 r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    return r;
-}
+__device__ __forceinline__ u32 pack_h2(float lo, float hi) { u32 r; asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo)); return r; }
 __device__ __forceinline__ float h_lo(u32 w) { float f; asm("{.reg .b16 l,h; mov.b32 {l,h}, %1; cvt.f32.f16 %0, l;}" : "=f"(f) : "r"(w)); return f; }
 __device__ __forceinline__ float h_hi(u32 w) { float f; asm("{.reg .b16 l,h; mov.b32 {l,h}, %1; cvt.f32.f16 %0, h;}" : "=f"(f) : "r"(w)); return f; }
 __device__ __forceinline__ float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;" : "=f"(f) : "h"(h)); return f; }
 __device__ __forceinline__ u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
-
-// fp32 pair -> fp16 head pair and fp16 remainder pair
-__device__ __forceinline__ void split2(float a, float b, u32& hi, u32& lo) {
-    hi = pack_h2(a, b);
-    lo = pack_h2(a - h_lo(hi), b - h_hi(hi));
-}
+__device__ __forceinline__ float fast_exp(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint4& a, u32 b0, u32 b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
-
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" :: "n"(NCONS) : "memory"); }
-
 __device__ __forceinline__ u32 ld_acquire(const u32* p) { u32 v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ u32 ld_relaxed(const u32* p) { u32 v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
-__device__ __forceinline__ void st_release(u32* p, u32 v) { asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(p), "r"(v) : "memory"); }
 __device__ __forceinline__ void red_add(float* p, float v) { asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory"); }
-
 __device__ __forceinline__ void mbar_init(u32 bar, u32 count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory"); }
 __device__ __forceinline__ void mbar_arrive(u32 bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory"); }
 __device__ __forceinline__ void mbar_expect(u32 bar, u32 bytes) { asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory"); }
 __device__ __forceinline__ bool mbar_try(u32 bar, u32 parity) {
     u32 ok;
-    asm volatile("{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    asm volatile("{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 __device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u32 bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" :: "r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// 16-byte asynchronous copies global (through L2 only) -> shared
+__device__ __forceinline__ void cp16(void* dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory"); }
+__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ uint4 lds128(const unsigned char* p) { return *reinterpret_cast<const uint4*>(p); }
 
 // orderable key of (value, index): larger value wins, then the lower index
 __device__ __forceinline__ u64 best_key(float v, u32 n) {
@@ -123,81 +110,90 @@ __device__ __forceinline__ u64 best_key(float v, u32 n) {
 #define PT_LOG_J0 10     // WIDE over the whole fold
 #define PT_LOG_NJ 11
 
-struct Place {
-    u32 base, layer;
-    int qkv_j0, qkv_nj, proj_j0, proj_nj, proj_k0, proj_nk, fc_j0, fc_nj, log_j0, log_nj;
-};
-
-__device__ __forceinline__ Place load_place(const int* __restrict__ PT, int cta) {
-    const int* p = PT + cta * PT_STRIDE;
-    Place P;
-    P.base = (u32)p[PT_BASE]; P.layer = (u32)p[PT_LAYER];
-    P.qkv_j0 = p[PT_QKV_J0]; P.qkv_nj = p[PT_QKV_NJ];
-    P.proj_j0 = p[PT_PROJ_J0]; P.proj_nj = p[PT_PROJ_NJ]; P.proj_k0 = p[PT_PROJ_K0]; P.proj_nk = p[PT_PROJ_NK];
-    P.fc_j0 = p[PT_FC_J0]; P.fc_nj = p[PT_FC_NJ];
-    P.log_j0 = p[PT_LOG_J0]; P.log_nj = p[PT_LOG_NJ];
-    return P;
-}
+// phases of a step, in order: layer l contributes QKV, ATT, PROJ, FC, P2; LOGITS closes the step
+#define PH_QKV 0
+#define PH_ATT 1
+#define PH_PROJ 2
+#define PH_FC 3
+#define PH_P2 4
+#define PH_LOGITS 5
+#define PH_PER_LAYER 5
 
 // A stream segment is a list of groups; a group is `rows` rows of `width` tiles, cut into chunks of
-// whole rows, at most V_CH tiles per chunk. NARROW segment: one group (rows = fold tiles, width = nj).
-// WIDE segment: one group per 8 output tiles (rows = fold tiles of the CTA, width <= 8).
-__device__ __forceinline__ int rows_per_chunk(int width) { return V_CH / width; }
-__device__ __forceinline__ u32 narrow_tiles(int nj, int kt) { return (u32)(nj * kt); }
-__device__ __forceinline__ u32 wide_tiles(int nj, int nk) { return (u32)(nj * nk); }
+// whole rows, at most V_CH tiles per chunk. NARROW segment: one group (rows = fold tiles, width =
+// output tiles). WIDE segment: one group per WG output tiles (rows = the CTA's fold tiles).
+struct Seg { int rows, nj; bool wide; };
+
+__device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
+    Seg s;
+    s.wide = (kind == PH_PROJ) | (kind == PH_P2) | (kind == PH_LOGITS);
+    s.rows = (kind == PH_PROJ) ? P[PT_PROJ_NK] : (kind == PH_P2) ? P[PT_FC_NJ] : KT_D;
+    s.nj = (kind == PH_QKV) ? P[PT_QKV_NJ] : (kind == PH_PROJ) ? P[PT_PROJ_NJ] : (kind == PH_FC) ? P[PT_FC_NJ]
+         : (kind == PH_P2) ? JT_D : (kind == PH_LOGITS) ? P[PT_LOG_NJ] : 0;
+    if (s.rows == 0) s.nj = 0;
+    return s;
+}
 
 // ---------------------------------------------------------------------------------------------
 // shared memory
 // ---------------------------------------------------------------------------------------------
 #define SM_RING 0
-#define SM_ACT (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)
-#define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)
-#define SM_RED (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)
-#define SM_PRM (SM_RED + NW * WN_MAX * V_NB * 128 * 4)
-#define PRM_TILE_HALVES (WN_MAX * 16)
-#define SM_PRM_BYTES ((3 * V_D + PRM_TILE_HALVES) * 2)
+#define SM_ACT (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)            // B operands of the current contraction
+#define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
+#define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // fp32 rows staged for LayerNorm
+#define SM_RED (SM_ZS + V_B * (V_D + 8) * 4)                      // NARROW partial sums, one tile per warp
+#define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
+#define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
 #define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
-#define SM_MISC_BYTES (NW * (V_E + 2) * 4 + V_B * 8 * NW + V_B * 4 + 64)
+#define MISC_ATT 0                                                // NW x (V_E + 2) floats
+#define MISC_BEST (((NW * (V_E + 2) * 4) + 7) & ~7)               // V_B x NW u64
+#define MISC_POS (MISC_BEST + V_B * NW * 8)                       // V_B ints
+#define MISC_STAT (MISC_POS + V_B * 4)                            // V_B x 2 floats
+#define SM_MISC_BYTES (MISC_STAT + V_B * 8 + 16)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
 #define SM_TOTAL (SM_BARS + 2 * V_NSLOT * 8)
 
 struct Ctx {
     unsigned char* smem;
     u32* bar;          // global counters
-    u32 gen;           // barrier generation of this CTA
+    u32 gen;           // barrier generation x CTAs
     u32 chunk;         // stream chunks consumed so far (same value in every consumer warp and the producer)
     int cta, ncta, tid, warp, lane;
     bool dead;         // a bounded wait expired somewhere: skip waits from now on
 #if V_TIMING
-    long long wait_clocks; u32 slow_waits;
+    int trn; bool tron; u64* trbuf;
 #endif
 };
+#if V_TIMING
+#define TRACE_EVENTS 56
+#define TRACE(id) do { if (c.tron && c.lane == 0 && c.trn < TRACE_EVENTS) c.trbuf[c.warp * TRACE_EVENTS + c.trn++] = ((u64)(id) << 48) | ((u64)clock64() & 0xFFFFFFFFFFFFull); } while (0)
+#else
+#define TRACE(id) do { } while (0)
+#endif
 
 __device__ __forceinline__ u32 full_bar(const Ctx& c, u32 slot) { return smem_u32(c.smem + SM_BARS) + slot * 8; }
 __device__ __forceinline__ u32 empty_bar(const Ctx& c, u32 slot) { return smem_u32(c.smem + SM_BARS) + (V_NSLOT + slot) * 8; }
 
-__device__ __noinline__ void give_up(Ctx& c, u32 where) {
-    c.dead = true;
-    atomicCAS(c.bar + BAR_STATUS, 0u, where | ((u32)c.cta << 16));
-    atomicExch(c.bar + BAR_ABORT, 1u);
+__device__ __noinline__ void give_up(u32* bar, u32 where, int cta) {
+    atomicCAS(bar + BAR_STATUS, 0u, where | ((u32)cta << 16));
+    atomicExch(bar + BAR_ABORT, 1u);
 }
 
-__device__ __forceinline__ void wait_mbar(Ctx& c, u32 bar, u32 parity, u32 where) {
-    if (c.dead) return;
-    if (mbar_try(bar, parity)) return;
-#if V_TIMING
-    c.slow_waits++;
-    const long long k0_ = clock64();
-    struct Acc_ { Ctx& c; long long k0; __device__ ~Acc_() { c.wait_clocks += clock64() - k0; } } acc_{c, k0_};
-#endif
+// slow path of a shared-memory barrier wait; returns false when the wait was abandoned
+__device__ __noinline__ bool mbar_wait_slow(u32* bar, u32 mbar, u32 parity, u32 where, int cta) {
     const u64 t0 = now_ns();
     u32 spins = 0;
-    while (!mbar_try(bar, parity)) {
+    while (!mbar_try(mbar, parity)) {
         if ((++spins & 63u) == 0) {
-            if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; return; }
-            if (now_ns() - t0 > WAIT_NS) { give_up(c, where); return; }
+            if (ld_relaxed(bar + BAR_ABORT)) return false;
+            if (now_ns() - t0 > WAIT_NS) { give_up(bar, where, cta); return false; }
         }
     }
+    return true;
+}
+__device__ __forceinline__ void wait_mbar(Ctx& c, u32 mbar, u32 parity, u32 where) {
+    if (c.dead || mbar_try(mbar, parity)) return;
+    if (!mbar_wait_slow(c.bar, mbar, parity, where, c.cta)) c.dead = true;
 }
 
 // Grid barrier for the consumer warps of all CTAs, in two halves so that loads that do not depend
@@ -212,196 +208,93 @@ __device__ __forceinline__ void phase_end(Ctx& c) {
     c.gen += (u32)c.ncta;
     if (c.tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" :: "l"(c.bar + BAR_COUNT) : "memory");
 }
-__device__ __forceinline__ void phase_wait(Ctx& c) {
-    if (c.tid == 0 && !c.dead) {
-        if ((int)(ld_acquire(c.bar + BAR_COUNT) - c.gen) < 0) {
-            const u64 t0 = now_ns();
-            u32 spins = 0;
-            while ((int)(ld_acquire(c.bar + BAR_COUNT) - c.gen) < 0) {
-                if ((++spins & 63u) == 0) {
-                    if (ld_relaxed(c.bar + BAR_ABORT)) break;
-                    if (now_ns() - t0 > WAIT_NS) { give_up(c, 0x100u); break; }
-                }
-            }
+__device__ __noinline__ bool grid_wait_slow(u32* bar, u32 gen, int cta) {
+    const u64 t0 = now_ns();
+    u32 spins = 0;
+    while ((int)(ld_acquire(bar + BAR_COUNT) - gen) < 0) {
+        if ((++spins & 63u) == 0) {
+            if (ld_relaxed(bar + BAR_ABORT)) return false;
+            if (now_ns() - t0 > WAIT_NS) { give_up(bar, 0x100u, cta); return false; }
         }
     }
+    return true;
+}
+__device__ __forceinline__ void phase_wait(Ctx& c) {
+    if (c.tid == 0 && !c.dead) grid_wait_slow(c.bar, c.gen, c.cta);
     cons_sync();
     if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
 }
 
-// 16-byte asynchronous copies global -> shared for the small per-phase parameters
-__device__ __forceinline__ void cp16(void* dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// Parameters of the next phase into shared memory: LayerNorm gain and shift, the bias added when a
-// combined vector is initialised (all three V_D halves), and the bias of this CTA's NARROW tiles.
-__device__ __noinline__ void fetch_params(Ctx& c, const u16* gw, const u16* gb, const u16* ib, const u16* tb, int tiles) {
-    u16* prm = reinterpret_cast<u16*>(c.smem + SM_PRM);
-    const int per = V_D / 8;                       // 16-byte pieces per vector
-    for (int i = c.tid; i < 3 * per; i += NCONS) {
-        const int v = i / per, q = i % per;
-        const u16* src = v == 0 ? gw : (v == 1 ? gb : ib);
-        if (src) cp16(prm + v * V_D + q * 8, src + q * 8);
-    }
-    if (tb && c.tid < tiles * 2) cp16(prm + 3 * V_D + c.tid * 8, tb + c.tid * 8);
-}
-
 // ---------------------------------------------------------------------------------------------
-// producer: walks this CTA's stream
+// producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void produce_group(Ctx& c, const unsigned char* src, int rows, int width) {
-    const int rpc = rows_per_chunk(width);
-    for (int r = 0; r < rows; r += rpc) {
-        const int nr = min(rpc, rows - r);
-        const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-        wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
-        if (c.dead) return;
-        const u32 bytes = (u32)(nr * width) * FRAG_BYTES;
-        mbar_expect(full_bar(c, slot), bytes);
-        bulk_g2s(smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src + (size_t)r * width * FRAG_BYTES, bytes, full_bar(c, slot));
-        c.chunk++;
-    }
-}
-
-__device__ __forceinline__ void produce_wide(Ctx& c, const unsigned char* src, int nj, int nk) {
-    for (int j = 0; j < nj; j += 8) {
-        const int w = min(8, nj - j);
-        produce_group(c, src, nk, w);
-        src += (size_t)nk * w * FRAG_BYTES;
-    }
-}
-
-__device__ __noinline__ void producer(Ctx& c, const Place& P, const unsigned char* __restrict__ WP) {
-    const unsigned char* base = WP + (size_t)P.base * FRAG_BYTES;
-    for (int l = 0; l < V_L; l++) {
-        const unsigned char* s = base + (size_t)l * P.layer * FRAG_BYTES;
-        if (P.qkv_nj) produce_group(c, s, KT_D, P.qkv_nj);
-        s += (size_t)narrow_tiles(P.qkv_nj, KT_D) * FRAG_BYTES;
-        produce_wide(c, s, P.proj_nj, P.proj_nk);
-        s += (size_t)wide_tiles(P.proj_nj, P.proj_nk) * FRAG_BYTES;
-        if (P.fc_nj) produce_group(c, s, KT_D, P.fc_nj);
-        s += (size_t)narrow_tiles(P.fc_nj, KT_D) * FRAG_BYTES;
-        produce_wide(c, s, JT_D, P.fc_nj);
-        if (c.dead) return;
-    }
-    produce_wide(c, base + (size_t)V_L * P.layer * FRAG_BYTES, P.log_nj, KT_D);
-}
-
-// ---------------------------------------------------------------------------------------------
-// consumer side of the stream
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ const unsigned char* chunk_acquire(Ctx& c) {
-    const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-    wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
-    return c.smem + SM_RING + slot * (V_CH * FRAG_BYTES);
-}
-__device__ __forceinline__ void chunk_release(Ctx& c) {
-    __syncwarp();
-    if (c.lane == 0) mbar_arrive(empty_bar(c, c.chunk % V_NSLOT));
-    c.chunk++;
-}
-
-__device__ __forceinline__ uint4 lds128(const unsigned char* p) { return *reinterpret_cast<const uint4*>(p); }
-
-// NARROW group: rows = fold tiles [0, kt), width = nj (<= WN_MAX). Warp w takes rows r = w (mod NW).
-// act: B operands, tile r at act + (r * V_NB + nb) * 512. Result: acc[jj][nb][4] partial per warp.
-__device__ __forceinline__ void narrow_gemm(Ctx& c, int kt, int nj, const unsigned char* act, float (&acc)[WN_MAX][V_NB][4]) {
-#pragma unroll
-    for (int jj = 0; jj < WN_MAX; jj++)
-#pragma unroll
-        for (int nb = 0; nb < V_NB; nb++)
-#pragma unroll
-            for (int i = 0; i < 4; i++) acc[jj][nb][i] = 0.f;
-    if (nj == 0) return;
-    const int rpc = rows_per_chunk(nj);
-    for (int r0 = 0; r0 < kt; r0 += rpc) {
-        const int nr = min(rpc, kt - r0);
-        const unsigned char* slot = chunk_acquire(c);
-        if (!c.dead) {
-            // first row of this chunk owned by this warp
-            int first = ((c.warp - (r0 % NW)) + NW) % NW;
-            for (int rr = first; rr < nr; rr += NW) {
-                const int r = r0 + rr;
-                uint4 b[V_NB];
-#pragma unroll
-                for (int nb = 0; nb < V_NB; nb++) b[nb] = lds128(act + ((size_t)(r * V_NB + nb) * 32 + c.lane) * 16);
-#pragma unroll
-                for (int jj = 0; jj < WN_MAX; jj++) {
-                    if (jj < nj) {
-                        const uint4 a = lds128(slot + ((size_t)(rr * nj + jj) * 32 + c.lane) * 16);
-#pragma unroll
-                        for (int nb = 0; nb < V_NB; nb++) {
-                            mma16816(acc[jj][nb], a, b[nb].x, b[nb].y);
-#if V_ACT_LO
-                            mma16816(acc[jj][nb], a, b[nb].z, b[nb].w);
-#endif
-                        }
-                    }
-                }
+__device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta) {
+    Ctx c;
+    c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta;
+    const unsigned char* src = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
+#pragma unroll 1
+    for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
+        const int kind = (ph == V_L * PH_PER_LAYER) ? PH_LOGITS : ph % PH_PER_LAYER;
+        if (kind == PH_ATT) continue;
+        const Seg s = seg_of(P, kind);
+#pragma unroll 1
+        for (int j = 0; j < s.nj; j += (s.wide ? WG : WN_MAX * 4)) {
+            const int width = s.wide ? min(WG, s.nj - j) : s.nj;
+            const int rpc = V_CH / width;
+#pragma unroll 1
+            for (int r = 0; r < s.rows; r += rpc) {
+                const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+                wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
+                if (c.dead) return;
+                const u32 bytes = (u32)(min(rpc, s.rows - r) * width) * FRAG_BYTES;
+                mbar_expect(full_bar(c, slot), bytes);
+                bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, bytes, full_bar(c, slot));
+                src += bytes;
+                c.chunk++;
             }
         }
-        chunk_release(c);
     }
 }
 
-// Sum the NARROW partials of all warps. Afterwards red[(jj * V_NB + nb) * 128 + lane * 4 + i] of
-// warp 0's block holds the complete sums for jj < nj.
-__device__ __forceinline__ void narrow_reduce(Ctx& c, int nj, float (&acc)[WN_MAX][V_NB][4]) {
-    float* red = reinterpret_cast<float*>(c.smem + SM_RED);
-#pragma unroll
-    for (int jj = 0; jj < WN_MAX; jj++)
-        if (jj < nj)
-#pragma unroll
-            for (int nb = 0; nb < V_NB; nb++)
-                *reinterpret_cast<float4*>(red + ((size_t)(c.warp * WN_MAX + jj) * V_NB + nb) * 128 + c.lane * 4) =
-                    make_float4(acc[jj][nb][0], acc[jj][nb][1], acc[jj][nb][2], acc[jj][nb][3]);
-    cons_sync();
-    const int total = nj * V_NB * 128;
-    for (int o = c.tid; o < total; o += NCONS) {
-        float s = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; w++) s += red[(size_t)w * WN_MAX * V_NB * 128 + o];
-        red[o] = s;      // slot (warp 0, o): only this thread reads the other warps' value at o
-    }
-    cons_sync();
-}
-
-// Output coordinates of element o of a reduced NARROW block: jj, nb, then the C fragment layout.
-__device__ __forceinline__ void narrow_coord(int o, int& jj, int& j_in, int& b) {
-    const int i = o & 3, ln = (o >> 2) & 31, nb = (o >> 7) % V_NB;
-    jj = (o >> 7) / V_NB;
-    j_in = (ln >> 2) + ((i & 2) ? 8 : 0);
-    b = nb * 8 + (ln & 3) * 2 + (i & 1);
-}
-
-// WIDE group: rows = fold tiles (nk), width = w (<= 8); warp w' < width owns output tile w'.
-// act tile for row r: act + ((r_act0 + r) * V_NB + nb) * 512.
-__device__ __forceinline__ void wide_gemm(Ctx& c, int nk, int width, const unsigned char* act, int r_act0, float (&acc)[V_NB][4]) {
+// ---------------------------------------------------------------------------------------------
+// one group of a contraction: `rows` x `width` tiles from the stream against the operand tiles at act.
+// NARROW: warp w works on output tile w % width and on every cnt-th fold tile (cnt = warps that share
+// the output tile); WIDE: warp w < width owns output tile w over all rows. In both cases the warp's
+// tiles are those with index w + k * stride in the group's row-major order. acc: this warp's sums.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wide, const unsigned char* act, float (&acc)[V_NB][4]) {
     float lo[V_NB][4];
 #pragma unroll
     for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
         for (int i = 0; i < 4; i++) { acc[nb][i] = 0.f; lo[nb][i] = 0.f; }
-    const int rpc = rows_per_chunk(width);
-    for (int r0 = 0; r0 < nk; r0 += rpc) {
-        const int nr = min(rpc, nk - r0);
-        const unsigned char* slot = chunk_acquire(c);
-        if (!c.dead && c.warp < width) {
-            for (int rr = 0; rr < nr; rr++) {
-                const uint4 a = lds128(slot + ((size_t)(rr * width + c.warp) * 32 + c.lane) * 16);
+    const int cnt = wide ? 1 : (NW - (c.warp % width) + width - 1) / width;    // rows advance by cnt
+    const int stride = cnt * width;
+    const bool active = wide ? (c.warp < width) : (c.warp / width < rows);
+    int f = active ? c.warp : 0x3fffffff;                                        // next tile of this warp
+    int row = wide ? 0 : c.warp / width;
+    const int rpc = V_CH / width, per = rpc * width, total = rows * width;
+#pragma unroll 1
+    for (int base = 0; base < total; base += per) {
+        const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+        wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+        const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES;
+        const int lim = c.dead ? 0 : min(base + per, total);
+#pragma unroll 1
+        for (; f < lim; f += stride, row += cnt) {
+            const uint4 a = lds128(tiles + ((size_t)f * 32 + c.lane) * 16);
 #pragma unroll
-                for (int nb = 0; nb < V_NB; nb++) {
-                    const uint4 b = lds128(act + ((size_t)((r_act0 + r0 + rr) * V_NB + nb) * 32 + c.lane) * 16);
-                    mma16816(acc[nb], a, b.x, b.y);
+            for (int nb = 0; nb < V_NB; nb++) {
+                const uint4 b = lds128(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * 16);
+                mma16816(acc[nb], a, b.x, b.y);
 #if V_ACT_LO
-                    mma16816(lo[nb], a, b.z, b.w);
+                mma16816(lo[nb], a, b.z, b.w);
 #endif
-                }
             }
         }
-        chunk_release(c);
+        __syncwarp();
+        if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+        c.chunk++;
     }
 #pragma unroll
     for (int nb = 0; nb < V_NB; nb++)
@@ -416,9 +309,8 @@ __device__ __forceinline__ void wide_gemm(Ctx& c, int nk, int width, const unsig
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void act_store4(unsigned char* act, int b, int k, float4 v) {
     // k is a multiple of 4: two words of the same register index
-    u32 h0, l0, h1, l1;
-    split2(v.x, v.y, h0, l0);
-    split2(v.z, v.w, h1, l1);
+    const u32 h0 = pack_h2(v.x, v.y), h1 = pack_h2(v.z, v.w);
+    const u32 l0 = pack_h2(v.x - h_lo(h0), v.y - h_hi(h0)), l1 = pack_h2(v.z - h_lo(h1), v.w - h_hi(h1));
     const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1;
     u32* base = reinterpret_cast<u32*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4) * 16);
     base[t * 4 + reg] = h0;
@@ -426,7 +318,6 @@ __device__ __forceinline__ void act_store4(unsigned char* act, int b, int k, flo
     base[(t + 1) * 4 + reg] = h1;
     base[(t + 1) * 4 + 2 + reg] = l1;
 }
-
 __device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, float v) {
     const u16 hi = f2h(v), lo = f2h(v - h2f(hi));
     const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1, half = kk & 1;
@@ -435,56 +326,86 @@ __device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, flo
     base[(2 + reg) * 2 + half] = lo;
 }
 
-// LayerNorm of the rows of z (global, fp32, [V_B][V_D]) into the operand tiles, one warp per row;
-// gain and shift come from the parameter block in shared memory. The same pass starts the vector
-// the following projection is combined into: init[b][d] += z[b][d] + bias[d], every CTA adding
-// its share of the elements (init was zeroed a phase earlier).
-__device__ __noinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act) {
+// Parameters of the next LayerNorm phase into shared memory: gain, shift, the bias added when the
+// following combined vector is started (each V_D halves), and the bias of this CTA's NARROW tiles.
+__device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* gb, const u16* ib, const u16* tb, int tiles) {
+    u16* prm = reinterpret_cast<u16*>(c.smem + SM_PRM);
+    const int per = V_D / 8;                       // 16-byte pieces per vector
+#pragma unroll 1
+    for (int i = c.tid; i < 3 * per; i += NCONS) {
+        const int v = i / per, q = i - v * per;
+        const u16* src = v == 0 ? gw : (v == 1 ? gb : ib);
+        if (src) cp16(prm + v * V_D + q * 8, src + q * 8);
+    }
+    if (tb && c.tid < tiles * 2) cp16(prm + 3 * V_D + c.tid * 8, tb + c.tid * 8);
+}
+
+// LayerNorm of the rows of z (global, fp32, [V_B][V_D]) into the operand tiles; gain and shift come
+// from the parameter block in shared memory. The rows are staged in shared memory (row stride
+// ZS_STRIDE floats, which spreads the rows over the banks), one warp per row computes mean and
+// variance (two passes), then every warp converts whole operand tiles: lane (b, t) of a tile
+// produces exactly its 16 bytes (head and remainder of the elements 2t, 2t+1, 2t+8, 2t+9 of row b),
+// one conflict-free 128-bit store. The same pass starts the vector the following projection is
+// combined into: init[b][d] += z[b][d] + bias[d], the fold tiles dealt over the CTAs (init was
+// zeroed a phase earlier).
+#define ZS_STRIDE (V_D + 8)
+__device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act) {
     const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
+    float* zs = reinterpret_cast<float*>(c.smem + SM_ZS);
+    float* stat = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_STAT);
+#pragma unroll 1
+    for (int i = c.tid; i < V_B * G4; i += NCONS) {
+        const int b = i / G4, g = i - b * G4;
+        cp16(zs + b * ZS_STRIDE + g * 4, z + (size_t)b * V_D + g * 4);
+    }
+    cp_wait();
+    cons_sync();
+    TRACE(40);
+#pragma unroll 1
     for (int b = c.warp; b < V_B; b += NW) {
-        float4 v[LNV];
+        const float4* row = reinterpret_cast<const float4*>(zs + b * ZS_STRIDE);
         float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < LNV; i++) {
-            const int d = (i * 32 + c.lane) * 4;
-            v[i] = (d < V_D) ? __ldcg(reinterpret_cast<const float4*>(z + (size_t)b * V_D + d)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        }
+#pragma unroll 2
+        for (int g = c.lane; g < G4; g += 32) { const float4 v = row[g]; s += (v.x + v.y) + (v.z + v.w); }
 #pragma unroll
         for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
         const float mean = s * (1.0f / V_D);
         float q = 0.f;
-#pragma unroll
-        for (int i = 0; i < LNV; i++) {
-            const int d = (i * 32 + c.lane) * 4;
-            if (d < V_D) {
-                const float a0 = v[i].x - mean, a1 = v[i].y - mean, a2 = v[i].z - mean, a3 = v[i].w - mean;
-                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
-            }
+#pragma unroll 2
+        for (int g = c.lane; g < G4; g += 32) {
+            const float4 v = row[g];
+            const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
+            q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
         }
 #pragma unroll
         for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
-#pragma unroll
-        for (int i = 0; i < LNV; i++) {
-            const int d = (i * 32 + c.lane) * 4;
-            if (d < V_D) {
-                const uint2 w = *reinterpret_cast<const uint2*>(prm + d);
-                const uint2 bb = *reinterpret_cast<const uint2*>(prm + V_D + d);
-                float4 o;
-                o.x = (v[i].x - mean) * rs * h_lo(w.x) + h_lo(bb.x);
-                o.y = (v[i].y - mean) * rs * h_hi(w.x) + h_hi(bb.x);
-                o.z = (v[i].z - mean) * rs * h_lo(w.y) + h_lo(bb.y);
-                o.w = (v[i].w - mean) * rs * h_hi(w.y) + h_hi(bb.y);
-                act_store4(act, b, d, o);
-                if (init && ((i * 32 + c.lane) % c.ncta) == c.cta) {
-                    const uint2 ib = *reinterpret_cast<const uint2*>(prm + 2 * V_D + d);
-                    float* dst = init + (size_t)b * V_D + d;
-                    red_add(dst, v[i].x + h_lo(ib.x)); red_add(dst + 1, v[i].y + h_hi(ib.x));
-                    red_add(dst + 2, v[i].z + h_lo(ib.y)); red_add(dst + 3, v[i].w + h_hi(ib.y));
-                }
+        if (c.lane == 0) { stat[2 * b] = mean; stat[2 * b + 1] = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS); }
+    }
+    cons_sync();
+    TRACE(41);
+    const int bl = c.lane >> 2, t = c.lane & 3;
+#pragma unroll 1
+    for (int it = c.warp; it < KT_D * V_NB; it += NW) {
+        const int kt = it / V_NB, nb = it - kt * V_NB, b = nb * 8 + bl, k = kt * 16 + 2 * t;
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (b < V_B) {
+            const float2 v0 = *reinterpret_cast<const float2*>(zs + b * ZS_STRIDE + k);
+            const float2 v1 = *reinterpret_cast<const float2*>(zs + b * ZS_STRIDE + k + 8);
+            const float mean = stat[2 * b], rs = stat[2 * b + 1];
+            const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
+            const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
+            const float o0 = (v0.x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0.y - mean) * rs * h_hi(w0) + h_hi(s0);
+            const float o2 = (v1.x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1.y - mean) * rs * h_hi(w1) + h_hi(s1);
+            out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
+            out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
+            if (init && (kt % c.ncta) == c.cta) {
+                const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
+                float* dst = init + (size_t)b * V_D + k;
+                red_add(dst, v0.x + h_lo(i0)); red_add(dst + 1, v0.y + h_hi(i0));
+                red_add(dst + 8, v1.x + h_lo(i1)); red_add(dst + 9, v1.y + h_hi(i1));
             }
         }
+        *reinterpret_cast<uint4*>(act + ((size_t)it * 32 + c.lane) * 16) = out;
     }
     cons_sync();
 }
@@ -493,20 +414,26 @@ __device__ __noinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, floa
 // per-chunk partial results (m, sum, unnormalised o[V_E]) of the attention phase, into operand
 // tiles 0..nk-1.
 #define PART_STRIDE (V_E + 2)
-__device__ __noinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act) {
+__device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act) {
     const int cols = nk * 16;
+#pragma unroll 1
     for (int i = c.tid; i < V_B * cols; i += NCONS) {
-        const int b = i / cols, kk = i % cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
+        const int b = i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
         const float* p = part + (size_t)((b * V_H + h) * V_NCH) * PART_STRIDE;
-        float m[V_NCH], M = -3.0e38f;
+        // all loads first (independent, one round trip), then the arithmetic
+        float mm[V_NCH], dd[V_NCH], oo[V_NCH], M = -3.0e38f;
 #pragma unroll
-        for (int ch = 0; ch < V_NCH; ch++) { m[ch] = __ldcg(p + ch * PART_STRIDE); M = fmaxf(M, m[ch]); }
+        for (int ch = 0; ch < V_NCH; ch++) {
+            mm[ch] = __ldcg(p + ch * PART_STRIDE); dd[ch] = __ldcg(p + ch * PART_STRIDE + 1); oo[ch] = __ldcg(p + ch * PART_STRIDE + 2 + e);
+        }
+#pragma unroll
+        for (int ch = 0; ch < V_NCH; ch++) M = fmaxf(M, mm[ch]);
         float num = 0.f, den = 0.f;
 #pragma unroll
         for (int ch = 0; ch < V_NCH; ch++) {
-            const float w = expf(m[ch] - M);
-            den += w * __ldcg(p + ch * PART_STRIDE + 1);
-            num += w * __ldcg(p + ch * PART_STRIDE + 2 + e);
+            const float w = fast_exp(mm[ch] - M);
+            den += w * dd[ch];
+            num += w * oo[ch];
         }
         act_store1(act, b, kk, num / den);
     }
@@ -514,61 +441,53 @@ __device__ __noinline__ void merge_to_act(Ctx& c, const float* __restrict__ part
 }
 
 // ---------------------------------------------------------------------------------------------
-// attention of one (sequence, head): online softmax over positions 0..n-1, K and V from the cache
+// attention of one (sequence, head) over positions [s_lo, n): online softmax, K and V from the cache;
+// result: (running max, sum, unnormalised o[V_E]) at out. 8 lanes per position (16 B each of the
+// 128 B row), 4 positions per warp per round.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void dot8(const uint4& kv, const float (&q)[8], float& s) {
-    s = q[0] * h_lo(kv.x) + q[1] * h_hi(kv.x) + q[2] * h_lo(kv.y) + q[3] * h_hi(kv.y) +
-        q[4] * h_lo(kv.z) + q[5] * h_hi(kv.z) + q[6] * h_lo(kv.w) + q[7] * h_hi(kv.w);
-}
-
 #define ATT_UNROLL 4
-// positions [s_lo, s_hi) of one (sequence, head); result: (running max, sum, unnormalised o[V_E]) at out
-__device__ __noinline__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
-                               float* __restrict__ out, int b, int h, int l, int s_lo, int n) {
-    // 8 lanes per position (16 B each of the 128 B row), 4 positions per warp per round
+__device__ __forceinline__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
+                                               float* __restrict__ out, int b, int h, int l, int s_lo, int n) {
     const int li = c.lane & 7, grp = c.warp * 4 + (c.lane >> 3);
     const int NG = NW * 4;
     float q[8];
     {
         const float* qp = qbuf + (size_t)b * V_D + h * V_E + li * 8;
         const float4 q0 = __ldcg(reinterpret_cast<const float4*>(qp)), q1 = __ldcg(reinterpret_cast<const float4*>(qp + 4));
-        q[0] = q0.x; q[1] = q0.y; q[2] = q0.z; q[3] = q0.w; q[4] = q1.x; q[5] = q1.y; q[6] = q1.z; q[7] = q1.w;
+        const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
+        q[0] = q0.x * sc; q[1] = q0.y * sc; q[2] = q0.z * sc; q[3] = q0.w * sc; q[4] = q1.x * sc; q[5] = q1.y * sc; q[6] = q1.z * sc; q[7] = q1.w * sc;
     }
     const size_t row0 = ((size_t)(b * V_L + l) * V_TMAX) * V_D + (size_t)h * V_E + li * 8;
     float m = -3.0e38f, den = 0.f, acc[8];
 #pragma unroll
     for (int i = 0; i < 8; i++) acc[i] = 0.f;
     // the trip count is the same for every lane of the warp (the shuffles below need all 32 lanes)
+#pragma unroll 1
     for (int base = s_lo; base < n; base += NG * ATT_UNROLL) {
-        const int s0 = base + grp;
         uint4 kk[ATT_UNROLL], vv[ATT_UNROLL];
 #pragma unroll
         for (int u = 0; u < ATT_UNROLL; u++) {
-            const int s = s0 + u * NG;
-            if (s < n) {
-                kk[u] = __ldcg(reinterpret_cast<const uint4*>(keys + row0 + (size_t)s * V_D));
-                vv[u] = __ldcg(reinterpret_cast<const uint4*>(vals + row0 + (size_t)s * V_D));
-            } else {
-                kk[u] = make_uint4(0, 0, 0, 0); vv[u] = make_uint4(0, 0, 0, 0);
-            }
+            const int s = min(base + grp + u * NG, n - 1);
+            kk[u] = __ldcg(reinterpret_cast<const uint4*>(keys + row0 + (size_t)s * V_D));
+            vv[u] = __ldcg(reinterpret_cast<const uint4*>(vals + row0 + (size_t)s * V_D));
         }
 #pragma unroll
         for (int u = 0; u < ATT_UNROLL; u++) {
-            const int s = s0 + u * NG;
-            float sc;
-            dot8(kk[u], q, sc);
+            const uint4 k4 = kk[u], v4 = vv[u];
+            float sc = q[0] * h_lo(k4.x) + q[1] * h_hi(k4.x) + q[2] * h_lo(k4.y) + q[3] * h_hi(k4.y) +
+                       q[4] * h_lo(k4.z) + q[5] * h_hi(k4.z) + q[6] * h_lo(k4.w) + q[7] * h_hi(k4.w);
             sc += __shfl_xor_sync(0xffffffffu, sc, 1);
             sc += __shfl_xor_sync(0xffffffffu, sc, 2);
             sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-            if (s < n) {
-                sc = sc / V_SCALE;
+            if (base + grp + u * NG < n) {
+                if (!V_SCALE_IS_POW2) sc = sc / V_SCALE;
                 const float mn = fmaxf(m, sc);
-                const float corr = expf(m - mn), p = expf(sc - mn);
+                const float corr = fast_exp(m - mn), p = fast_exp(sc - mn);
                 den = den * corr + p;
-                acc[0] = acc[0] * corr + p * h_lo(vv[u].x); acc[1] = acc[1] * corr + p * h_hi(vv[u].x);
-                acc[2] = acc[2] * corr + p * h_lo(vv[u].y); acc[3] = acc[3] * corr + p * h_hi(vv[u].y);
-                acc[4] = acc[4] * corr + p * h_lo(vv[u].z); acc[5] = acc[5] * corr + p * h_hi(vv[u].z);
-                acc[6] = acc[6] * corr + p * h_lo(vv[u].w); acc[7] = acc[7] * corr + p * h_hi(vv[u].w);
+                acc[0] = acc[0] * corr + p * h_lo(v4.x); acc[1] = acc[1] * corr + p * h_hi(v4.x);
+                acc[2] = acc[2] * corr + p * h_lo(v4.y); acc[3] = acc[3] * corr + p * h_hi(v4.y);
+                acc[4] = acc[4] * corr + p * h_lo(v4.z); acc[5] = acc[5] * corr + p * h_hi(v4.z);
+                acc[6] = acc[6] * corr + p * h_lo(v4.w); acc[7] = acc[7] * corr + p * h_hi(v4.w);
                 m = mn;
             }
         }
@@ -578,17 +497,14 @@ __device__ __noinline__ void attention_item(Ctx& c, const u16* __restrict__ keys
     for (int x = 8; x <= 16; x <<= 1) {
         const float m2 = __shfl_xor_sync(0xffffffffu, m, x), d2 = __shfl_xor_sync(0xffffffffu, den, x);
         const float mn = fmaxf(m, m2);
-        const float c1 = expf(m - mn), c2 = expf(m2 - mn);
+        const float c1 = fast_exp(m - mn), c2 = fast_exp(m2 - mn);
         den = den * c1 + d2 * c2;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const float a2 = __shfl_xor_sync(0xffffffffu, acc[i], x);
-            acc[i] = acc[i] * c1 + a2 * c2;
-        }
+        for (int i = 0; i < 8; i++) acc[i] = acc[i] * c1 + __shfl_xor_sync(0xffffffffu, acc[i], x) * c2;
         m = mn;
     }
     // merge the warps through shared memory: per warp (m, den, acc[V_E])
-    float* ms = reinterpret_cast<float*>(c.smem + SM_MISC);
+    float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
     if (c.lane < 8) {
         float* w = ms + c.warp * (V_E + 2);
         if (c.lane == 0) { w[0] = m; w[1] = den; }
@@ -598,12 +514,12 @@ __device__ __noinline__ void attention_item(Ctx& c, const u16* __restrict__ keys
     cons_sync();
     if (c.tid < V_E) {
         float M = -3.0e38f;
-#pragma unroll
+#pragma unroll 1
         for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
         float num = 0.f, dd = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int w = 0; w < NW; w++) {
-            const float sc = expf(ms[w * (V_E + 2)] - M);
+            const float sc = fast_exp(ms[w * (V_E + 2)] - M);
             dd += ms[w * (V_E + 2) + 1] * sc;
             num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
         }
@@ -625,25 +541,22 @@ struct Args {
     const unsigned char* WP; const int* PT;
 };
 
-__device__ __forceinline__ int pos_of(const Args& a, int b) { return a.t[b * V_TSTRIDE]; }
-
 #if V_TIMING
-// thread 0 of CTA V_TIMING-1 sums clock64 deltas per site in shared memory (cheap) and adds them to TS at the end
+// thread 0 of CTA V_TIMING-1 sums clock64 deltas per site in shared memory and adds them to TS at the end
 #define TICK(k) do { if (c.cta == V_TIMING - 1 && c.tid == 0) { const long long now_ = clock64(); ts_[k] += now_ - tlast_; tlast_ = now_; } } while (0)
 #else
 #define TICK(k) do { } while (0)
 #endif
 
-__device__ void step_body(const Args& a) {
+__device__ __forceinline__ void step_body(const Args& a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Ctx c;
     c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false;
-#if V_TIMING
-    c.wait_clocks = 0; c.slow_waits = 0;
-#endif
     c.cta = blockIdx.x; c.ncta = gridDim.x; c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
 #if V_TIMING
+    __shared__ u64 trace_[(V_NW + 1) * TRACE_EVENTS];
     __shared__ long long ts_[16];
+    c.trn = 0; c.tron = false; c.trbuf = trace_;
     if (threadIdx.x == 0) for (int i = 0; i < 16; i++) ts_[i] = 0;
     long long tlast_ = clock64();
     const u64 t_begin_ = now_ns();
@@ -651,11 +564,12 @@ __device__ void step_body(const Args& a) {
 
     // inputs outside their ranges would index outside the caches and tables: refuse the step
     // (every CTA sees the same values and takes the same branch)
-    int* s_pos = reinterpret_cast<int*>(smem + SM_MISC + NW * (V_E + 2) * 4 + V_B * 8 * NW + 16);
+    int* s_pos = reinterpret_cast<int*>(smem + SM_MISC + MISC_POS);
     {
         bool bad = false;
+#pragma unroll 1
         for (int b = 0; b < V_B; b++) {
-            const int tb = pos_of(a, b), xb = a.x[b];
+            const int tb = a.t[b * V_TSTRIDE], xb = a.x[b];
             bad |= (tb < 0) | (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
             if (c.tid == 0) s_pos[b] = tb;
         }
@@ -664,24 +578,18 @@ __device__ void step_body(const Args& a) {
             return;
         }
     }
-
     if (c.tid == 0) {
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // operand tiles start as zero: rows of a batch tile beyond V_B stay zero for the whole launch
-    for (int i = c.tid; i < (SM_RED - SM_ACT) / 16; i += NTHREADS)
-        reinterpret_cast<uint4*>(smem + SM_ACT)[i] = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+    for (int i = c.tid; i < (SM_ZS - SM_ACT) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_ACT)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
-    const Place P = load_place(a.PT, c.cta);
+    const int* P = a.PT + c.cta * PT_STRIDE;
     if (c.warp == NW) {
-        if (c.lane == 0) {
-            producer(c, P, a.WP);
-#if V_TIMING
-            if (c.cta == V_TIMING - 1) { a.TS[18] += (u64)c.wait_clocks; a.TS[19] += c.slow_waits; a.TS[20] += c.chunk; }
-#endif
-        }
+        if (c.lane == 0) producer(smem, a.bar, P, a.WP, c.cta);
         return;
     }
 
@@ -693,175 +601,140 @@ __device__ void step_body(const Args& a) {
     float* Z = a.S + V_OFF_Z;
     float* qbuf = a.S + V_OFF_Q;
     float* part = a.S + V_OFF_PART;
+    float* logit = a.S + V_OFF_LOGIT;
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
+    u64 best[V_NB][2];
+#pragma unroll
+    for (int nb = 0; nb < V_NB; nb++) { best[nb][0] = 0; best[nb][1] = 0; }
 
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
+#pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
-        const int b = i / V_D, d = i % V_D;
+        const int b = i / V_D, d = i - b * V_D;
         Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)s_pos[b] * V_D + d]);
         Z[ZS + i] = 0.f;
     }
     TICK(0);
     phase_end(c);
-    fetch_params(c, a.ln1w, a.ln1b, a.ob, a.qkvb + P.qkv_j0 * 16, P.qkv_nj);
+    fetch_params(c, a.ln1w, a.ln1b, a.ob, a.qkvb + P[PT_QKV_J0] * 16, P[PT_QKV_NJ]);
     phase_wait(c);
     TICK(1);
 
-    for (int l = 0; l < V_L; l++) {
-        float* zin = Z + (size_t)((2 * l) % 3) * ZS;
+#pragma unroll 1
+    for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
+        const int l = ph / PH_PER_LAYER;
+        const int kind = (l == V_L) ? PH_LOGITS : ph - l * PH_PER_LAYER;
+        float* zin = Z + (size_t)((2 * l) % 3) * ZS;          // layer input (for LOGITS: the final state)
         float* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
         float* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
+#if V_TIMING
+        c.tron = (c.cta == V_TIMING - 1) && (l == V_L / 2);
+#endif
+        TRACE(1 + kind);
 
-        // ---- LN1 + QKV (+bias): q to scratch, K and V rounded to fp16 into the cache at t.
-        //      The same pass starts z1 = z + ob (the projection adds into it two phases later)
-        //      and clears z2, which nobody reads any more.
-        for (int i = gtid; i < V_B * V_D; i += gthreads) z2[i] = 0.f;
-        cp_wait();
-        cons_sync();
-        ln_to_act(c, zin, z1, act);
-        {
-            float acc[WN_MAX][V_NB][4];
-            narrow_gemm(c, KT_D, P.qkv_nj, act, acc);
-            narrow_reduce(c, P.qkv_nj, acc);
-            const int total = P.qkv_nj * V_NB * 128;
-            for (int o = c.tid; o < total; o += NCONS) {
-                int jj, j_in, b;
-                narrow_coord(o, jj, j_in, b);
-                if (b < V_B) {
-                    const int j = (P.qkv_j0 + jj) * 16 + j_in;
-                    const float v = red[o] + h2f(prm[3 * V_D + jj * 16 + j_in]);
-                    if (j < V_D) qbuf[(size_t)b * V_D + j] = v;
-                    else {
-                        const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (j % V_D);
-                        if (j < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
+        // ---- prologue: what the phase reads from other CTAs, into shared memory
+        if (kind == PH_QKV || kind == PH_FC || kind == PH_LOGITS) {
+            // LN1 (starts z1 = z + ob, clears z2) | LN2 (starts z2 = z1 + pb, clears zin for the next layer) | LNf
+            float* clr = (kind == PH_QKV) ? z2 : (kind == PH_FC) ? zin : (float*)0;
+            if (clr) {
+#pragma unroll 1
+                for (int i = gtid; i < V_B * V_D; i += gthreads) clr[i] = 0.f;
+            }
+            ln_to_act(c, (kind == PH_FC) ? z1 : zin, (kind == PH_QKV) ? z1 : (kind == PH_FC) ? z2 : (float*)0, act);
+        } else if (kind == PH_ATT) {
+            // one (sequence, head, chunk of positions) at a time, partial results to scratch
+#pragma unroll 1
+            for (int it = c.cta; it < V_B * V_H * V_NCH; it += c.ncta) {
+                const int ch = it % V_NCH, bh = it / V_NCH, b = bh / V_H, h = bh - b * V_H;
+                const int n = s_pos[b] + 1, cs = (n + V_NCH - 1) / V_NCH;
+                attention_item(c, a.keys, a.vals, qbuf, part + (size_t)it * PART_STRIDE, b, h, l, ch * cs, min(n, (ch + 1) * cs));
+            }
+        } else if (kind == PH_PROJ) {
+            if (P[PT_PROJ_NJ]) merge_to_act(c, part, P[PT_PROJ_K0], P[PT_PROJ_NK], act);
+        }
+        TRACE(10 + kind);
+
+        // ---- the contraction, group by group, each followed by its epilogue
+        const Seg sg = seg_of(P, kind);
+#pragma unroll 1
+        for (int j = 0; j < sg.nj; j += (sg.wide ? WG : WN_MAX * 4)) {
+            const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
+            float acc[V_NB][4];
+            gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
+            if (!sg.wide) {
+                // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
+#pragma unroll
+                for (int nb = 0; nb < V_NB; nb++)
+                    *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+                cons_sync();
+#pragma unroll 1
+                for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
+                    const int jj = o / (V_NB * 128), r = o - jj * (V_NB * 128);
+                    float v = 0.f;
+#pragma unroll 1
+                    for (int w = jj; w < NW; w += width) v += red[(size_t)w * V_NB * 128 + r];
+                    const int i = r & 3, ln = (r >> 2) & 31, nb = r >> 7;
+                    const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (ln & 3) * 2 + (i & 1);
+                    v += h2f(prm[3 * V_D + jj * 16 + j_in]);
+                    if (kind == PH_QKV) {
+                        // q to scratch, K and V rounded to fp16 into the cache at t
+                        if (b < V_B) {
+                            const int jx = (P[PT_QKV_J0] + jj) * 16 + j_in;
+                            if (jx < V_D) qbuf[(size_t)b * V_D + jx] = v;
+                            else {
+                                const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
+                                if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
+                            }
+                        }
+                    } else {
+                        // g = gelu(u) -> operand tiles of the MLP projection: fold index = jj*16 + j_in
+                        const float g = (b < V_B) ? V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))) : 0.f;
+                        act_store1(gact, b, jj * 16 + j_in, g);
                     }
                 }
-            }
-        }
-        TICK(2);
-        phase_end(c);
-        phase_wait(c);
-        TICK(3);
-
-        // ---- attention: one (sequence, head, chunk of positions) at a time, partial results to scratch
-        for (int it = c.cta; it < V_B * V_H * V_NCH; it += c.ncta) {
-            const int ch = it % V_NCH, bh = it / V_NCH, b = bh / V_H, h = bh % V_H;
-            const int n = s_pos[b] + 1, cs = (n + V_NCH - 1) / V_NCH;
-            attention_item(c, a.keys, a.vals, qbuf, part + (size_t)it * PART_STRIDE, b, h, l, ch * cs, min(n, (ch + 1) * cs));
-        }
-        TICK(4);
-        phase_end(c);
-        phase_wait(c);
-        TICK(5);
-
-        // ---- attn-proj: z1 += o . ow, partial sums over this CTA's fold range
-        if (P.proj_nj) {
-            merge_to_act(c, part, P.proj_k0, P.proj_nk, act);
-            float acc[V_NB][4];
-            wide_gemm(c, P.proj_nk, P.proj_nj, act, 0, acc);
-            if (c.warp < P.proj_nj) {
-                const int jt = P.proj_j0 + c.warp;
+                cons_sync();
+            } else if (c.warp < width) {
+                const int jt = ((kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0) + j + c.warp;
+                float* zt = (kind == PH_PROJ) ? z1 : z2;
 #pragma unroll
                 for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
                     for (int i = 0; i < 4; i++) {
-                        const int j = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                        if (b < V_B) red_add(z1 + (size_t)b * V_D + j, acc[nb][i]);
+                        const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
+                        if (kind != PH_LOGITS) {
+                            if (b < V_B) red_add(zt + (size_t)b * V_D + jx, acc[nb][i]);
+                        } else if (b < V_B && jx < V_N) {
+                            logit[(size_t)b * V_N + jx] = acc[nb][i];
+                            const u64 k = best_key(acc[nb][i], (u32)jx);
+                            if (k > best[nb][i & 1]) best[nb][i & 1] = k;
+                        }
                     }
             }
         }
-        TICK(6);
-        phase_end(c);
-        fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
-                     a.fcb + (size_t)l * V_F + P.fc_j0 * 16, P.fc_nj);
-        phase_wait(c);
-        TICK(7);
+        TRACE(20 + kind);
+        if (kind == PH_FC || kind == PH_LOGITS) continue;          // FC feeds P2 inside the CTA; LOGITS ends below
 
-        // ---- LN2 + FC + GELU on this CTA's slice of f, then its partial of the MLP projection.
-        //      The LN pass starts z2 = z1 + pb; zin is free from here on and is cleared for the
-        //      next layer's projection.
-        for (int i = gtid; i < V_B * V_D; i += gthreads) zin[i] = 0.f;
-        cp_wait();
-        cons_sync();
-        ln_to_act(c, z1, z2, act);
-        TICK(12);
-        {
-            float acc[WN_MAX][V_NB][4];
-            narrow_gemm(c, KT_D, P.fc_nj, act, acc);
-            TICK(13);
-            narrow_reduce(c, P.fc_nj, acc);
-            // g = gelu(u + fcb) -> operand tiles of the projection: fold index = jj*16 + j_in
-            const int total = P.fc_nj * V_NB * 128;
-            for (int o = c.tid; o < total; o += NCONS) {
-                int jj, j_in, b;
-                narrow_coord(o, jj, j_in, b);
-                float g = 0.f;
-                if (b < V_B) {
-                    const float u = red[o] + h2f(prm[3 * V_D + jj * 16 + j_in]);
-                    g = V_GELU_A * u * (1.0f + tanhf(V_GELU_B * (u + V_GELU_C * u * u * u)));
-                }
-                act_store1(gact, b, jj * 16 + j_in, g);
-            }
-            cons_sync();
-            TICK(14);
-        }
-        for (int jg = 0; jg < JT_D; jg += 8) {
-            const int width = min(8, JT_D - jg);
-            float acc[V_NB][4];
-            wide_gemm(c, P.fc_nj, width, gact, 0, acc);
-            if (c.warp < width && P.fc_nj) {
-                const int jt = jg + c.warp;
-#pragma unroll
-                for (int nb = 0; nb < V_NB; nb++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int j = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                        if (b < V_B) red_add(z2 + (size_t)b * V_D + j, acc[nb][i]);
-                    }
-            }
-        }
-        TICK(8);
+        // ---- grid barrier; the next LayerNorm's parameters are fetched while waiting
+        TICK(2 + 2 * kind - (kind == PH_P2 ? 2 : 0));
         phase_end(c);
-        if (l + 1 < V_L)
-            fetch_params(c, a.ln1w + (size_t)(l + 1) * V_D, a.ln1b + (size_t)(l + 1) * V_D, a.ob + (size_t)(l + 1) * V_D,
-                         a.qkvb + (size_t)(l + 1) * 3 * V_D + P.qkv_j0 * 16, P.qkv_nj);
-        else
-            fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
+        if (kind == PH_PROJ)
+            fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
+                         a.fcb + (size_t)l * V_F + P[PT_FC_J0] * 16, P[PT_FC_NJ]);
+        else if (kind == PH_P2) {
+            if (l + 1 < V_L)
+                fetch_params(c, a.ln1w + (size_t)(l + 1) * V_D, a.ln1b + (size_t)(l + 1) * V_D, a.ob + (size_t)(l + 1) * V_D,
+                             a.qkvb + (size_t)(l + 1) * 3 * V_D + P[PT_QKV_J0] * 16, P[PT_QKV_NJ]);
+            else
+                fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
+        }
+        TRACE(30 + kind);
         phase_wait(c);
-        TICK(9);
+        TICK(3 + 2 * kind - (kind == PH_P2 ? 2 : 0));
     }
 
-    // ---- LN_f + logits + argmax
-    float* zf = Z + (size_t)((2 * V_L) % 3) * ZS;
-    cp_wait();
-    cons_sync();
-    ln_to_act(c, zf, (float*)0, act);
-    u64 best[V_NB][2];
-#pragma unroll
-    for (int nb = 0; nb < V_NB; nb++) { best[nb][0] = 0; best[nb][1] = 0; }
-    float* logit = a.S + V_OFF_LOGIT;
-    for (int jg = 0; jg < P.log_nj; jg += 8) {
-        const int width = min(8, P.log_nj - jg);
-        float acc[V_NB][4];
-        wide_gemm(c, KT_D, width, act, 0, acc);
-        if (c.warp < width) {
-            const int jt = P.log_j0 + jg + c.warp;
-#pragma unroll
-            for (int nb = 0; nb < V_NB; nb++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const int n = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                    if (b < V_B && n < V_N) {
-                        logit[(size_t)b * V_N + n] = acc[nb][i];
-                        const u64 k = best_key(acc[nb][i], (u32)n);
-                        if (k > best[nb][i & 1]) best[nb][i & 1] = k;
-                    }
-                }
-        }
-    }
-    // per batch row: max over the lanes that hold the same row (lanes with equal lane&3), then over warps
-    u64* wbest = reinterpret_cast<u64*>(smem + ((SM_MISC + NW * (V_E + 2) * 4 + 7) & ~7));
+    // ---- argmax: per batch row the max over the lanes that hold it (equal lane&3), the warps, the CTAs
+    u64* wbest = reinterpret_cast<u64*>(smem + SM_MISC + MISC_BEST);
 #pragma unroll
     for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
@@ -879,6 +752,7 @@ __device__ void step_body(const Args& a) {
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     if (c.tid < V_B) {
         u64 k = 0;
+#pragma unroll 1
         for (int w = 0; w < NW; w++) if (wbest[c.tid * NW + w] > k) k = wbest[c.tid * NW + w];
         if (k) atomicMax(gbest + c.tid, k);
     }
@@ -890,6 +764,7 @@ __device__ void step_body(const Args& a) {
         const u32 old = atomicAdd(a.bar + BAR_DONE, 1u);
         if (old == (u32)c.ncta - 1) {
             __threadfence();
+#pragma unroll 1
             for (int b = 0; b < V_B; b++) {
                 const u64 k = atomicExch(gbest + b, 0ull);
                 const u32 n = 0xFFFFFFFFu - (u32)(k & 0xFFFFFFFFull);
@@ -899,6 +774,7 @@ __device__ void step_body(const Args& a) {
 #endif
             }
 #if V_FEEDBACK
+#pragma unroll 1
             for (int b = 0; b < (V_TSTRIDE ? V_B : 1); b++) a.t_out[b] += V_TSTEP;
 #endif
             atomicExch(a.bar + BAR_COUNT, 0u);     // every CTA is past its last barrier
@@ -907,11 +783,11 @@ __device__ void step_body(const Args& a) {
     }
     TICK(11);
 #if V_TIMING
+    if (c.cta == V_TIMING - 1 && c.lane == 0)
+        for (int i = 0; i < TRACE_EVENTS; i++) a.TS[64 + c.warp * TRACE_EVENTS + i] = i < c.trn ? trace_[c.warp * TRACE_EVENTS + i] : 0ull;
     if (c.cta == V_TIMING - 1 && c.tid == 0) {
         for (int i = 0; i < 16; i++) a.TS[i] += (u64)ts_[i];
-        a.TS[16] += (u64)c.wait_clocks; a.TS[17] += c.slow_waits;
         a.TS[21] += now_ns() - t_begin_;        // nanoseconds of this CTA's launch, to convert clocks
-        a.TS[22] += (u64)(clock64() - (tlast_ - 0)) * 0 + 1;   // launches
     }
 #endif
 }
@@ -927,10 +803,10 @@ struct PackArgs {
 // A(m = output j, k) of the five contractions
 __device__ __forceinline__ u16 w_elem(const PackArgs& a, int kind, int l, int j, int k) {
     switch (kind) {
-        case 0: return a.qkvw[((size_t)l * V_D + k) * (3 * V_D) + j];
-        case 1: return a.ow[((size_t)l * V_D + k) * V_D + j];
-        case 2: return a.fcw[((size_t)l * V_D + k) * V_F + j];
-        case 3: return a.pw[((size_t)l * V_F + k) * V_D + j];
+        case PH_QKV: return a.qkvw[((size_t)l * V_D + k) * (3 * V_D) + j];
+        case PH_PROJ: return a.ow[((size_t)l * V_D + k) * V_D + j];
+        case PH_FC: return a.fcw[((size_t)l * V_D + k) * V_F + j];
+        case PH_P2: return a.pw[((size_t)l * V_F + k) * V_D + j];
         default: return j < V_N ? a.wte[(size_t)j * V_D + k] : (u16)0;
     }
 }
@@ -946,38 +822,41 @@ __device__ __forceinline__ void pack_tile(const PackArgs& a, unsigned char* dst,
     reinterpret_cast<uint4*>(dst)[lane] = v;
 }
 
-// NARROW group: tile index = kt * nj + jj
-__device__ void pack_narrow(const PackArgs& a, unsigned char* dst, int kind, int l, int j0, int nj, int kt_n, int wid, int nwarp, int lane) {
-    const int n = nj * kt_n;
-    for (int i = wid; i < n; i += nwarp) pack_tile(a, dst + (size_t)i * FRAG_BYTES, kind, l, j0 + i % nj, i / nj, lane);
-}
-// WIDE segment: groups of 8 output tiles; inside a group tile index = k_rel * width + w
-__device__ void pack_wide(const PackArgs& a, unsigned char* dst, int kind, int l, int j0, int nj, int k0, int nk, int wid, int nwarp, int lane) {
-    const int n = nj * nk;
+// one segment: NARROW tile index = k * nj + jj; WIDE groups of WG output tiles, inside a group
+// tile index = k_rel * width + w. Returns the number of tiles.
+__device__ int pack_segment(const PackArgs& a, unsigned char* dst, const int* __restrict__ P, int kind, int l, int wid, int nwarp, int lane) {
+    const Seg s = seg_of(P, kind);
+    const int n = s.rows * s.nj;
+    const int j0 = (kind == PH_QKV) ? P[PT_QKV_J0] : (kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_FC) ? P[PT_FC_J0]
+                 : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0;
+    const int k0 = (kind == PH_PROJ) ? P[PT_PROJ_K0] : (kind == PH_P2) ? P[PT_FC_J0] : 0;
     for (int i = wid; i < n; i += nwarp) {
-        const int grp = i / (8 * nk);                      // full groups before this tile hold 8*nk tiles
-        const int width = min(8, nj - grp * 8);
-        const int r = i - grp * 8 * nk;
-        pack_tile(a, dst + (size_t)i * FRAG_BYTES, kind, l, j0 + grp * 8 + r % width, k0 + r / width, lane);
+        int jt, kt;
+        if (!s.wide) { jt = j0 + i % s.nj; kt = i / s.nj; }
+        else {
+            const int grp = i / (WG * s.rows);                 // full groups before this tile hold WG*rows tiles
+            const int width = min(WG, s.nj - grp * WG);
+            const int r = i - grp * WG * s.rows;
+            jt = j0 + grp * WG + r % width; kt = k0 + r / width;
+        }
+        pack_tile(a, dst + (size_t)i * FRAG_BYTES, kind, l, jt, kt, lane);
     }
+    return n;
 }
 
 // grid: (V_L + 1) blocks per CTA of the step kernel: blockIdx.x = cta * (V_L + 1) + l; l == V_L packs the logits
 __device__ void pack_body(const PackArgs& a) {
     const int cta = blockIdx.x / (V_L + 1), l = blockIdx.x % (V_L + 1);
-    const Place P = load_place(a.PT, cta);
+    const int* P = a.PT + cta * PT_STRIDE;
     const int wid = threadIdx.x >> 5, nwarp = blockDim.x >> 5, lane = threadIdx.x & 31;
-    unsigned char* base = a.WP + (size_t)P.base * FRAG_BYTES;
+    unsigned char* base = a.WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
     if (l == V_L) {
-        pack_wide(a, base + (size_t)V_L * P.layer * FRAG_BYTES, 4, 0, P.log_j0, P.log_nj, 0, KT_D, wid, nwarp, lane);
+        pack_segment(a, base + (size_t)V_L * (u32)P[PT_LAYER] * FRAG_BYTES, P, PH_LOGITS, 0, wid, nwarp, lane);
         return;
     }
-    unsigned char* s = base + (size_t)l * P.layer * FRAG_BYTES;
-    pack_narrow(a, s, 0, l, P.qkv_j0, P.qkv_nj, KT_D, wid, nwarp, lane);
-    s += (size_t)narrow_tiles(P.qkv_nj, KT_D) * FRAG_BYTES;
-    pack_wide(a, s, 1, l, P.proj_j0, P.proj_nj, P.proj_k0, P.proj_nk, wid, nwarp, lane);
-    s += (size_t)wide_tiles(P.proj_nj, P.proj_nk) * FRAG_BYTES;
-    pack_narrow(a, s, 2, l, P.fc_j0, P.fc_nj, KT_D, wid, nwarp, lane);
-    s += (size_t)narrow_tiles(P.fc_nj, KT_D) * FRAG_BYTES;
-    pack_wide(a, s, 3, l, 0, JT_D, P.fc_j0, P.fc_nj, wid, nwarp, lane);
+    unsigned char* s = base + (size_t)l * (u32)P[PT_LAYER] * FRAG_BYTES;
+    for (int kind = PH_QKV; kind <= PH_P2; kind++) {
+        if (kind == PH_ATT) continue;
+        s += (size_t)pack_segment(a, s, P, kind, l, wid, nwarp, lane) * FRAG_BYTES;
+    }
 }

@@ -140,7 +140,7 @@ class Kernel:
             self.grid = self.sms                                 # one persistent CTA per SM
             self.S = torch.zeros(lowered.scratch_floats, dtype=torch.float32, device=self.device)
             self.bar = torch.zeros(lowered.counters, dtype=torch.int32, device=self.device)
-            self.TS = torch.zeros(1024, dtype=torch.int64, device=self.device)
+            self.TS = torch.zeros(2048, dtype=torch.int64, device=self.device)
             self.PT = torch.from_numpy(np.ascontiguousarray(lowered.place)).to(self.device)
             self.WP = torch.empty(max(lowered.packed_bytes, 512), dtype=torch.uint8, device=self.device)
             self.args, self.keep, self._bound = None, None, None

@@ -33,6 +33,7 @@ KERNEL_TEXT = Path(__file__).resolve().parent / 'csrc' / 'step_kernel.cuh'
 
 CTYPE = {'f32': 'float', 'f16': 'unsigned short', 'i32': 'int'}
 NW = 8                 # consumer warps per CTA (one more warp streams the weights)
+WG = NW                # output tiles per WIDE group: one per consumer warp
 CHUNK_TILES = 32       # 16 KB ring slots
 WN_MAX = 4             # widest NARROW placement
 PT_STRIDE = 16
@@ -247,7 +248,7 @@ def place_step(dims, grid):
         load[c] += KT_D
     qkv = cnt
     # attn-proj: groups of 8 output tiles x slices of the fold, one unit per CTA
-    groups = math.ceil(JT_D / 8)
+    groups = math.ceil(JT_D / WG)
     splits = max(1, min(KT_D, G // groups))
     nk = math.ceil(KT_D / splits)
     units = [(jg, k0) for jg in range(groups) for k0 in range(0, KT_D, nk)]
@@ -256,7 +257,7 @@ def place_step(dims, grid):
     proj = [None] * G
     order = sorted(range(G), key=lambda i: (load[i], i))
     for (jg, k0), c in zip(units, order):
-        j0, nj = jg * 8, min(8, JT_D - jg * 8)
+        j0, nj = jg * WG, min(WG, JT_D - jg * WG)
         kk = min(nk, KT_D - k0)
         proj[c] = (j0, nj, k0, kk)
         load[c] += nj * kk
@@ -363,9 +364,10 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     KT_D = D // 16
-    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + NW * WN_MAX * NB * 128 * 4 + (3 * D + WN_MAX * 16) * 2 + 16
-             + NW * (E + 2) * 4 + B * 8 * NW + B * 4 + 64 + 16)
-    nslot = (SMEM_LIMIT - fixed - 1024) // (CHUNK_TILES * 512 + 16)
+    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + B * (D + 8) * 4 + NW * NB * 512 + (3 * D + WN_MAX * 16) * 2 + 16
+             + NW * (E + 2) * 4 + 8 + B * NW * 8 + B * 4 + B * 8 + 16 + 16)
+    budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
+    nslot = (budget - fixed - 1024) // (CHUNK_TILES * 512 + 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget at this batch')
     nslot = min(nslot, 16)
@@ -375,7 +377,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         return repr(float(np.float32(v))) + 'f'
     scale = dims['scale']
     defs = dict(V_NW=NW, V_B=B, V_NB=NB, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
-                V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
+                V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
@@ -417,7 +419,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', 'every CTA recomputes, one warp per row, into mma operand tiles'),
         (f'{q["$qkv"]} + emits', f'NARROW: whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA; bias, q, K/V emit in the epilogue'),
         (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)', f'one CTA per (sequence, head, 1/{nch} of the positions), online softmax in registers, merged by the projection'),
-        (f'{q["$oo"]}, {q["$z1"]}', f'WIDE: {notes["proj_units"]} units of 8 output tiles x {notes["proj_nk"]} fold tiles, fp32 atomics'),
+        (f'{q["$oo"]}, {q["$z1"]}', f'WIDE: {notes["proj_units"]} units of up to {WG} output tiles x {notes["proj_nk"]} fold tiles, fp32 atomics'),
         (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', 'every CTA recomputes'),
         (f'{q["$u"]}, {q["$g"]}', f'NARROW: {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
         (f'{q["$z2"]}', 'WIDE over the CTA\'s own f tiles, fp32 atomics'),
@@ -426,9 +428,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes'),
     ]
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
-        + ['logits', 'finish', 'mlp: LN2', 'mlp: FC', 'mlp: GELU', '-',
-           'consumer stream wait (clocks)', 'consumer waits not ready', 'producer wait (clocks)', 'producer waits not ready',
-           'chunks', 'launch ns', 'launches']
+        + ['logits', 'finish']
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                   barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
