@@ -9,10 +9,11 @@ token; the median of --repeats runs is reported. The prompt is a seeded uniform 
 the weights are seeded random-init fp16 (the pretrained checkpoint and prompt need a download).
 
 Workloads (BASELINE.json configs): cfg1 = GPT-2 small batch 1, cfg2 = batch 8 (the default: the
-configuration the metric is quoted on), both 128-token prompts + 256 steps; xl1 = XL shape batch 1.
-With --gpus N > 1 every rank (one process per GPU, torchrun) runs the same workload on its own
-sequences: weak scaling, no exchange on the step path; generated tokens are gathered to rank 0 at
-the end.
+configuration the metric is quoted on), both 128-token prompts + 256 steps; cfg3 = batch 64 with
+512-token prompts; xl1 / xl16 = XL shape at batch 1 / 16; cfg5 = 256 ragged sequences split over the
+GPUs (strong scaling). With --gpus N > 1 every rank (one process per GPU, torchrun) runs its own
+sequences (the same batch per GPU: weak scaling, except cfg5) with no exchange on the step path;
+generated tokens are gathered to rank 0 at the end.
 
 `value`   tokens/s with everything resident in HBM (CUDA events around the K launches)
 `e2e`     tokens/s through the public API with host buffers: every step copies the input tokens
@@ -39,7 +40,11 @@ import numpy as np      # noqa: E402
 WORKLOADS = {
     'cfg1': dict(shape='gpt2', batch=1, prompt=128, gen=256),
     'cfg2': dict(shape='gpt2', batch=8, prompt=128, gen=256),
+    'cfg3': dict(shape='gpt2', batch=64, prompt=512, gen=512),
     'xl1': dict(shape='gpt2_xl', batch=1, prompt=128, gen=256),
+    'xl16': dict(shape='gpt2_xl', batch=16, prompt=128, gen=256),
+    # 256 sequences over all GPUs (strong scaling), ragged prompts of 64..512 tokens, per-sequence positions
+    'cfg5': dict(shape='gpt2', batch=256, prompt=512, gen=256, ragged=(64, 512), total=True),
     'tiny': dict(shape='tiny3', batch=2, prompt=8, gen=16),
 }
 METRIC, UNIT = 'decode tokens/s', 'tokens/s'
@@ -157,20 +162,45 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group('nccl', device_id=torch.device('cuda', local))
-    B, P, K, Wm = wl['batch'], wl['prompt'], args.steps, max(args.warmup, 3)
+    P, K, Wm = wl['prompt'], args.steps, max(args.warmup, 3)
+    total = bool(wl.get('total'))
+    if total and wl['batch'] % world:
+        raise SystemExit(f'{wl["batch"]} sequences do not split over {world} GPUs')
+    B = wl['batch'] // world if total else wl['batch']
     tmax = P + max(K, Wm) + 1
     if tmax > sh.C:
         raise SystemExit(f'prompt + steps = {tmax} exceeds the position table ({sh.C})')
     hf = SynthGPT2(sh, seed=0)
-    m = VestaGPT2(hf, batch=B, tmax=tmax, device=local)
-    prompts = make_prompts(sh, B * world, P, seed=1)[rank * B:(rank + 1) * B]      # every rank its own sequences
-    pd = torch.from_numpy(prompts.copy()).cuda()
+    ragged = wl.get('ragged')
+    if ragged:
+        from vesta_gpu_b200.synth import make_ragged_prompts
+        from vesta_gpu_b200.shard import partition
+        lens_all, toks_all = make_ragged_prompts(sh, B * world, ragged[0], ragged[1], seed=1)
+        mine = partition(lens_all, world)[rank]
+        lens, prompts = lens_all[mine], toks_all[mine]
+        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local, per_sequence_t=True, prompt_len=P)
+        m.prompt.copy_(torch.from_numpy(prompts[:, :P].copy()))
+        m.plen.copy_(torch.from_numpy(lens))
+        start = torch.from_numpy((lens - P).astype(np.int32)).cuda()         # <= 0: every prompt ends at step P
+        first_tok = torch.from_numpy(np.where(lens == P, prompts[:, 0], 0).astype(np.int32)).cuda()
+        ctx_lens = [[int(n) + i + 1 for n in lens_all] for i in range(K)]    # attended positions of every sequence per step
+    else:
+        mine = list(range(rank * B, (rank + 1) * B))
+        prompts = make_prompts(sh, B * world, P, seed=1)[rank * B:(rank + 1) * B]      # every rank its own sequences
+        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local)
+        pd = torch.from_numpy(prompts.copy()).cuda()
+        ctx_lens = [[P + i + 1] * (B * world) for i in range(K)]
 
     def prefill():
         m.reset()
-        for t in range(P):
-            m.x.copy_(pd[:, t])
-            m.step()
+        if ragged:
+            # the kernel feeds itself from the prompt buffer; sequences start late so that all prompts end together
+            m.t.copy_(start); m.x.copy_(first_tok)
+            m.step(P)
+        else:
+            for t in range(P):
+                m.x.copy_(pd[:, t])
+                m.step()
 
     def sync_all():
         torch.cuda.synchronize()
@@ -214,16 +244,22 @@ def main():
         sync_all()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
+        seen = []
         for _ in range(K):
             m.x.copy_(hx, non_blocking=True)        # host -> device: this step's input tokens
             m.step()
             hn.copy_(m.next(), non_blocking=True)   # device -> host: the chosen tokens
             torch.cuda.current_stream().synchronize()
             hx.copy_(hn.to(torch.int32))
+            seen.append(hx.clone())
         e1.record()
         sync_all()
         e2e_times.append(e0.elapsed_time(e1) * 1e-3)
-    e2e_ok = bool(torch.equal(hx.cuda(), stream[:, -1])) if K > 1 else True
+    # after K host-driven steps hx holds the token chosen by generation step K; the device loop's stream
+    # holds the tokens before steps 1..K, so its last column is the token chosen by step K-1
+    e2e_ok = None
+    if K > 1:
+        e2e_ok = bool(torch.equal(torch.stack(seen[:-1], 1), stream[:, 1:].cpu()))
     clocks = sampler.stop(mark) if sampler else None
 
     med = statistics.median(times)
@@ -232,21 +268,21 @@ def main():
         tt = torch.tensor([med, e2e_med], device='cuda', dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         med, e2e_med = float(tt[0]), float(tt[1])
-    all_tokens = gather_tokens(stream.to(torch.int32), list(range(rank * B, (rank + 1) * B)), B * world)
+    all_tokens = gather_tokens(stream.to(torch.int32), list(mine), B * world)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
     assert all_tokens.shape == (B * world, K)
 
-    ctxs = [P + i + 1 for i in range(K)]
-    bytes_per_step = sum(sh.step_bytes([n] * B) for n in ctxs) / K
+    # algorithmic bytes of one launch on one GPU: every weight once + the attended K/V of its sequences
+    bytes_per_step = sum(sh.weight_bytes() + sh.kv_bytes_per_pos() * sum(c) / world for c in ctx_lens) / K
     peak, peak_src = peaks()
     achieved = bytes_per_step / (med / K) / 1e9
     line = dict(metric=METRIC, value=B * world * K / med, unit=UNIT, n_gpus=world, steps=K, warmup=Wm,
-                ms_per_step=1e3 * med / K, higher_is_better=True, scaling='weak', vs_baseline=None,
+                ms_per_step=1e3 * med / K, higher_is_better=True, scaling='strong' if total else 'weak', vs_baseline=None,
                 dtype='f16 weights and KV, f32 accumulate', data='synthetic',
-                config=dict(workload=args.workload, **wl, batch_per_gpu=B, repeats=args.repeats,
+                config=dict(workload=args.workload, **{k: v for k, v in wl.items() if k != 'total'}, batch_per_gpu=B, repeats=args.repeats,
                             l2='weights + KV read per step (%.0f MB) exceed the 126 MB L2' % (bytes_per_step / 1e6),
                             cv=round(statistics.pstdev(times) / statistics.mean(times), 4)),
                 clocks=clocks, gpu_launches=K,

@@ -124,6 +124,59 @@ def test_against_oracle_other_batches(batch):
     m.k.check()
 
 
+@pytest.mark.parametrize('batch,slab_tiles', [(20, 1), (20, None), (9, 1), (33, 2)])
+def test_batches_above_one_slab(batch, slab_tiles):
+    """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged)"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import make_prompts
+    steps = 5
+    m, hf = model(TINY3, 11, 'rich', batch, steps, slab_tiles=slab_tiles)
+    W = O.upcast(hf.weights)
+    feed = make_prompts(TINY3, batch, steps, seed=batch)
+    caches = [O.new_cache(TINY3, steps) for _ in range(batch)]
+    m.reset()
+    for t in range(steps):
+        m.x.copy_(torch.from_numpy(feed[:, t].copy()).cuda()); m.step()
+        lg = m.logits().cpu().numpy(); nx = m.next().cpu().numpy()
+        for i in range(batch):
+            ref, rn = O.step(TINY3, W, caches[i][0], caches[i][1], int(feed[i, t]), t)
+            assert np.abs(lg[i] - ref).max() < TIGHT, (t, i)
+            if O.margin(ref) > MARGIN:
+                assert int(nx[i]) == rn
+    m.k.check()
+
+
+def test_ragged_prompts_fed_on_the_device():
+    """per-sequence prompt lengths, consumed by the kernel's own feedback (no host write between steps),
+    late starts so that every prompt ends at the same step; the greedy streams equal the oracle's"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import make_ragged_prompts
+    B, gen = 6, 8
+    lens, toks = make_ragged_prompts(TINY3, B, 1, 9, seed=3)
+    pmax = int(lens.max()); steps = pmax + gen
+    m, hf = model(TINY3, 11, 'rich', B, steps, per_sequence_t=True, prompt_len=pmax)
+    W = O.upcast(hf.weights)
+    m.reset()
+    m.prompt.copy_(torch.from_numpy(toks[:, :pmax].copy())); m.plen.copy_(torch.from_numpy(lens))
+    start = (lens - pmax).astype(np.int32)
+    m.t.copy_(torch.from_numpy(start)); m.x.copy_(torch.from_numpy(np.where(start == 0, toks[:, 0], 0).astype(np.int32)))
+    got = []
+    for _ in range(steps - 1):
+        m.step(); got.append(m.x.clone())
+    got = torch.stack(got, 1).cpu().numpy()
+    m.k.check()
+    assert m.t.cpu().numpy().tolist() == (lens + gen - 1).tolist()
+    for i in range(B):
+        r = O.decode(TINY3, W, toks[i, :lens[i]], gen)
+        mine = got[i, pmax - 1: pmax - 1 + gen - 1]
+        ref = r['tokens'][lens[i] - 1: lens[i] - 1 + gen - 1]
+        sure = r['margins'][lens[i] - 1: lens[i] - 1 + gen - 1] > MARGIN
+        stop = len(ref) if sure.all() else int(np.argmin(sure))
+        assert np.array_equal(mine[:stop], ref[:stop]), i
+
+
 def test_per_sequence_positions_ragged_starts():
     """every sequence at its own position: sequence b starts b*2 steps late"""
     from oracle import gpt2_numpy as O

@@ -147,3 +147,15 @@ def test_per_sequence_positions():
     low = lower_for(TINY, 4, 32, per_sequence_t=True)
     assert '#define V_TSTRIDE 1' in low.src
     assert dict((p[0], p[1]) for p in low.params)['t'] == 'i32'
+
+
+def test_slabs_and_device_side_prompts():
+    low = lower_for(GPT2_SMALL, 64, 1024)
+    assert low.dims['NB'] == 4 and '#define V_NB 4' in low.src           # 32 rows per slab, two slabs
+    assert low.shared_bytes <= 227 * 1024
+    low = lower_for(TINY, 20, 16, slab_tiles=1)
+    assert low.dims['NB'] == 1
+    low = lower_for(TINY, 4, 16, per_sequence_t=True, prompt_len=9)
+    assert [p[0] for p in low.params][-2:] == ['prompt', 'plen'] and '#define V_PLEN 9' in low.src
+    low = lower_for(TINY, 4, 16, feedback=False, prompt_len=9)            # nothing to feed back into
+    assert [p[0] for p in low.params][-1] == 'vals' and '#define V_PLEN 0' in low.src

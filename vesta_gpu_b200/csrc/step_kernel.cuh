@@ -110,26 +110,34 @@ __device__ __forceinline__ u64 best_key(float v, u32 n) {
 #define PT_LOG_J0 10     // WIDE over the whole fold
 #define PT_LOG_NJ 11
 
-// phases of a step, in order: layer l contributes QKV, ATT, PROJ, FC, P2; LOGITS closes the step
+// A step is a sequence of phases separated by grid barriers: per layer QKV, ATT, PROJ, MLP (= FC then
+// P2 inside the CTA), then LOGITS. Batches above one slab (SB = 8 * V_NB rows: what the operand
+// tiles in shared memory hold) repeat the contraction phases slab by slab; the weight stream of
+// the phase is then read once per slab (from L2 after the first).
 #define PH_QKV 0
 #define PH_ATT 1
 #define PH_PROJ 2
 #define PH_FC 3
 #define PH_P2 4
 #define PH_LOGITS 5
-#define PH_PER_LAYER 5
+#define PH_PER_LAYER 4                // QKV, ATT, PROJ, MLP
+#define SB (8 * V_NB)                 // rows per slab
+#define NSLAB ((V_B + SB - 1) / SB)
 
 // A stream segment is a list of groups; a group is `rows` rows of `width` tiles, cut into chunks of
 // whole rows, at most V_CH tiles per chunk. NARROW segment: one group (rows = fold tiles, width =
 // output tiles). WIDE segment: one group per WG output tiles (rows = the CTA's fold tiles).
-struct Seg { int rows, nj; bool wide; };
+// off: first tile of the segment inside the layer's part of the stream.
+struct Seg { int rows, nj, off; bool wide; };
 
 __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
     Seg s;
+    const int n_qkv = P[PT_QKV_NJ] * KT_D, n_proj = P[PT_PROJ_NJ] * P[PT_PROJ_NK], n_fc = P[PT_FC_NJ] * KT_D;
     s.wide = (kind == PH_PROJ) | (kind == PH_P2) | (kind == PH_LOGITS);
     s.rows = (kind == PH_PROJ) ? P[PT_PROJ_NK] : (kind == PH_P2) ? P[PT_FC_NJ] : KT_D;
     s.nj = (kind == PH_QKV) ? P[PT_QKV_NJ] : (kind == PH_PROJ) ? P[PT_PROJ_NJ] : (kind == PH_FC) ? P[PT_FC_NJ]
          : (kind == PH_P2) ? JT_D : (kind == PH_LOGITS) ? P[PT_LOG_NJ] : 0;
+    s.off = (kind == PH_PROJ) ? n_qkv : (kind == PH_FC) ? n_qkv + n_proj : (kind == PH_P2) ? n_qkv + n_proj + n_fc : 0;
     if (s.rows == 0) s.nj = 0;
     return s;
 }
@@ -140,16 +148,17 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define SM_RING 0
 #define SM_ACT (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)            // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
-#define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // fp32 rows staged for LayerNorm
-#define SM_RED (SM_ZS + V_B * (V_D + 8) * 4)                      // NARROW partial sums, one tile per warp
+#define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // eight fp32 rows staged for LayerNorm
+#define SM_RED (SM_ZS + 8 * (V_D + 8) * 4)                        // NARROW partial sums, one tile per warp
 #define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
 #define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
 #define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
 #define MISC_ATT 0                                                // NW x (V_E + 2) floats
-#define MISC_BEST (((NW * (V_E + 2) * 4) + 7) & ~7)               // V_B x NW u64
-#define MISC_POS (MISC_BEST + V_B * NW * 8)                       // V_B ints
-#define MISC_STAT (MISC_POS + V_B * 4)                            // V_B x 2 floats
-#define SM_MISC_BYTES (MISC_STAT + V_B * 8 + 16)
+#define MISC_BEST (((NW * (V_E + 2) * 4) + 7) & ~7)               // SB x NW u64
+#define MISC_POS (MISC_BEST + SB * NW * 8)                        // V_B ints
+#define MISC_STAT (MISC_POS + V_B * 4)                            // 8 x 2 floats
+#define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
+#define SM_MISC_BYTES (MISC_FLAG + 16)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
 #define SM_TOTAL (SM_BARS + 2 * V_NSLOT * 8)
 
@@ -231,28 +240,36 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta) {
     Ctx c;
     c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta;
-    const unsigned char* src = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
+    const unsigned char* base = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
 #pragma unroll 1
     for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
-        const int kind = (ph == V_L * PH_PER_LAYER) ? PH_LOGITS : ph % PH_PER_LAYER;
-        if (kind == PH_ATT) continue;
-        const Seg s = seg_of(P, kind);
+        const int l = ph / PH_PER_LAYER;
+        const int first = (l == V_L) ? PH_LOGITS : (ph - l * PH_PER_LAYER == 3 ? PH_FC : ph - l * PH_PER_LAYER);
+        if (first == PH_ATT) continue;
+        const int last = (first == PH_FC) ? PH_P2 : first;
 #pragma unroll 1
-        for (int j = 0; j < s.nj; j += (s.wide ? WG : WN_MAX * 4)) {
-            const int width = s.wide ? min(WG, s.nj - j) : s.nj;
-            const int rpc = V_CH / width;
+        for (int slab = 0; slab < NSLAB; slab++)
 #pragma unroll 1
-            for (int r = 0; r < s.rows; r += rpc) {
-                const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-                wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
-                if (c.dead) return;
-                const u32 bytes = (u32)(min(rpc, s.rows - r) * width) * FRAG_BYTES;
-                mbar_expect(full_bar(c, slot), bytes);
-                bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, bytes, full_bar(c, slot));
-                src += bytes;
-                c.chunk++;
+            for (int kind = first; kind <= last; kind++) {
+                const Seg s = seg_of(P, kind);
+                const unsigned char* src = base + ((size_t)l * (u32)P[PT_LAYER] + s.off) * FRAG_BYTES;
+#pragma unroll 1
+                for (int j = 0; j < s.nj; j += (s.wide ? WG : WN_MAX * 4)) {
+                    const int width = s.wide ? min(WG, s.nj - j) : s.nj;
+                    const int rpc = V_CH / width;
+#pragma unroll 1
+                    for (int r = 0; r < s.rows; r += rpc) {
+                        const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+                        wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
+                        if (c.dead) return;
+                        const u32 bytes = (u32)(min(rpc, s.rows - r) * width) * FRAG_BYTES;
+                        mbar_expect(full_bar(c, slot), bytes);
+                        bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, bytes, full_bar(c, slot));
+                        src += bytes;
+                        c.chunk++;
+                    }
+                }
             }
-        }
     }
 }
 
@@ -340,7 +357,7 @@ __device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* g
     if (tb && c.tid < tiles * 2) cp16(prm + 3 * V_D + c.tid * 8, tb + c.tid * 8);
 }
 
-// LayerNorm of the rows of z (global, fp32, [V_B][V_D]) into the operand tiles; gain and shift come
+// LayerNorm of `nrows` rows of z (global, fp32, row stride V_D: one slab) into the operand tiles; gain and shift come
 // from the parameter block in shared memory. The rows are staged in shared memory (row stride
 // ZS_STRIDE floats, which spreads the rows over the banks), one warp per row computes mean and
 // variance (two passes), then every warp converts whole operand tiles: lane (b, t) of a tile
@@ -349,77 +366,82 @@ __device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* g
 // combined into: init[b][d] += z[b][d] + bias[d], the fold tiles dealt over the CTAs (init was
 // zeroed a phase earlier).
 #define ZS_STRIDE (V_D + 8)
-__device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act) {
+__device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act, int nrows) {
     const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
     float* zs = reinterpret_cast<float*>(c.smem + SM_ZS);
     float* stat = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_STAT);
-#pragma unroll 1
-    for (int i = c.tid; i < V_B * G4; i += NCONS) {
-        const int b = i / G4, g = i - b * G4;
-        cp16(zs + b * ZS_STRIDE + g * 4, z + (size_t)b * V_D + g * 4);
-    }
-    cp_wait();
-    cons_sync();
-    TRACE(40);
-#pragma unroll 1
-    for (int b = c.warp; b < V_B; b += NW) {
-        const float4* row = reinterpret_cast<const float4*>(zs + b * ZS_STRIDE);
-        float s = 0.f;
-#pragma unroll 2
-        for (int g = c.lane; g < G4; g += 32) { const float4 v = row[g]; s += (v.x + v.y) + (v.z + v.w); }
-#pragma unroll
-        for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-        const float mean = s * (1.0f / V_D);
-        float q = 0.f;
-#pragma unroll 2
-        for (int g = c.lane; g < G4; g += 32) {
-            const float4 v = row[g];
-            const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
-            q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
-        }
-#pragma unroll
-        for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-        if (c.lane == 0) { stat[2 * b] = mean; stat[2 * b + 1] = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS); }
-    }
-    cons_sync();
-    TRACE(41);
     const int bl = c.lane >> 2, t = c.lane & 3;
+    // eight rows (one batch tile of the operand) at a time
 #pragma unroll 1
-    for (int it = c.warp; it < KT_D * V_NB; it += NW) {
-        const int kt = it / V_NB, nb = it - kt * V_NB, b = nb * 8 + bl, k = kt * 16 + 2 * t;
-        uint4 out = make_uint4(0, 0, 0, 0);
-        if (b < V_B) {
-            const float2 v0 = *reinterpret_cast<const float2*>(zs + b * ZS_STRIDE + k);
-            const float2 v1 = *reinterpret_cast<const float2*>(zs + b * ZS_STRIDE + k + 8);
-            const float mean = stat[2 * b], rs = stat[2 * b + 1];
-            const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
-            const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
-            const float o0 = (v0.x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0.y - mean) * rs * h_hi(w0) + h_hi(s0);
-            const float o2 = (v1.x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1.y - mean) * rs * h_hi(w1) + h_hi(s1);
-            out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
-            out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
-            if (init && (kt % c.ncta) == c.cta) {
-                const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
-                float* dst = init + (size_t)b * V_D + k;
-                red_add(dst, v0.x + h_lo(i0)); red_add(dst + 1, v0.y + h_hi(i0));
-                red_add(dst + 8, v1.x + h_lo(i1)); red_add(dst + 9, v1.y + h_hi(i1));
-            }
+    for (int nb = 0; nb < V_NB; nb++) {
+        const int r0 = nb * 8, nr = min(8, nrows - r0);        // nr <= 0: the tile is written as zeros
+#pragma unroll 1
+        for (int i = c.tid; i < nr * G4; i += NCONS) {
+            const int b = i / G4, g = i - b * G4;
+            cp16(zs + b * ZS_STRIDE + g * 4, z + (size_t)(r0 + b) * V_D + g * 4);
         }
-        *reinterpret_cast<uint4*>(act + ((size_t)it * 32 + c.lane) * 16) = out;
+        cp_wait();
+        cons_sync();
+        TRACE(40);
+#pragma unroll 1
+        for (int b = c.warp; b < nr; b += NW) {
+            const float4* row = reinterpret_cast<const float4*>(zs + b * ZS_STRIDE);
+            float s = 0.f;
+#pragma unroll 2
+            for (int g = c.lane; g < G4; g += 32) { const float4 v = row[g]; s += (v.x + v.y) + (v.z + v.w); }
+#pragma unroll
+            for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+            const float mean = s * (1.0f / V_D);
+            float q = 0.f;
+#pragma unroll 2
+            for (int g = c.lane; g < G4; g += 32) {
+                const float4 v = row[g];
+                const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
+                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+            }
+#pragma unroll
+            for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
+            if (c.lane == 0) { stat[2 * b] = mean; stat[2 * b + 1] = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS); }
+        }
+        cons_sync();
+        TRACE(41);
+#pragma unroll 1
+        for (int kt = c.warp; kt < KT_D; kt += NW) {
+            const int k = kt * 16 + 2 * t;
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (bl < nr) {
+                const float2 v0 = *reinterpret_cast<const float2*>(zs + bl * ZS_STRIDE + k);
+                const float2 v1 = *reinterpret_cast<const float2*>(zs + bl * ZS_STRIDE + k + 8);
+                const float mean = stat[2 * bl], rs = stat[2 * bl + 1];
+                const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
+                const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
+                const float o0 = (v0.x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0.y - mean) * rs * h_hi(w0) + h_hi(s0);
+                const float o2 = (v1.x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1.y - mean) * rs * h_hi(w1) + h_hi(s1);
+                out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
+                out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
+                if (init && (kt % c.ncta) == c.cta) {
+                    const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
+                    float* dst = init + (size_t)(r0 + bl) * V_D + k;
+                    red_add(dst, v0.x + h_lo(i0)); red_add(dst + 1, v0.y + h_hi(i0));
+                    red_add(dst + 8, v1.x + h_lo(i1)); red_add(dst + 9, v1.y + h_hi(i1));
+                }
+            }
+            *reinterpret_cast<uint4*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * 16) = out;
+        }
+        cons_sync();
     }
-    cons_sync();
 }
 
 // Attention output for the fold range [k0*16, (k0+nk)*16) of the projection, merged from the
 // per-chunk partial results (m, sum, unnormalised o[V_E]) of the attention phase, into operand
 // tiles 0..nk-1.
 #define PART_STRIDE (V_E + 2)
-__device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act) {
+__device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, int row0, int nrows) {
     const int cols = nk * 16;
 #pragma unroll 1
-    for (int i = c.tid; i < V_B * cols; i += NCONS) {
+    for (int i = c.tid; i < nrows * cols; i += NCONS) {
         const int b = i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
-        const float* p = part + (size_t)((b * V_H + h) * V_NCH) * PART_STRIDE;
+        const float* p = part + (size_t)(((row0 + b) * V_H + h) * V_NCH) * PART_STRIDE;
         // all loads first (independent, one round trip), then the arithmetic
         float mm[V_NCH], dd[V_NCH], oo[V_NCH], M = -3.0e38f;
 #pragma unroll
@@ -435,7 +457,7 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
             den += w * dd[ch];
             num += w * oo[ch];
         }
-        act_store1(act, b, kk, num / den);
+        act_store1(act, b, kk, den > 0.f ? num / den : 0.f);      // a sequence that has not started attends to nothing
     }
     cons_sync();
 }
@@ -467,7 +489,7 @@ __device__ __forceinline__ void attention_item(Ctx& c, const u16* __restrict__ k
         uint4 kk[ATT_UNROLL], vv[ATT_UNROLL];
 #pragma unroll
         for (int u = 0; u < ATT_UNROLL; u++) {
-            const int s = min(base + grp + u * NG, n - 1);
+            const int s = min(base + grp + u * NG, n - 1);          // n >= 1 inside the loop
             kk[u] = __ldcg(reinterpret_cast<const uint4*>(keys + row0 + (size_t)s * V_D));
             vv[u] = __ldcg(reinterpret_cast<const uint4*>(vals + row0 + (size_t)s * V_D));
         }
@@ -537,6 +559,7 @@ struct Args {
     const u16 *wte, *wpe, *ln1w, *ln1b, *qkvb, *ob, *ln2w, *ln2b, *fcb, *pb, *lnfw, *lnfb;
     u16 *keys, *vals;
     int* x_out; int* t_out;
+    const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
 };
@@ -562,18 +585,19 @@ __device__ __forceinline__ void step_body(const Args& a) {
     const u64 t_begin_ = now_ns();
 #endif
 
-    // inputs outside their ranges would index outside the caches and tables: refuse the step
-    // (every CTA sees the same values and takes the same branch)
+    // Positions and tokens outside their ranges would index outside the caches and tables: refuse the
+    // step (every CTA sees the same values and takes the same branch). A negative position marks a
+    // sequence that has not started yet: its row is carried along but reads and writes no cache.
     int* s_pos = reinterpret_cast<int*>(smem + SM_MISC + MISC_POS);
     {
-        bool bad = false;
+        int bad = 0;
 #pragma unroll 1
-        for (int b = 0; b < V_B; b++) {
+        for (int b = c.tid; b < V_B; b += NTHREADS) {
             const int tb = a.t[b * V_TSTRIDE], xb = a.x[b];
-            bad |= (tb < 0) | (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
-            if (c.tid == 0) s_pos[b] = tb;
+            bad |= (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
+            s_pos[b] = tb;
         }
-        if (bad) {
+        if (__syncthreads_or(bad)) {
             if (c.cta == 0 && c.tid == 0) atomicCAS(a.bar + BAR_STATUS, 0u, 0x900u);
             return;
         }
@@ -582,7 +606,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // operand tiles start as zero: rows of a batch tile beyond V_B stay zero for the whole launch
+    // operand tiles start as zero: rows of a batch tile beyond the batch stay zero for the whole launch
 #pragma unroll 1
     for (int i = c.tid; i < (SM_ZS - SM_ACT) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_ACT)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
@@ -598,21 +622,20 @@ __device__ __forceinline__ void step_body(const Args& a) {
     unsigned char* gact = smem + SM_GACT;
     float* red = reinterpret_cast<float*>(smem + SM_RED);
     const u16* prm = reinterpret_cast<const u16*>(smem + SM_PRM);
+    u64* wbest = reinterpret_cast<u64*>(smem + SM_MISC + MISC_BEST);
     float* Z = a.S + V_OFF_Z;
     float* qbuf = a.S + V_OFF_Q;
     float* part = a.S + V_OFF_PART;
     float* logit = a.S + V_OFF_LOGIT;
+    u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
-    u64 best[V_NB][2];
-#pragma unroll
-    for (int nb = 0; nb < V_NB; nb++) { best[nb][0] = 0; best[nb][1] = 0; }
 
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
 #pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
         const int b = i / V_D, d = i - b * V_D;
-        Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)s_pos[b] * V_D + d]);
+        Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)max(s_pos[b], 0) * V_D + d]);
         Z[ZS + i] = 0.f;
     }
     TICK(0);
@@ -624,159 +647,184 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #pragma unroll 1
     for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
         const int l = ph / PH_PER_LAYER;
-        const int kind = (l == V_L) ? PH_LOGITS : ph - l * PH_PER_LAYER;
+        const int first = (l == V_L) ? PH_LOGITS : (ph - l * PH_PER_LAYER == 3 ? PH_FC : ph - l * PH_PER_LAYER);
+        const int last = (first == PH_FC) ? PH_P2 : first;
         float* zin = Z + (size_t)((2 * l) % 3) * ZS;          // layer input (for LOGITS: the final state)
         float* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
         float* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
 #if V_TIMING
         c.tron = (c.cta == V_TIMING - 1) && (l == V_L / 2);
 #endif
-        TRACE(1 + kind);
+        TRACE(1 + first);
 
-        // ---- prologue: what the phase reads from other CTAs, into shared memory
-        if (kind == PH_QKV || kind == PH_FC || kind == PH_LOGITS) {
-            // LN1 (starts z1 = z + ob, clears z2) | LN2 (starts z2 = z1 + pb, clears zin for the next layer) | LNf
-            float* clr = (kind == PH_QKV) ? z2 : (kind == PH_FC) ? zin : (float*)0;
-            if (clr) {
-#pragma unroll 1
-                for (int i = gtid; i < V_B * V_D; i += gthreads) clr[i] = 0.f;
-            }
-            ln_to_act(c, (kind == PH_FC) ? z1 : zin, (kind == PH_QKV) ? z1 : (kind == PH_FC) ? z2 : (float*)0, act);
-        } else if (kind == PH_ATT) {
+        if (first == PH_ATT) {
             // one (sequence, head, chunk of positions) at a time, partial results to scratch
 #pragma unroll 1
             for (int it = c.cta; it < V_B * V_H * V_NCH; it += c.ncta) {
                 const int ch = it % V_NCH, bh = it / V_NCH, b = bh / V_H, h = bh - b * V_H;
-                const int n = s_pos[b] + 1, cs = (n + V_NCH - 1) / V_NCH;
+                const int n = s_pos[b] + 1, cs = (max(n, 1) + V_NCH - 1) / V_NCH;
                 attention_item(c, a.keys, a.vals, qbuf, part + (size_t)it * PART_STRIDE, b, h, l, ch * cs, min(n, (ch + 1) * cs));
             }
-        } else if (kind == PH_PROJ) {
-            if (P[PT_PROJ_NJ]) merge_to_act(c, part, P[PT_PROJ_K0], P[PT_PROJ_NK], act);
-        }
-        TRACE(10 + kind);
-
-        // ---- the contraction, group by group, each followed by its epilogue
-        const Seg sg = seg_of(P, kind);
+        } else {
+            // LN1 phase clears z2 (the MLP adds into it two barriers later); LN2 phase clears zin for the next layer
+            float* clr = (first == PH_QKV) ? z2 : (first == PH_FC) ? zin : (float*)0;
+            if (clr) {
 #pragma unroll 1
-        for (int j = 0; j < sg.nj; j += (sg.wide ? WG : WN_MAX * 4)) {
-            const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
-            float acc[V_NB][4];
-            gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
-            if (!sg.wide) {
-                // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
-#pragma unroll
-                for (int nb = 0; nb < V_NB; nb++)
-                    *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
-                cons_sync();
-#pragma unroll 1
-                for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
-                    const int jj = o / (V_NB * 128), r = o - jj * (V_NB * 128);
-                    float v = 0.f;
-#pragma unroll 1
-                    for (int w = jj; w < NW; w += width) v += red[(size_t)w * V_NB * 128 + r];
-                    const int i = r & 3, ln = (r >> 2) & 31, nb = r >> 7;
-                    const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (ln & 3) * 2 + (i & 1);
-                    v += h2f(prm[3 * V_D + jj * 16 + j_in]);
-                    if (kind == PH_QKV) {
-                        // q to scratch, K and V rounded to fp16 into the cache at t
-                        if (b < V_B) {
-                            const int jx = (P[PT_QKV_J0] + jj) * 16 + j_in;
-                            if (jx < V_D) qbuf[(size_t)b * V_D + jx] = v;
-                            else {
-                                const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
-                                if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
-                            }
-                        }
-                    } else {
-                        // g = gelu(u) -> operand tiles of the MLP projection: fold index = jj*16 + j_in
-                        const float g = (b < V_B) ? V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))) : 0.f;
-                        act_store1(gact, b, jj * 16 + j_in, g);
-                    }
-                }
-                cons_sync();
-            } else if (c.warp < width) {
-                const int jt = ((kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0) + j + c.warp;
-                float* zt = (kind == PH_PROJ) ? z1 : z2;
-#pragma unroll
-                for (int nb = 0; nb < V_NB; nb++)
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), b = nb * 8 + (c.lane & 3) * 2 + (i & 1);
-                        if (kind != PH_LOGITS) {
-                            if (b < V_B) red_add(zt + (size_t)b * V_D + jx, acc[nb][i]);
-                        } else if (b < V_B && jx < V_N) {
-                            logit[(size_t)b * V_N + jx] = acc[nb][i];
-                            const u64 k = best_key(acc[nb][i], (u32)jx);
-                            if (k > best[nb][i & 1]) best[nb][i & 1] = k;
-                        }
-                    }
+                for (int i = gtid; i < V_B * V_D; i += gthreads) clr[i] = 0.f;
             }
         }
-        TRACE(20 + kind);
-        if (kind == PH_FC || kind == PH_LOGITS) continue;          // FC feeds P2 inside the CTA; LOGITS ends below
+
+#pragma unroll 1
+        for (int slab = 0; slab < ((first == PH_ATT) ? 0 : NSLAB); slab++) {
+            const int row0 = slab * SB, nrows = min(SB, V_B - row0);
+#pragma unroll 1
+            for (int kind = first; kind <= last; kind++) {
+                // ---- prologue: what the contraction reads from other CTAs, into operand tiles
+                if (kind == PH_QKV || kind == PH_FC || kind == PH_LOGITS)
+                    // LN1 (starts z1 = z + ob) | LN2 (starts z2 = z1 + pb) | LNf
+                    ln_to_act(c, ((kind == PH_FC) ? z1 : zin) + (size_t)row0 * V_D,
+                              (kind == PH_QKV) ? z1 + (size_t)row0 * V_D : (kind == PH_FC) ? z2 + (size_t)row0 * V_D : (float*)0, act, nrows);
+                else if (kind == PH_PROJ && P[PT_PROJ_NJ])
+                    merge_to_act(c, part, P[PT_PROJ_K0], P[PT_PROJ_NK], act, row0, nrows);
+                TRACE(10 + kind);
+
+                // ---- the contraction, group by group, each followed by its epilogue
+                const Seg sg = seg_of(P, kind);
+                u64 best[V_NB][2];
+#pragma unroll
+                for (int nb = 0; nb < V_NB; nb++) { best[nb][0] = 0; best[nb][1] = 0; }
+#pragma unroll 1
+                for (int j = 0; j < sg.nj; j += (sg.wide ? WG : WN_MAX * 4)) {
+                    const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
+                    float acc[V_NB][4];
+                    gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
+                    if (!sg.wide) {
+                        // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
+#pragma unroll
+                        for (int nb = 0; nb < V_NB; nb++)
+                            *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+                        cons_sync();
+#pragma unroll 1
+                        for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
+                            const int jj = o / (V_NB * 128), r = o - jj * (V_NB * 128);
+                            float v = 0.f;
+#pragma unroll 1
+                            for (int w = jj; w < NW; w += width) v += red[(size_t)w * V_NB * 128 + r];
+                            const int i = r & 3, ln = (r >> 2) & 31, nb = r >> 7;
+                            const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (ln & 3) * 2 + (i & 1), b = row0 + rb;
+                            v += h2f(prm[3 * V_D + jj * 16 + j_in]);
+                            if (kind == PH_QKV) {
+                                // q to scratch, K and V rounded to fp16 into the cache at t
+                                if (rb < nrows) {
+                                    const int jx = (P[PT_QKV_J0] + jj) * 16 + j_in;
+                                    if (jx < V_D) qbuf[(size_t)b * V_D + jx] = v;
+                                    else if (s_pos[b] >= 0) {
+                                        const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
+                                        if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
+                                    }
+                                }
+                            } else {
+                                // g = gelu(u) -> operand tiles of the MLP projection: fold index = jj*16 + j_in
+                                const float g = (rb < nrows) ? V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))) : 0.f;
+                                act_store1(gact, rb, jj * 16 + j_in, g);
+                            }
+                        }
+                        cons_sync();
+                    } else if (c.warp < width) {
+                        const int jt = ((kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0) + j + c.warp;
+                        float* zt = (kind == PH_PROJ) ? z1 : z2;
+#pragma unroll
+                        for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+                            for (int i = 0; i < 4; i++) {
+                                const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (c.lane & 3) * 2 + (i & 1), b = row0 + rb;
+                                if (kind != PH_LOGITS) {
+                                    if (rb < nrows) red_add(zt + (size_t)b * V_D + jx, acc[nb][i]);
+                                } else if (rb < nrows && jx < V_N) {
+                                    logit[(size_t)b * V_N + jx] = acc[nb][i];
+                                    const u64 k = best_key(acc[nb][i], (u32)jx);
+                                    if (k > best[nb][i & 1]) best[nb][i & 1] = k;
+                                }
+                            }
+                    }
+                }
+                if (kind == PH_LOGITS) {
+                    // argmax of the slab: per row the max over the lanes that hold it (equal lane&3), the warps, the CTAs
+#pragma unroll
+                    for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+                        for (int p = 0; p < 2; p++) {
+                            u64 k = best[nb][p];
+#pragma unroll
+                            for (int m = 4; m <= 16; m <<= 1) {
+                                const u64 o = __shfl_xor_sync(0xffffffffu, k, m);
+                                if (o > k) k = o;
+                            }
+                            if ((c.lane >> 2) == 0) wbest[(nb * 8 + (c.lane & 3) * 2 + p) * NW + c.warp] = k;
+                        }
+                    cons_sync();
+                    if (c.tid < nrows) {
+                        u64 k = 0;
+#pragma unroll 1
+                        for (int w = 0; w < NW; w++) if (wbest[c.tid * NW + w] > k) k = wbest[c.tid * NW + w];
+                        if (k) atomicMax(gbest + row0 + c.tid, k);
+                    }
+                    cons_sync();
+                }
+                TRACE(20 + kind);
+            }
+        }
+        if (first == PH_LOGITS) break;
 
         // ---- grid barrier; the next LayerNorm's parameters are fetched while waiting
-        TICK(2 + 2 * kind - (kind == PH_P2 ? 2 : 0));
+        TICK(2 + 2 * (ph - l * PH_PER_LAYER));
         phase_end(c);
-        if (kind == PH_PROJ)
+        if (first == PH_PROJ)
             fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
                          a.fcb + (size_t)l * V_F + P[PT_FC_J0] * 16, P[PT_FC_NJ]);
-        else if (kind == PH_P2) {
+        else if (first == PH_FC) {
             if (l + 1 < V_L)
                 fetch_params(c, a.ln1w + (size_t)(l + 1) * V_D, a.ln1b + (size_t)(l + 1) * V_D, a.ob + (size_t)(l + 1) * V_D,
                              a.qkvb + (size_t)(l + 1) * 3 * V_D + P[PT_QKV_J0] * 16, P[PT_QKV_NJ]);
             else
                 fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
         }
-        TRACE(30 + kind);
+        TRACE(30 + first);
         phase_wait(c);
-        TICK(3 + 2 * kind - (kind == PH_P2 ? 2 : 0));
-    }
-
-    // ---- argmax: per batch row the max over the lanes that hold it (equal lane&3), the warps, the CTAs
-    u64* wbest = reinterpret_cast<u64*>(smem + SM_MISC + MISC_BEST);
-#pragma unroll
-    for (int nb = 0; nb < V_NB; nb++)
-#pragma unroll
-        for (int p = 0; p < 2; p++) {
-            u64 k = best[nb][p];
-#pragma unroll
-            for (int m = 4; m <= 16; m <<= 1) {
-                const u64 o = __shfl_xor_sync(0xffffffffu, k, m);
-                if (o > k) k = o;
-            }
-            const int b = nb * 8 + (c.lane & 3) * 2 + p;
-            if ((c.lane >> 2) == 0 && b < V_B) wbest[b * NW + c.warp] = k;
-        }
-    cons_sync();
-    u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
-    if (c.tid < V_B) {
-        u64 k = 0;
-#pragma unroll 1
-        for (int w = 0; w < NW; w++) if (wbest[c.tid * NW + w] > k) k = wbest[c.tid * NW + w];
-        if (k) atomicMax(gbest + c.tid, k);
+        TICK(3 + 2 * (ph - l * PH_PER_LAYER));
     }
     TICK(10);
-    // the last CTA to arrive publishes next, feeds it back into x and advances t
+
+    // ---- the last CTA to arrive publishes next, feeds it (or the next prompt token) back into x, advances t
+    int* flag = reinterpret_cast<int*>(smem + SM_MISC + MISC_FLAG);
     cons_sync();
     if (c.tid == 0) {
         __threadfence();
-        const u32 old = atomicAdd(a.bar + BAR_DONE, 1u);
-        if (old == (u32)c.ncta - 1) {
-            __threadfence();
+        *flag = (atomicAdd(a.bar + BAR_DONE, 1u) == (u32)c.ncta - 1);
+        __threadfence();
+    }
+    cons_sync();
+    if (*flag) {
 #pragma unroll 1
-            for (int b = 0; b < V_B; b++) {
-                const u64 k = atomicExch(gbest + b, 0ull);
-                const u32 n = 0xFFFFFFFFu - (u32)(k & 0xFFFFFFFFull);
-                a.S[V_OFF_NEXT + b] = (float)n;
+        for (int b = c.tid; b < V_B; b += NCONS) {
+            const u64 k = atomicExch(gbest + b, 0ull);
+            const u32 n = 0xFFFFFFFFu - (u32)(k & 0xFFFFFFFFull);
+            a.S[V_OFF_NEXT + b] = (float)n;
 #if V_FEEDBACK
-                a.x_out[b] = (int)n;
+            int nx = (int)n;
+#if V_PLEN
+            const int tn = s_pos[b] + V_TSTEP;
+            if (tn >= 0 && tn < a.plen[b]) nx = a.prompt[(size_t)b * V_PLEN + tn];
 #endif
-            }
+            a.x_out[b] = (nx < 0 || nx >= V_N) ? 0 : nx;
+            if (V_TSTRIDE) a.t_out[b] = s_pos[b] + V_TSTEP;
+#endif
+        }
 #if V_FEEDBACK
-#pragma unroll 1
-            for (int b = 0; b < (V_TSTRIDE ? V_B : 1); b++) a.t_out[b] += V_TSTEP;
+        if (!V_TSTRIDE && c.tid == 0) a.t_out[0] = s_pos[0] + V_TSTEP;
 #endif
+        cons_sync();
+        if (c.tid == 0) {
             atomicExch(a.bar + BAR_COUNT, 0u);     // every CTA is past its last barrier
             atomicExch(a.bar + BAR_DONE, 0u);
         }
@@ -854,9 +902,8 @@ __device__ void pack_body(const PackArgs& a) {
         pack_segment(a, base + (size_t)V_L * (u32)P[PT_LAYER] * FRAG_BYTES, P, PH_LOGITS, 0, wid, nwarp, lane);
         return;
     }
-    unsigned char* s = base + (size_t)l * (u32)P[PT_LAYER] * FRAG_BYTES;
     for (int kind = PH_QKV; kind <= PH_P2; kind++) {
         if (kind == PH_ATT) continue;
-        s += (size_t)pack_segment(a, s, P, kind, l, wid, nwarp, lane) * FRAG_BYTES;
+        pack_segment(a, base + ((size_t)l * (u32)P[PT_LAYER] + seg_of(P, kind).off) * FRAG_BYTES, P, kind, l, wid, nwarp, lane);
     }
 }

@@ -46,11 +46,12 @@ def shape_of(W, heads=None):
 
 class VestaGPT2:
     def __init__(self, hf, dtype='f16', batch=1, tmax=1024, feedback=True, program=None, timing=False,
-                 blocks_per_sm=None, per_sequence_t=False, device=None):
+                 blocks_per_sm=None, per_sequence_t=False, device=None, prompt_len=0, slab_tiles=None):
         """program: path of a .vst file; default: the step program for the sizes of the weights
         (identical to programs/gpt2.vst for GPT-2 small). per_sequence_t: every sequence keeps its
         own position t[b] (ragged batches); default one position for the whole batch as in the
-        reference."""
+        reference. prompt_len > 0 adds the buffers `prompt` (batch, prompt_len) and `plen` (batch,): the
+        kernel then feeds prompt[b][t+1] while t + 1 < plen[b] and its own choice afterwards."""
         tdt = TORCH_DT[dtype]
         dev = torch.device('cuda', torch.cuda.current_device() if device is None else device)
         self.device = dev
@@ -63,9 +64,12 @@ class VestaGPT2:
         self.x = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.t = torch.zeros(batch if per_sequence_t else 1, dtype=torch.int32, device=dev)
         R = {'x': self.x, 't': self.t, **self.W, 'keys': self.keys, 'vals': self.vals}
+        if prompt_len:
+            self.prompt = torch.zeros(batch, prompt_len, dtype=torch.int32, device=dev)
+            self.plen = torch.zeros(batch, dtype=torch.int32, device=dev)
         names = {torch.int32: 'i32', torch.float16: 'f16', torch.float32: 'f32'}
         spec = {n: (((batch,) if per_sequence_t else ()), 'i32') if n == 't' else (tuple(v.shape), names[v.dtype])
-                for n, v in R.items()}
+                for n, v in R.items() if n not in ('prompt', 'plen')}
         if program is None:
             text = decode_program(sh)
         else:
@@ -74,8 +78,10 @@ class VestaGPT2:
         per_token = ('x', 'keys', 'vals') + (('t',) if per_sequence_t else ())
         self.low = lower(text, spec, axis_max={'s': tmax}, batch=batch, per_token=per_token,
                          outputs=('logit', 'next'), feedback={'x': 'next', 't': 1} if feedback else None,
-                         timing=timing, grid=sms)
+                         timing=timing, grid=sms, prompt_len=prompt_len if feedback else 0, slab_tiles=slab_tiles)
         self.k = Kernel(self.low, device=dev.index, blocks_per_sm=blocks_per_sm)
+        if prompt_len and feedback:
+            R = dict(R, prompt=self.prompt, plen=self.plen)
         self.k.bind(R)
         self.weight_bytes = sum(v.numel() * v.element_size() for n, v in self.W.items() if n != 'wpe') \
             + sh.D * self.W['wpe'].element_size()

@@ -290,11 +290,15 @@ def place_step(dims, grid):
 
 # ------------------------------------------------------------------ assembly
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
-          grid=DEFAULT_SMS, act_lo=None):
+          grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None):
     """See the module docstring. `res`: name -> (shape, dtype) as the kernel sees them (batched
     where per-token; scalars have shape ()). `axis_max`: bound of the run-time position axis,
     e.g. {'s': tmax}. `grid`: CTAs to place for (one per SM). 't' may be listed in per_token, in
-    which case every sequence has its own position (shape (batch,))."""
+    which case every sequence has its own position (shape (batch,)); a negative position marks a
+    sequence that has not started yet. `prompt_len` > 0 adds two kernel parameters after the
+    residues, `prompt` (batch, prompt_len) i32 and `plen` (batch,) i32: the feedback then feeds
+    prompt[b][t+1] instead of the model's own choice while t + 1 < plen[b], so that prompts (ragged,
+    or the reference's tokens for teacher forcing) are consumed without a host round trip."""
     env, ext, recv = recognise(text)
     dims = _dims(env, ext)
     D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
@@ -343,11 +347,13 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         if o not in (env['$logit'], env['$next']):
             raise NotImplementedError(f'output {o}: only {env["$logit"]} and {env["$next"]} are kept for the host')
 
-    NB = (B + 7) // 8
-    if NB > 4:
-        raise NotImplementedError('batch above 32 rows per launch is not placed yet')
+    # rows per slab (8 per batch tile): the operand tiles of a slab live in shared memory next to the
+    # weight ring, at most ~100 KB of them; larger batches run the contraction phases slab by slab
+    NB = min((B + 7) // 8, max(1, (100 * 1024) // ((D // 16) * 512)))
+    if slab_tiles:
+        NB = min(NB, int(slab_tiles))
     if act_lo is None:
-        act_lo = NB <= 2
+        act_lo = True
     rec, tiles, notes = place_step(dims, grid)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
@@ -364,8 +370,9 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     KT_D = D // 16
-    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + B * (D + 8) * 4 + NW * NB * 512 + (3 * D + WN_MAX * 16) * 2 + 16
-             + NW * (E + 2) * 4 + 8 + B * NW * 8 + B * 4 + B * 8 + 16 + 16)
+    SBr = 8 * NB
+    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + 8 * (D + 8) * 4 + NW * NB * 512 + (3 * D + WN_MAX * 16) * 2 + 16
+             + NW * (E + 2) * 4 + 8 + SBr * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
     budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
     nslot = (budget - fixed - 1024) // (CHUNK_TILES * 512 + 16)
     if nslot < 2:
@@ -380,7 +387,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
-                V_TIMING=int(timing), V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
+                V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
                 V_MAXGRID=grid, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch)
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
@@ -390,6 +397,9 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         em = name in emitted
         params.append((name, dt, em))
         sig.append(f'{"" if em else "const "}{CTYPE[dt]}* __restrict__ R_{name}')
+    if prompt_len and fb:
+        params += [('prompt', 'i32', False), ('plen', 'i32', False)]
+        sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
     R = {k: 'R_' + v for k, v in roles.items()}
     step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
                                 'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
@@ -401,6 +411,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         fill.append(f'a.x_out = {R["x"]}; a.t_out = {R["t"]};')
     else:
         fill.append('a.x_out = 0; a.t_out = 0;')
+    fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
     fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT;')
     pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
     pack_params = [roles[k] for k in pack_roles]
