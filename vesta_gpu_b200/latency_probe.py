@@ -89,9 +89,10 @@ extern "C" __global__ void micro(float* out, u32* bar, int iters, int variant) {
     if (cta == 0 && tid == 0) out[0] = (float)(t1 - t0) / iters;
 }
 '''
+
+
 def main():
-    
-        L = lib(); torch.zeros(1, device='cuda'); ok(L.vesta_init(0))
+    L = lib(); torch.zeros(1, device='cuda'); ok(L.vesta_init(0))
     cubin = compile_cubin(SRC, cache=False)
     buf = ctypes.create_string_buffer(cubin, len(cubin))
     mod, fn = ctypes.c_void_p(), ctypes.c_void_p()
