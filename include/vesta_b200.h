@@ -63,6 +63,30 @@ int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dyna
 int vesta_step_run(void* bound, void* stream, int steps);
 void vesta_step_release(void* bound);
 
+/* No counterpart in the reference: one decode step for callers that must not allocate device
+ * memory (a plugin inside a host that owns all of it, a serving loop with a frozen memory plan).
+ * Launches the compiled step function `function` (from vesta_module_get_function) exactly as
+ * vesta_launch_cooperative would, but with the kernel's work space (fp32 scratch, counters, timing
+ * sums, normally allocated by the caller) in a fixed array inside the library's device image,
+ * vesta_static_scratch_bytes() bytes (4 MiB) per GPU for the life of the process. The caller passes
+ * the residues (inputs, the KV cache), the packed weights and the plan table it already owns, the
+ * sizes the lowering reported (scratch_floats, counters) and where the logits and next lie in the
+ * scratch; the results are copied to logits_out / next_out (device or pinned host memory) on
+ * `stream`. Allocates nothing; a step that needs more scratch than the array holds is refused with
+ * an error (vesta_static_last_error) and nothing is launched. The array is shared by every call and
+ * keeps the last call's contents: each call clears the range it uses first, and calls that overlap
+ * on the GPU race on it. The first call on a device resolves the array's address and should be
+ * made before any stream capture. */
+size_t vesta_static_scratch_bytes(void);
+const char* vesta_static_last_error(void);
+int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
+                      int n_residues, const unsigned long long* residue_pointers,
+                      unsigned long long packed_weights, unsigned long long plan_table,
+                      size_t scratch_floats, size_t counters,
+                      size_t logit_offset, size_t logit_count, float* logits_out,
+                      size_t next_offset, size_t next_count, float* next_out,
+                      void* stream);
+
 #ifdef __cplusplus
 }
 #endif

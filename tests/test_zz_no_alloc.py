@@ -1,0 +1,82 @@
+"""vesta_step_static: the decode step for callers that may not allocate device memory.
+
+Some hosts of this library own every byte of device memory themselves (a plugin inside another
+runtime, a serving process that froze its memory plan after start-up), so cudaMalloc, or
+any helper that allocates on their behalf, is off the table for them. For those callers the
+library keeps the step kernel's work space in a fixed 4 MiB array of its own. This test drives
+that entry point through the C ABI next to the ordinary path (whose work space PyTorch allocates)
+on the same inputs, two steps in a row, and expects the same logits and tokens.
+
+Collected last on purpose: the entry point shares one array per GPU across all callers, and the
+test must hold both in a fresh process and after everything else has run.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TIGHT
+
+pytestmark = pytest.mark.gpu
+
+
+def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=None):
+    low = k.lowered
+    ptrs = [residues[name].data_ptr() for name, _, _ in low.params]
+    arr = (ctypes.c_ulonglong * len(ptrs))(*ptrs)
+    lo, _, lshape = low.scratch['logit']
+    no, _, nshape = low.scratch['next']
+    return lib.vesta_step_static(k.fn, k.grid, k.block, k.smem, len(ptrs), arr,
+                                 ctypes.c_ulonglong(k.WP.data_ptr()), ctypes.c_ulonglong(k.PT.data_ptr()),
+                                 ctypes.c_size_t(low.scratch_floats if scratch_floats is None else scratch_floats),
+                                 ctypes.c_size_t(low.counters),
+                                 ctypes.c_size_t(lo), ctypes.c_size_t(int(np.prod(lshape))), ctypes.c_void_p(logits_out.data_ptr()),
+                                 ctypes.c_size_t(no), ctypes.c_size_t(int(np.prod(nshape))), ctypes.c_void_p(next_out.data_ptr()),
+                                 ctypes.c_void_p(stream))
+
+
+def test_static_scratch_step_matches_the_allocating_path():
+    from vesta_gpu_b200 import launch
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import SynthGPT2
+    from vesta_gpu_b200.gpt2 import VestaGPT2
+    lib = launch.lib()
+    lib.vesta_step_static.restype = ctypes.c_int
+    lib.vesta_static_last_error.restype = ctypes.c_char_p
+    lib.vesta_static_scratch_bytes.restype = ctypes.c_size_t
+    assert lib.vesta_static_scratch_bytes() == 4 << 20
+
+    B, tmax = 3, 16
+    m = VestaGPT2(SynthGPT2(TINY3, 11, 'rich'), batch=B, tmax=tmax)
+    m.reset()
+    start = torch.tensor([5, 17, 300], dtype=torch.int32, device='cuda')
+    m.x.copy_(start)
+
+    # a second set of per-sequence state for the no-allocation path: same weights, own x, t and KV cache
+    mine = dict(m.k.keep)
+    mine['x'] = start.clone()
+    mine['t'] = torch.zeros_like(m.t)
+    mine['keys'] = torch.zeros_like(m.keys)
+    mine['vals'] = torch.zeros_like(m.vals)
+    logits = torch.empty(B, TINY3.N, dtype=torch.float32, device='cuda')
+    nxt = torch.empty(B, dtype=torch.float32, device='cuda')
+    stream = torch.cuda.current_stream().cuda_stream
+
+    for step in range(2):                       # two calls in a row: the second one finds the first one's leftovers
+        m.step()
+        rc = static_step(lib, m.k, mine, stream, logits, nxt)
+        assert rc == 0, lib.vesta_static_last_error()
+        torch.cuda.synchronize()
+        assert torch.allclose(logits, m.logits(), atol=TIGHT, rtol=0), step
+        assert torch.equal(nxt, m.next()), step
+        assert torch.equal(mine['x'], m.x) and torch.equal(mine['t'], m.t), step
+        assert torch.equal(mine['keys'], m.keys) or torch.allclose(mine['keys'].float(), m.keys.float(), atol=2e-3)
+    m.k.check()
+
+    # a step that needs more work space than the library holds is refused, with a message, and launches nothing
+    before = logits.clone()
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, scratch_floats=(4 << 20))
+    assert rc != 0 and b'static scratch holds' in lib.vesta_static_last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(before, logits)
