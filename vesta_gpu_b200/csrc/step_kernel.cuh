@@ -40,7 +40,8 @@ typedef unsigned short u16;
 #define JT_D (V_D / 16)
 #define FRAG_BYTES 512
 #define WN_MAX 4                      // widest NARROW placement (output tiles per CTA)
-#define WG NW                         // output tiles per WIDE group: one per consumer warp
+#define TPW 2                         // output tiles a warp owns in a WIDE group
+#define WG (TPW * NW)                  // output tiles per WIDE group
 #define G4 (V_D / 4)                  // float4 groups per activation row
 
 // bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter
@@ -276,47 +277,78 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
 // ---------------------------------------------------------------------------------------------
 // one group of a contraction: `rows` x `width` tiles from the stream against the operand tiles at act.
 // NARROW: warp w works on output tile w % width and on every cnt-th fold tile (cnt = warps that share
-// the output tile); WIDE: warp w < width owns output tile w over all rows. In both cases the warp's
-// tiles are those with index w + k * stride in the group's row-major order. acc: this warp's sums.
+// the output tile); its tiles are those with index w + k * cnt * width in the group's row-major
+// order; sums in acc[0]. WIDE: warp w owns output tiles w and w + NW (where < width) over all rows;
+// sums in acc[0] and acc[1].
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wide, const unsigned char* act, float (&acc)[V_NB][4]) {
-    float lo[V_NB][4];
+__device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wide, const unsigned char* act, float (&acc)[TPW][V_NB][4]) {
+    float lo[TPW][V_NB][4];
 #pragma unroll
-    for (int nb = 0; nb < V_NB; nb++)
+    for (int t = 0; t < TPW; t++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) { acc[nb][i] = 0.f; lo[nb][i] = 0.f; }
-    const int cnt = wide ? 1 : (NW - (c.warp % width) + width - 1) / width;    // rows advance by cnt
-    const int stride = cnt * width;
-    const bool active = wide ? (c.warp < width) : (c.warp / width < rows);
-    int f = active ? c.warp : 0x3fffffff;                                        // next tile of this warp
-    int row = wide ? 0 : c.warp / width;
+        for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) { acc[t][nb][i] = 0.f; lo[t][nb][i] = 0.f; }
     const int rpc = V_CH / width, per = rpc * width, total = rows * width;
+    if (wide) {
+        const bool own0 = c.warp < width, own1 = c.warp + NW < width;
+        int row = 0;
 #pragma unroll 1
-    for (int base = 0; base < total; base += per) {
-        const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-        wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
-        const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES;
-        const int lim = c.dead ? 0 : min(base + per, total);
-#pragma unroll 1
-        for (; f < lim; f += stride, row += cnt) {
-            const uint4 a = lds128(tiles + ((size_t)f * 32 + c.lane) * 16);
+        for (int base = 0; base < total; base += per) {
+            const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+            wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) + (size_t)c.lane * 16;
+            const int nr = c.dead ? 0 : min(rpc, rows - row);
+#pragma unroll 2
+            for (int r = 0; r < nr; r++) {
+                const unsigned char* tp = tiles + (size_t)(r * width + c.warp) * FRAG_BYTES;
+                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
+                if (own0) a0 = lds128(tp);
+                if (own1) a1 = lds128(tp + NW * FRAG_BYTES);
 #pragma unroll
-            for (int nb = 0; nb < V_NB; nb++) {
-                const uint4 b = lds128(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * 16);
-                mma16816(acc[nb], a, b.x, b.y);
-#if V_ACT_LO
-                mma16816(lo[nb], a, b.z, b.w);
-#endif
+                for (int nb = 0; nb < V_NB; nb++) {
+                    const uint4 b = lds128(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * 16);
+                    if (own0) { mma16816(acc[0][nb], a0, b.x, b.y); if (V_ACT_LO) mma16816(lo[0][nb], a0, b.z, b.w); }
+                    if (own1) { mma16816(acc[1][nb], a1, b.x, b.y); if (V_ACT_LO) mma16816(lo[1][nb], a1, b.z, b.w); }
+                }
             }
+            row += rpc;
+            __syncwarp();
+            if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+            c.chunk++;
         }
-        __syncwarp();
-        if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
-        c.chunk++;
+    } else {
+        const int cnt = (NW - (c.warp % width) + width - 1) / width;             // rows advance by cnt
+        const int stride = cnt * width;
+        int f = (c.warp / width < rows) ? c.warp : 0x3fffffff;                   // next tile of this warp
+        int row = c.warp / width;
+#pragma unroll 1
+        for (int base = 0; base < total; base += per) {
+            const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+            wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES + (size_t)c.lane * 16;
+            const int lim = c.dead ? 0 : min(base + per, total);
+#pragma unroll 2
+            for (; f < lim; f += stride, row += cnt) {
+                const uint4 a = lds128(tiles + (size_t)f * FRAG_BYTES);
+#pragma unroll
+                for (int nb = 0; nb < V_NB; nb++) {
+                    const uint4 b = lds128(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * 16);
+                    mma16816(acc[0][nb], a, b.x, b.y);
+                    if (V_ACT_LO) mma16816(lo[0][nb], a, b.z, b.w);
+                }
+            }
+            __syncwarp();
+            if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+            c.chunk++;
+        }
     }
 #pragma unroll
-    for (int nb = 0; nb < V_NB; nb++)
+    for (int t = 0; t < TPW; t++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) acc[nb][i] += lo[nb][i];
+        for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) acc[t][nb][i] += lo[t][nb][i];
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -387,13 +419,13 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
         for (int b = c.warp; b < nr; b += NW) {
             const float4* row = reinterpret_cast<const float4*>(zs + b * ZS_STRIDE);
             float s = 0.f;
-#pragma unroll 2
+#pragma unroll 4
             for (int g = c.lane; g < G4; g += 32) { const float4 v = row[g]; s += (v.x + v.y) + (v.z + v.w); }
 #pragma unroll
             for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
             const float mean = s * (1.0f / V_D);
             float q = 0.f;
-#pragma unroll 2
+#pragma unroll 4
             for (int g = c.lane; g < G4; g += 32) {
                 const float4 v = row[g];
                 const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
@@ -405,7 +437,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
         }
         cons_sync();
         TRACE(41);
-#pragma unroll 1
+#pragma unroll 2
         for (int kt = c.warp; kt < KT_D; kt += NW) {
             const int k = kt * 16 + 2 * t;
             uint4 out = make_uint4(0, 0, 0, 0);
@@ -696,13 +728,13 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #pragma unroll 1
                 for (int j = 0; j < sg.nj; j += (sg.wide ? WG : WN_MAX * 4)) {
                     const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
-                    float acc[V_NB][4];
+                    float acc[TPW][V_NB][4];
                     gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
                     if (!sg.wide) {
                         // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
 #pragma unroll
                         for (int nb = 0; nb < V_NB; nb++)
-                            *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[nb][0], acc[nb][1], acc[nb][2], acc[nb][3]);
+                            *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[0][nb][0], acc[0][nb][1], acc[0][nb][2], acc[0][nb][3]);
                         cons_sync();
 #pragma unroll 1
                         for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
@@ -730,22 +762,26 @@ __device__ __forceinline__ void step_body(const Args& a) {
                             }
                         }
                         cons_sync();
-                    } else if (c.warp < width) {
-                        const int jt = ((kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0) + j + c.warp;
+                    } else {
                         float* zt = (kind == PH_PROJ) ? z1 : z2;
 #pragma unroll
-                        for (int nb = 0; nb < V_NB; nb++)
+                        for (int tw = 0; tw < TPW; tw++) {
+                            if (c.warp + tw * NW >= width) continue;
+                            const int jt = ((kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0) + j + c.warp + tw * NW;
 #pragma unroll
-                            for (int i = 0; i < 4; i++) {
-                                const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (c.lane & 3) * 2 + (i & 1), b = row0 + rb;
-                                if (kind != PH_LOGITS) {
-                                    if (rb < nrows) red_add(zt + (size_t)b * V_D + jx, acc[nb][i]);
-                                } else if (rb < nrows && jx < V_N) {
-                                    logit[(size_t)b * V_N + jx] = acc[nb][i];
-                                    const u64 k = best_key(acc[nb][i], (u32)jx);
-                                    if (k > best[nb][i & 1]) best[nb][i & 1] = k;
+                            for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+                                for (int i = 0; i < 4; i++) {
+                                    const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (c.lane & 3) * 2 + (i & 1), b = row0 + rb;
+                                    if (kind != PH_LOGITS) {
+                                        if (rb < nrows) red_add(zt + (size_t)b * V_D + jx, acc[tw][nb][i]);
+                                    } else if (rb < nrows && jx < V_N) {
+                                        logit[(size_t)b * V_N + jx] = acc[tw][nb][i];
+                                        const u64 k = best_key(acc[tw][nb][i], (u32)jx);
+                                        if (k > best[nb][i & 1]) best[nb][i & 1] = k;
+                                    }
                                 }
-                            }
+                        }
                     }
                 }
                 if (kind == PH_LOGITS) {

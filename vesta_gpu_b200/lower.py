@@ -33,7 +33,7 @@ KERNEL_TEXT = Path(__file__).resolve().parent / 'csrc' / 'step_kernel.cuh'
 
 CTYPE = {'f32': 'float', 'f16': 'unsigned short', 'i32': 'int'}
 NW = 8                 # consumer warps per CTA (one more warp streams the weights)
-WG = NW                # output tiles per WIDE group: one per consumer warp
+WG = 2 * NW            # output tiles per WIDE group: two per consumer warp
 CHUNK_TILES = 32       # 16 KB ring slots
 WN_MAX = 4             # widest NARROW placement
 PT_STRIDE = 16
