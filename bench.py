@@ -48,6 +48,9 @@ WORKLOADS = {
     'tiny': dict(shape='tiny3', batch=2, prompt=8, gen=16),
 }
 METRIC, UNIT = 'decode tokens/s', 'tokens/s'
+# DRAM bytes (read + write) of one vesta_step launch from the ncu capture summarised in
+# profiles/vesta_step_gpt2_small_b8.md (context ~135); null for workloads that were not captured
+NCU_TRAFFIC = {'cfg2': 255.1e6}
 
 
 def peaks():
@@ -288,7 +291,7 @@ def main():
                 clocks=clocks, gpu_launches=K,
                 e2e=dict(value=B * world * K / e2e_med, unit=UNIT, h2d_bytes_per_step=B * 4, d2h_bytes_per_step=B * 4,
                          tokens_match_device_loop=e2e_ok),
-                roofline=dict(bound='hbm', achieved=achieved, peak=peak, unit='GB/s', frac=achieved / peak, traffic=None,
+                roofline=dict(bound='hbm', achieved=achieved, peak=peak, unit='GB/s', frac=achieved / peak, traffic=NCU_TRAFFIC.get(args.workload),
                               peak_source=peak_src, bytes_per_launch=bytes_per_step, kernel='vesta_step',
                               frac_of_8tbs=achieved / 8000.0))
     if not args.no_cpu_baseline and world == 1:
