@@ -151,7 +151,7 @@ def test_per_sequence_positions():
 
 def test_slabs_and_device_side_prompts():
     low = lower_for(GPT2_SMALL, 64, 1024)
-    assert low.dims['NB'] == 4 and '#define V_NB 4' in low.src           # 32 rows per slab, two slabs
+    assert low.dims['NB'] == 2 and '#define V_NB 2' in low.src           # 16 rows per slab, four slabs
     assert low.shared_bytes <= 227 * 1024
     low = lower_for(TINY, 20, 16, slab_tiles=1)
     assert low.dims['NB'] == 1

@@ -147,7 +147,8 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 // shared memory
 // ---------------------------------------------------------------------------------------------
 #define SM_RING 0
-#define SM_ACT (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)            // B operands of the current contraction
+#define SM_KV (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)             // K/V tiles of the attention phase
+#define SM_ACT (SM_KV + 2 * NW * 16 * 256)                        // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
 #define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // eight fp32 rows staged for LayerNorm
 #define SM_RED (SM_ZS + 8 * (V_D + 8) * 4)                        // NARROW partial sums, one tile per warp
@@ -495,45 +496,108 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 }
 
 // ---------------------------------------------------------------------------------------------
-// attention of one (sequence, head) over positions [s_lo, n): online softmax, K and V from the cache;
-// result: (running max, sum, unnormalised o[V_E]) at out. 8 lanes per position (16 B each of the
-// 128 B row), 4 positions per warp per round.
+// attention: this CTA's work items are (sequence, head, chunk of the positions); an item is processed
+// in tiles of KV_POS positions whose K and V rows (128 B each per head) are copied into shared memory
+// with cp.async, two tiles ahead of the arithmetic, so that the cache streams while the softmax runs.
+// The first tile is requested before the grid barrier that ends the QKV phase; the row of the current
+// position (written during that phase by another CTA) is fetched after the barrier.
+// Arithmetic: 8 lanes per position (8 dims each), 4 positions per warp at a time, online softmax in
+// registers; result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
-#define ATT_UNROLL 4
-__device__ __forceinline__ void attention_item(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
-                                               float* __restrict__ out, int b, int h, int l, int s_lo, int n) {
-    const int li = c.lane & 7, grp = c.warp * 4 + (c.lane >> 3);
-    const int NG = NW * 4;
-    float q[8];
-    {
-        const float* qp = qbuf + (size_t)b * V_D + h * V_E + li * 8;
-        const float4 q0 = __ldcg(reinterpret_cast<const float4*>(qp)), q1 = __ldcg(reinterpret_cast<const float4*>(qp + 4));
-        const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
-        q[0] = q0.x * sc; q[1] = q0.y * sc; q[2] = q0.z * sc; q[3] = q0.w * sc; q[4] = q1.x * sc; q[5] = q1.y * sc; q[6] = q1.z * sc; q[7] = q1.w * sc;
+#define KV_POS (NW * 16)                         // positions per tile: four per 8-lane group
+#define KV_STAGE_BYTES (KV_POS * 256)            // K rows then V rows
+#define KV_STAGES 2
+
+struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
+
+__device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int ncta) {
+    while (a.it < V_B * V_H * V_NCH) {
+        const int ch = a.it % V_NCH, bh = a.it / V_NCH;
+        a.b = bh / V_H; a.h = bh - a.b * V_H;
+        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + V_NCH - 1) / V_NCH;
+        a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
+        return;
     }
-    const size_t row0 = ((size_t)(b * V_L + l) * V_TMAX) * V_D + (size_t)h * V_E + li * 8;
-    float m = -3.0e38f, den = 0.f, acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] = 0.f;
-    // the trip count is the same for every lane of the warp (the shuffles below need all 32 lanes)
+}
+__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < V_B * V_H * V_NCH; }
+__device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int ncta) {
+    a.s += KV_POS;
+    if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
+}
+
+// request the rows [a.s, min(a.hi, a.s + KV_POS)) of the item into a stage, except position `skip`
+__device__ __forceinline__ void att_fetch(Ctx& c, const AttIter& a, const u16* __restrict__ keys, const u16* __restrict__ vals, int l,
+                                          unsigned char* stage, int skip) {
+    const int cnt = min(KV_POS, a.hi - a.s);
+    const size_t row0 = ((size_t)(a.b * V_L + l) * V_TMAX) * V_D + (size_t)a.h * V_E;
 #pragma unroll 1
-    for (int base = s_lo; base < n; base += NG * ATT_UNROLL) {
-        uint4 kk[ATT_UNROLL], vv[ATT_UNROLL];
-#pragma unroll
-        for (int u = 0; u < ATT_UNROLL; u++) {
-            const int s = min(base + grp + u * NG, n - 1);          // n >= 1 inside the loop
-            kk[u] = __ldcg(reinterpret_cast<const uint4*>(keys + row0 + (size_t)s * V_D));
-            vv[u] = __ldcg(reinterpret_cast<const uint4*>(vals + row0 + (size_t)s * V_D));
+    for (int i = c.tid; i < cnt * 16; i += NCONS) {
+        const int pos = i >> 4, piece = i & 15;
+        if (a.s + pos == skip) continue;
+        const u16* src = ((piece & 8) ? vals : keys) + row0 + (size_t)(a.s + pos) * V_D + (piece & 7) * 8;
+        cp16(stage + (piece >> 3) * (KV_POS * 128) + pos * 128 + (piece & 7) * 16, src);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+// the first tile of this CTA, before the barrier: everything but the row of the current position
+__device__ __forceinline__ void attention_prefetch(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, int l, const int* s_pos) {
+    AttIter a; a.it = c.cta;
+    att_load_item(a, s_pos, c.ncta);
+    if (att_valid(a)) att_fetch(c, a, keys, vals, l, c.smem + SM_KV, s_pos[a.b]);
+}
+
+__device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
+                                                float* __restrict__ part, int l, const int* s_pos) {
+    const int li = c.lane & 7, grp = c.warp * 4 + (c.lane >> 3);
+    AttIter cur, pf;
+    cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
+    if (!att_valid(cur)) return;
+    pf = cur;
+    // the row that was left out before the barrier
+    {
+        const int t = s_pos[cur.b];
+        if (t >= cur.s && t < min(cur.hi, cur.s + KV_POS) && c.tid < 16) {
+            const size_t row0 = ((size_t)(cur.b * V_L + l) * V_TMAX) * V_D + (size_t)cur.h * V_E;
+            const u16* src = ((c.tid & 8) ? vals : keys) + row0 + (size_t)t * V_D + (c.tid & 7) * 8;
+            cp16(c.smem + SM_KV + (c.tid >> 3) * (KV_POS * 128) + (t - cur.s) * 128 + (c.tid & 7) * 16, src);
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    att_advance(pf, s_pos, c.ncta);
+    if (att_valid(pf)) att_fetch(c, pf, keys, vals, l, c.smem + SM_KV + KV_STAGE_BYTES, -1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+
+    int stage = 0;
+    float q[8], m = -3.0e38f, den = 0.f, acc[8];
+    bool fresh = true;                               // the next tile starts an item
+#pragma unroll 1
+    while (att_valid(cur)) {
+        if (fresh) {
+            const float* qp = qbuf + (size_t)cur.b * V_D + cur.h * V_E + li * 8;
+            const float4 q0 = __ldcg(reinterpret_cast<const float4*>(qp)), q1 = __ldcg(reinterpret_cast<const float4*>(qp + 4));
+            const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
+            q[0] = q0.x * sc; q[1] = q0.y * sc; q[2] = q0.z * sc; q[3] = q0.w * sc; q[4] = q1.x * sc; q[5] = q1.y * sc; q[6] = q1.z * sc; q[7] = q1.w * sc;
+            m = -3.0e38f; den = 0.f;
 #pragma unroll
-        for (int u = 0; u < ATT_UNROLL; u++) {
-            const uint4 k4 = kk[u], v4 = vv[u];
+            for (int i = 0; i < 8; i++) acc[i] = 0.f;
+            fresh = false;
+        }
+        asm volatile("cp.async.wait_group 1;" ::: "memory");       // this tile has landed; the next one may be in flight
+        cons_sync();
+        const unsigned char* kv = c.smem + SM_KV + stage * KV_STAGE_BYTES;
+        const int cnt = min(KV_POS, cur.hi - cur.s);
+        // the trip count is the same for every lane of the warp (the shuffles need all 32 lanes)
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int pos = grp + u * (NW * 4);
+            const uint4 k4 = lds128(kv + pos * 128 + li * 16), v4 = lds128(kv + KV_POS * 128 + pos * 128 + li * 16);
             float sc = q[0] * h_lo(k4.x) + q[1] * h_hi(k4.x) + q[2] * h_lo(k4.y) + q[3] * h_hi(k4.y) +
                        q[4] * h_lo(k4.z) + q[5] * h_hi(k4.z) + q[6] * h_lo(k4.w) + q[7] * h_hi(k4.w);
             sc += __shfl_xor_sync(0xffffffffu, sc, 1);
             sc += __shfl_xor_sync(0xffffffffu, sc, 2);
             sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-            if (base + grp + u * NG < n) {
+            if (pos < cnt) {
                 if (!V_SCALE_IS_POW2) sc = sc / V_SCALE;
                 const float mn = fmaxf(m, sc);
                 const float corr = fast_exp(m - mn), p = fast_exp(sc - mn);
@@ -545,42 +609,54 @@ __device__ __forceinline__ void attention_item(Ctx& c, const u16* __restrict__ k
                 m = mn;
             }
         }
-    }
-    // merge the 4 position groups of the warp (lanes li, li+8, li+16, li+24 hold the same dims)
+        const bool last = cur.s + KV_POS >= cur.hi;
+        float* out = part + (size_t)cur.it * PART_STRIDE;
+        if (last) {
+            // merge the 4 position groups of the warp (lanes li, li+8, li+16, li+24 hold the same dims)
 #pragma unroll
-    for (int x = 8; x <= 16; x <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m, x), d2 = __shfl_xor_sync(0xffffffffu, den, x);
-        const float mn = fmaxf(m, m2);
-        const float c1 = fast_exp(m - mn), c2 = fast_exp(m2 - mn);
-        den = den * c1 + d2 * c2;
+            for (int x = 8; x <= 16; x <<= 1) {
+                const float m2 = __shfl_xor_sync(0xffffffffu, m, x), d2 = __shfl_xor_sync(0xffffffffu, den, x);
+                const float mn = fmaxf(m, m2);
+                const float c1 = fast_exp(m - mn), c2 = fast_exp(m2 - mn);
+                den = den * c1 + d2 * c2;
 #pragma unroll
-        for (int i = 0; i < 8; i++) acc[i] = acc[i] * c1 + __shfl_xor_sync(0xffffffffu, acc[i], x) * c2;
-        m = mn;
-    }
-    // merge the warps through shared memory: per warp (m, den, acc[V_E])
-    float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
-    if (c.lane < 8) {
-        float* w = ms + c.warp * (V_E + 2);
-        if (c.lane == 0) { w[0] = m; w[1] = den; }
+                for (int i = 0; i < 8; i++) acc[i] = acc[i] * c1 + __shfl_xor_sync(0xffffffffu, acc[i], x) * c2;
+                m = mn;
+            }
+            // merge the warps through shared memory: per warp (m, den, acc[V_E])
+            float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
+            if (c.lane < 8) {
+                float* w = ms + c.warp * (V_E + 2);
+                if (c.lane == 0) { w[0] = m; w[1] = den; }
 #pragma unroll
-        for (int i = 0; i < 8; i++) w[2 + li * 8 + i] = acc[i];
-    }
-    cons_sync();
-    if (c.tid < V_E) {
-        float M = -3.0e38f;
-#pragma unroll 1
-        for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
-        float num = 0.f, dd = 0.f;
-#pragma unroll 1
-        for (int w = 0; w < NW; w++) {
-            const float sc = fast_exp(ms[w * (V_E + 2)] - M);
-            dd += ms[w * (V_E + 2) + 1] * sc;
-            num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
+                for (int i = 0; i < 8; i++) w[2 + li * 8 + i] = acc[i];
+            }
         }
-        out[2 + c.tid] = num;
-        if (c.tid == 0) { out[0] = M; out[1] = dd; }
+        cons_sync();                                   // everybody is done with this stage (and ms is written)
+        if (last && c.tid < V_E) {
+            const float* ms = reinterpret_cast<const float*>(c.smem + SM_MISC + MISC_ATT);
+            float M = -3.0e38f;
+#pragma unroll 1
+            for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
+            float num = 0.f, dd = 0.f;
+#pragma unroll 1
+            for (int w = 0; w < NW; w++) {
+                const float sc = fast_exp(ms[w * (V_E + 2)] - M);
+                dd += ms[w * (V_E + 2) + 1] * sc;
+                num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
+            }
+            out[2 + c.tid] = num;
+            if (c.tid == 0) { out[0] = M; out[1] = dd; }
+        }
+        fresh = last;
+        att_advance(cur, s_pos, c.ncta);
+        att_advance(pf, s_pos, c.ncta);
+        if (att_valid(pf)) att_fetch(c, pf, keys, vals, l, c.smem + SM_KV + stage * KV_STAGE_BYTES, -1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        stage ^= 1;
     }
-    cons_sync();
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    cons_sync();                                       // ms may be reused by the next phase
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -690,13 +766,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         TRACE(1 + first);
 
         if (first == PH_ATT) {
-            // one (sequence, head, chunk of positions) at a time, partial results to scratch
-#pragma unroll 1
-            for (int it = c.cta; it < V_B * V_H * V_NCH; it += c.ncta) {
-                const int ch = it % V_NCH, bh = it / V_NCH, b = bh / V_H, h = bh - b * V_H;
-                const int n = s_pos[b] + 1, cs = (max(n, 1) + V_NCH - 1) / V_NCH;
-                attention_item(c, a.keys, a.vals, qbuf, part + (size_t)it * PART_STRIDE, b, h, l, ch * cs, min(n, (ch + 1) * cs));
-            }
+            attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos);
         } else {
             // LN1 phase clears z2 (the MLP adds into it two barriers later); LN2 phase clears zin for the next layer
             float* clr = (first == PH_QKV) ? z2 : (first == PH_FC) ? zin : (float*)0;
@@ -825,6 +895,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
             else
                 fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
         }
+        if (first == PH_QKV) attention_prefetch(c, a.keys, a.vals, l, s_pos);
         TRACE(30 + first);
         phase_wait(c);
         TICK(3 + 2 * (ph - l * PH_PER_LAYER));

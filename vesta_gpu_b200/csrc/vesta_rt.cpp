@@ -39,6 +39,7 @@ struct Driver {
                                   unsigned, CUstream, void**) = nullptr;
     CUresult (*Launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                        CUstream, void**, void**) = nullptr;
+    CUresult (*LaunchEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
 };
 Driver g_cu;
 
@@ -59,7 +60,8 @@ int driver() {
               sym(lib, "cuModuleLoadData", d.ModuleLoadData) && sym(lib, "cuModuleUnload", d.ModuleUnload) &&
               sym(lib, "cuModuleGetFunction", d.ModuleGetFunction) && sym(lib, "cuFuncSetAttribute", d.FuncSetAttribute) &&
               sym(lib, "cuOccupancyMaxActiveBlocksPerMultiprocessor", d.Occupancy) &&
-              sym(lib, "cuLaunchCooperativeKernel", d.LaunchCooperative) && sym(lib, "cuLaunchKernel", d.Launch);
+              sym(lib, "cuLaunchCooperativeKernel", d.LaunchCooperative) && sym(lib, "cuLaunchKernel", d.Launch) &&
+              sym(lib, "cuLaunchKernelEx", d.LaunchEx);
     if (!ok) return fail(-1, "libcuda.so.1 lacks a required driver entry point");
     d.lib = lib;
     g_cu = d;
@@ -239,6 +241,29 @@ int vesta_launch(void* function, unsigned grid, unsigned block, unsigned dynamic
     if (int e = driver()) return e;
     return cu(g_cu.Launch((CUfunction)function, grid, 1, 1, block, 1, 1, dynamic_smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
+}
+
+int vesta_launch_cluster(void* function, unsigned grid, unsigned block, unsigned dynamic_smem, unsigned cluster,
+                         int cooperative, void* stream, void** args) {
+    if (int e = driver()) return e;
+    if (cluster > 8) {
+        if (int e = cu(g_cu.FuncSetAttribute((CUfunction)function, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1),
+                       "cuFuncSetAttribute(NON_PORTABLE_CLUSTER_SIZE_ALLOWED)")) return e;
+    }
+    CUlaunchAttribute attr[2];
+    unsigned n = 0;
+    if (cluster > 1) {
+        attr[n].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attr[n].value.clusterDim.x = cluster; attr[n].value.clusterDim.y = 1; attr[n].value.clusterDim.z = 1;
+        n++;
+    }
+    if (cooperative) { attr[n].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE; attr[n].value.cooperative = 1; n++; }
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = dynamic_smem; cfg.hStream = (CUstream)stream; cfg.attrs = attr; cfg.numAttrs = n;
+    return cu(g_cu.LaunchEx(&cfg, (CUfunction)function, args, nullptr), "cuLaunchKernelEx");
 }
 
 int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,

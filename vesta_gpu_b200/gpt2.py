@@ -46,7 +46,7 @@ def shape_of(W, heads=None):
 
 class VestaGPT2:
     def __init__(self, hf, dtype='f16', batch=1, tmax=1024, feedback=True, program=None, timing=False,
-                 blocks_per_sm=None, per_sequence_t=False, device=None, prompt_len=0, slab_tiles=None):
+                 blocks_per_sm=None, per_sequence_t=False, device=None, prompt_len=0, slab_tiles=None, tune=None):
         """program: path of a .vst file; default: the step program for the sizes of the weights
         (identical to programs/gpt2.vst for GPT-2 small). per_sequence_t: every sequence keeps its
         own position t[b] (ragged batches); default one position for the whole batch as in the
@@ -78,7 +78,7 @@ class VestaGPT2:
         per_token = ('x', 'keys', 'vals') + (('t',) if per_sequence_t else ())
         self.low = lower(text, spec, axis_max={'s': tmax}, batch=batch, per_token=per_token,
                          outputs=('logit', 'next'), feedback={'x': 'next', 't': 1} if feedback else None,
-                         timing=timing, grid=sms, prompt_len=prompt_len if feedback else 0, slab_tiles=slab_tiles)
+                         timing=timing, grid=sms, prompt_len=prompt_len if feedback else 0, slab_tiles=slab_tiles, tune=tune)
         self.k = Kernel(self.low, device=dev.index, blocks_per_sm=blocks_per_sm)
         if prompt_len and feedback:
             R = dict(R, prompt=self.prompt, plen=self.plen)

@@ -290,7 +290,7 @@ def place_step(dims, grid):
 
 # ------------------------------------------------------------------ assembly
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
-          grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None):
+          grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None):
     """See the module docstring. `res`: name -> (shape, dtype) as the kernel sees them (batched
     where per-token; scalars have shape ()). `axis_max`: bound of the run-time position axis,
     e.g. {'s': tmax}. `grid`: CTAs to place for (one per SM). 't' may be listed in per_token, in
@@ -348,10 +348,20 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
             raise NotImplementedError(f'output {o}: only {env["$logit"]} and {env["$next"]} are kept for the host')
 
     # rows per slab (8 per batch tile): the operand tiles of a slab live in shared memory next to the
-    # weight ring, at most ~100 KB of them; larger batches run the contraction phases slab by slab
-    NB = min((B + 7) // 8, max(1, (100 * 1024) // ((D // 16) * 512)))
+    # weight ring, the K/V tiles and the LayerNorm staging; the largest slab that still leaves three
+    # ring slots is taken, larger batches run the contraction phases slab by slab
+    KT_D = D // 16
+    budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
+
+    def smem_fixed(nb):
+        return (2 * NW * 16 * 256 + KT_D * nb * 512 + WN_MAX * nb * 512 + 8 * (D + 8) * 4 + NW * nb * 512
+                + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
+
+    NB = min((B + 7) // 8, 8)
     if slab_tiles:
         NB = min(NB, int(slab_tiles))
+    while NB > 1 and (budget - smem_fixed(NB) - 1024) // (CHUNK_TILES * 512 + 16) < 3:
+        NB -= 1
     if act_lo is None:
         act_lo = True
     rec, tiles, notes = place_step(dims, grid)
@@ -364,16 +374,14 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     off_q = off_z + 3 * up(B * D)
     # position chunks per (sequence, head) in the attention phase: fewest rounds of the grid per position
     nch = min(range(1, 17), key=lambda k: (math.ceil(B * H * k / grid) / k, k))
+    tune = dict(tune or {})
+    nch = int(tune.get('nch', nch))
     off_part = off_q + up(B * D)
     off_best = off_part + up(B * H * nch * (E + 2))
     scratch_floats = off_best + up(2 * B)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
-    KT_D = D // 16
-    SBr = 8 * NB
-    fixed = (KT_D * NB * 512 + WN_MAX * NB * 512 + 8 * (D + 8) * 4 + NW * NB * 512 + (3 * D + WN_MAX * 16) * 2 + 16
-             + NW * (E + 2) * 4 + 8 + SBr * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
-    budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
+    fixed = smem_fixed(NB)
     nslot = (budget - fixed - 1024) // (CHUNK_TILES * 512 + 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget at this batch')
@@ -388,7 +396,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch)
+                V_MAXGRID=grid, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
