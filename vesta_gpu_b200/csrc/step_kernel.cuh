@@ -148,7 +148,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 // ---------------------------------------------------------------------------------------------
 #define SM_RING 0
 #define SM_KV (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)             // K/V tiles of the attention phase
-#define SM_ACT (SM_KV + 2 * NW * 16 * 256)                        // B operands of the current contraction
+#define SM_ACT (SM_KV + 2 * 2 * NW * 16 * 144)                    // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
 #define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // eight fp32 rows staged for LayerNorm
 #define SM_RED (SM_ZS + 8 * (V_D + 8) * 4)                        // NARROW partial sums, one tile per warp
@@ -501,11 +501,16 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // with cp.async, two tiles ahead of the arithmetic, so that the cache streams while the softmax runs.
 // The first tile is requested before the grid barrier that ends the QKV phase; the row of the current
 // position (written during that phase by another CTA) is fetched after the barrier.
-// Arithmetic: 8 lanes per position (8 dims each), 4 positions per warp at a time, online softmax in
-// registers; result per item: (running max, sum, unnormalised o[V_E]).
+// Arithmetic on the tensor pipe: a warp takes 16 positions of the tile. Scores: A = the K rows
+// (ldmatrix, 16 positions x 16 dims per step), B = the query, its fp16 head in column 0 and its fp16
+// remainder in column 1, so that column 0 + column 1 is the fp32-accurate dot product. Online softmax
+// on the 16 scores (held by the lanes with lane%4 == 0). Output: A = V transposed (ldmatrix.trans,
+// 16 dims x 16 positions), B = the weights, head and remainder again in columns 0 and 1.
+// Result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
-#define KV_POS (NW * 16)                         // positions per tile: four per 8-lane group
-#define KV_STAGE_BYTES (KV_POS * 256)            // K rows then V rows
+#define KV_POS (NW * 16)                         // positions per tile: sixteen per warp
+#define KV_ROW 144                               // bytes per staged row: 128 of data, 16 of padding (ldmatrix without bank conflicts)
+#define KV_STAGE_BYTES (2 * KV_POS * KV_ROW)     // K rows then V rows
 #define KV_STAGES 2
 
 struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
@@ -535,7 +540,7 @@ __device__ __forceinline__ void att_fetch(Ctx& c, const AttIter& a, const u16* _
         const int pos = i >> 4, piece = i & 15;
         if (a.s + pos == skip) continue;
         const u16* src = ((piece & 8) ? vals : keys) + row0 + (size_t)(a.s + pos) * V_D + (piece & 7) * 8;
-        cp16(stage + (piece >> 3) * (KV_POS * 128) + pos * 128 + (piece & 7) * 16, src);
+        cp16(stage + (piece >> 3) * (KV_POS * KV_ROW) + pos * KV_ROW + (piece & 7) * 16, src);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
@@ -547,20 +552,31 @@ __device__ __forceinline__ void attention_prefetch(Ctx& c, const u16* __restrict
     if (att_valid(a)) att_fetch(c, a, keys, vals, l, c.smem + SM_KV, s_pos[a.b]);
 }
 
+__device__ __forceinline__ void ldsm4(u32 (&r)[4], const unsigned char* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm4t(u32 (&r)[4], const unsigned char* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_r(float (&c)[4], const u32 (&a)[4], u32 b0, u32 b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
                                                 float* __restrict__ part, int l, const int* s_pos) {
-    const int li = c.lane & 7, grp = c.warp * 4 + (c.lane >> 3);
+    const int g = c.lane >> 2, t = c.lane & 3;
     AttIter cur, pf;
     cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
     if (!att_valid(cur)) return;
     pf = cur;
     // the row that was left out before the barrier
     {
-        const int t = s_pos[cur.b];
-        if (t >= cur.s && t < min(cur.hi, cur.s + KV_POS) && c.tid < 16) {
+        const int tp = s_pos[cur.b];
+        if (tp >= cur.s && tp < min(cur.hi, cur.s + KV_POS) && c.tid < 16) {
             const size_t row0 = ((size_t)(cur.b * V_L + l) * V_TMAX) * V_D + (size_t)cur.h * V_E;
-            const u16* src = ((c.tid & 8) ? vals : keys) + row0 + (size_t)t * V_D + (c.tid & 7) * 8;
-            cp16(c.smem + SM_KV + (c.tid >> 3) * (KV_POS * 128) + (t - cur.s) * 128 + (c.tid & 7) * 16, src);
+            const u16* src = ((c.tid & 8) ? vals : keys) + row0 + (size_t)tp * V_D + (c.tid & 7) * 8;
+            cp16(c.smem + SM_KV + (c.tid >> 3) * (KV_POS * KV_ROW) + (tp - cur.s) * KV_ROW + (c.tid & 7) * 16, src);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -569,72 +585,97 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     else asm volatile("cp.async.commit_group;" ::: "memory");
 
     int stage = 0;
-    float q[8], m = -3.0e38f, den = 0.f, acc[8];
+    u32 bq[V_E / 16][2];                             // B operand of the scores: the query, head (column 0) / remainder (column 1)
+    float m = -3.0e38f, den = 0.f, o[V_E / 16][4];   // o[mt]: dims mt*16 + g (regs 0+1) and mt*16 + g + 8 (regs 2+3), lanes t == 0
     bool fresh = true;                               // the next tile starts an item
 #pragma unroll 1
     while (att_valid(cur)) {
         if (fresh) {
-            const float* qp = qbuf + (size_t)cur.b * V_D + cur.h * V_E + li * 8;
-            const float4 q0 = __ldcg(reinterpret_cast<const float4*>(qp)), q1 = __ldcg(reinterpret_cast<const float4*>(qp + 4));
+            const float* qp = qbuf + (size_t)cur.b * V_D + cur.h * V_E;
             const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
-            q[0] = q0.x * sc; q[1] = q0.y * sc; q[2] = q0.z * sc; q[3] = q0.w * sc; q[4] = q1.x * sc; q[5] = q1.y * sc; q[6] = q1.z * sc; q[7] = q1.w * sc;
+#pragma unroll
+            for (int kq = 0; kq < V_E / 16; kq++) {
+                bq[kq][0] = 0; bq[kq][1] = 0;
+                if (g < 2) {
+                    const float2 a0 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
+                    const float2 a1 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
+                    const u32 h0 = pack_h2(a0.x * sc, a0.y * sc), h1 = pack_h2(a1.x * sc, a1.y * sc);
+                    bq[kq][0] = g == 0 ? h0 : pack_h2(a0.x * sc - h_lo(h0), a0.y * sc - h_hi(h0));
+                    bq[kq][1] = g == 0 ? h1 : pack_h2(a1.x * sc - h_lo(h1), a1.y * sc - h_hi(h1));
+                }
+            }
             m = -3.0e38f; den = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; i++) acc[i] = 0.f;
+            for (int mt = 0; mt < V_E / 16; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
             fresh = false;
         }
         asm volatile("cp.async.wait_group 1;" ::: "memory");       // this tile has landed; the next one may be in flight
         cons_sync();
-        const unsigned char* kv = c.smem + SM_KV + stage * KV_STAGE_BYTES;
+        const unsigned char* kt = c.smem + SM_KV + stage * KV_STAGE_BYTES;
+        const unsigned char* vt = kt + KV_POS * KV_ROW;
         const int cnt = min(KV_POS, cur.hi - cur.s);
-        // the trip count is the same for every lane of the warp (the shuffles need all 32 lanes)
+        const int p0 = c.warp * 16;                                 // this warp's positions of the tile
+        if (p0 < cnt) {
+            // scores of 16 positions: rows g and g + 8 of the tile slice, in the lanes with t == 0
+            float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int u = 0; u < 4; u++) {
-            const int pos = grp + u * (NW * 4);
-            const uint4 k4 = lds128(kv + pos * 128 + li * 16), v4 = lds128(kv + KV_POS * 128 + pos * 128 + li * 16);
-            float sc = q[0] * h_lo(k4.x) + q[1] * h_hi(k4.x) + q[2] * h_lo(k4.y) + q[3] * h_hi(k4.y) +
-                       q[4] * h_lo(k4.z) + q[5] * h_hi(k4.z) + q[6] * h_lo(k4.w) + q[7] * h_hi(k4.w);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-            if (pos < cnt) {
-                if (!V_SCALE_IS_POW2) sc = sc / V_SCALE;
-                const float mn = fmaxf(m, sc);
-                const float corr = fast_exp(m - mn), p = fast_exp(sc - mn);
-                den = den * corr + p;
-                acc[0] = acc[0] * corr + p * h_lo(v4.x); acc[1] = acc[1] * corr + p * h_hi(v4.x);
-                acc[2] = acc[2] * corr + p * h_lo(v4.y); acc[3] = acc[3] * corr + p * h_hi(v4.y);
-                acc[4] = acc[4] * corr + p * h_lo(v4.z); acc[5] = acc[5] * corr + p * h_hi(v4.z);
-                acc[6] = acc[6] * corr + p * h_lo(v4.w); acc[7] = acc[7] * corr + p * h_hi(v4.w);
-                m = mn;
+            for (int kq = 0; kq < V_E / 16; kq++) {
+                u32 a[4];
+                ldsm4(a, kt + (p0 + (c.lane & 15)) * KV_ROW + kq * 32 + (c.lane >> 4) * 16);
+                mma_r(sacc, a, bq[kq][0], bq[kq][1]);
+            }
+            float s0 = sacc[0] + sacc[1], s1 = sacc[2] + sacc[3];
+            if (!V_SCALE_IS_POW2) { s0 = s0 / V_SCALE; s1 = s1 / V_SCALE; }
+            if (t != 0 || p0 + g >= cnt) s0 = -3.0e38f;
+            if (t != 0 || p0 + g + 8 >= cnt) s1 = -3.0e38f;
+            float mx = fmaxf(s0, s1);
+#pragma unroll
+            for (int x = 4; x <= 16; x <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+            mx = __shfl_sync(0xffffffffu, mx, 0);                   // lanes with t != 0 saw only their own minus infinity
+            const float mn = fmaxf(m, mx);
+            const float corr = fast_exp(m - mn);
+            const float pa = (s0 > -1.0e38f) ? fast_exp(s0 - mn) : 0.f, pb = (s1 > -1.0e38f) ? fast_exp(s1 - mn) : 0.f;
+            float ps = pa + pb;
+#pragma unroll
+            for (int x = 4; x <= 16; x <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
+            ps = __shfl_sync(0xffffffffu, ps, 0);
+            den = den * corr + ps;
+            m = mn;
+#pragma unroll
+            for (int mt = 0; mt < V_E / 16; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) o[mt][i] *= corr;
+            // weights as the B operand: lane (g, t) holds positions 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1); the weight
+            // of position r < 8 is `pa` of lane 4r, that of position r + 8 is `pb` of lane 4r
+            const float w00 = __shfl_sync(0xffffffffu, pa, 8 * t), w01 = __shfl_sync(0xffffffffu, pa, 8 * t + 4);
+            const float w10 = __shfl_sync(0xffffffffu, pb, 8 * t), w11 = __shfl_sync(0xffffffffu, pb, 8 * t + 4);
+            u32 b0 = pack_h2(w00, w01), b1 = pack_h2(w10, w11);
+            if (g == 1) { b0 = pack_h2(w00 - h_lo(b0), w01 - h_hi(b0)); b1 = pack_h2(w10 - h_lo(b1), w11 - h_hi(b1)); }
+            if (g > 1) { b0 = 0; b1 = 0; }
+#pragma unroll
+            for (int mt = 0; mt < V_E / 16; mt++) {
+                u32 a[4];
+                const int j = c.lane >> 3;
+                ldsm4t(a, vt + (p0 + (c.lane & 7) + ((j >> 1) ? 8 : 0)) * KV_ROW + mt * 32 + ((j & 1) ? 16 : 0));
+                mma_r(o[mt], a, b0, b1);
             }
         }
         const bool last = cur.s + KV_POS >= cur.hi;
         float* out = part + (size_t)cur.it * PART_STRIDE;
+        float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
         if (last) {
-            // merge the 4 position groups of the warp (lanes li, li+8, li+16, li+24 hold the same dims)
+            // per warp (m, den, o[V_E]) into shared memory
+            float* w = ms + c.warp * (V_E + 2);
+            if (c.lane == 0) { w[0] = m; w[1] = den; }
+            if (t == 0) {
 #pragma unroll
-            for (int x = 8; x <= 16; x <<= 1) {
-                const float m2 = __shfl_xor_sync(0xffffffffu, m, x), d2 = __shfl_xor_sync(0xffffffffu, den, x);
-                const float mn = fmaxf(m, m2);
-                const float c1 = fast_exp(m - mn), c2 = fast_exp(m2 - mn);
-                den = den * c1 + d2 * c2;
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc[i] = acc[i] * c1 + __shfl_xor_sync(0xffffffffu, acc[i], x) * c2;
-                m = mn;
-            }
-            // merge the warps through shared memory: per warp (m, den, acc[V_E])
-            float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
-            if (c.lane < 8) {
-                float* w = ms + c.warp * (V_E + 2);
-                if (c.lane == 0) { w[0] = m; w[1] = den; }
-#pragma unroll
-                for (int i = 0; i < 8; i++) w[2 + li * 8 + i] = acc[i];
+                for (int mt = 0; mt < V_E / 16; mt++) { w[2 + mt * 16 + g] = o[mt][0] + o[mt][1]; w[2 + mt * 16 + g + 8] = o[mt][2] + o[mt][3]; }
             }
         }
         cons_sync();                                   // everybody is done with this stage (and ms is written)
         if (last && c.tid < V_E) {
-            const float* ms = reinterpret_cast<const float*>(c.smem + SM_MISC + MISC_ATT);
             float M = -3.0e38f;
 #pragma unroll 1
             for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
@@ -714,9 +755,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // operand tiles start as zero: rows of a batch tile beyond the batch stay zero for the whole launch
+    // operand tiles and K/V stages start as zero: rows of a batch tile beyond the batch stay zero for the whole
+    // launch, and staged rows past the end of a chunk only ever meet a weight of zero
 #pragma unroll 1
-    for (int i = c.tid; i < (SM_ZS - SM_ACT) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_ACT)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = c.tid; i < (SM_ZS - SM_KV) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_KV)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
     const int* P = a.PT + c.cta * PT_STRIDE;

@@ -354,7 +354,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
 
     def smem_fixed(nb):
-        return (2 * NW * 16 * 256 + KT_D * nb * 512 + WN_MAX * nb * 512 + 8 * (D + 8) * 4 + NW * nb * 512
+        return (2 * 2 * NW * 16 * 144 + KT_D * nb * 512 + WN_MAX * nb * 512 + 8 * (D + 8) * 4 + NW * nb * 512
                 + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
@@ -372,8 +372,11 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     off_logit, off_next = 0, up(B * N)
     off_z = up(off_next + B)
     off_q = off_z + 3 * up(B * D)
-    # position chunks per (sequence, head) in the attention phase: fewest rounds of the grid per position
-    nch = min(range(1, 17), key=lambda k: (math.ceil(B * H * k / grid) / k, k))
+    # position chunks per (sequence, head) in the attention phase: rounds of the grid x (positions per chunk
+    # + the fixed cost of an item, about one tile of 128 positions), at a typical context of tmax / 2
+    def att_cost(k):
+        return math.ceil(B * H * k / grid) * (max(tmax // 2, 1) / k + 192)
+    nch = min(range(1, 17), key=lambda k: (att_cost(k), k))
     tune = dict(tune or {})
     nch = int(tune.get('nch', nch))
     off_part = off_q + up(B * D)
