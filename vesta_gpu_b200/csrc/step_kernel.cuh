@@ -151,7 +151,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define SM_ACT (SM_KV + 2 * 2 * NW * 16 * 144)                    // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
 #define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // eight fp32 rows staged for LayerNorm
-#define SM_RED (SM_ZS + 8 * (V_D + 8) * 4)                        // NARROW partial sums, one tile per warp
+#define SM_RED (SM_ZS + (V_LN_DIST ? 0 : 8 * (V_D + 8) * 4))          // NARROW partial sums, one tile per warp
 #define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
 #define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
 #define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
@@ -463,6 +463,70 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
         }
         cons_sync();
     }
+}
+
+// Distributed LayerNorm (batches of more than two batch tiles): instead of every CTA normalising every row
+// of its slab, the rows are dealt over all warps of the grid; a warp normalises its row once and writes
+// it as operand tiles to global memory (actg: per slab [fold tile][batch tile][lane][16 B], the layout
+// of the shared-memory operand), and starts the vector the following projection is combined into
+// (init[r] = z[r] + bias, a plain store: nothing has been added to it yet). After a grid barrier every
+// CTA copies the tiles of the slab it works on into shared memory.
+#define LNV ((G4 + 31) / 32)
+#define SLAB_TILE_BYTES (KT_D * V_NB * FRAG_BYTES)
+__device__ __forceinline__ void ln_rows_to_global(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* __restrict__ actg) {
+    const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
+#pragma unroll 1
+    for (int r = c.cta * NW + c.warp; r < V_B; r += c.ncta * NW) {
+        float4 v[LNV];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            const int g = i * 32 + c.lane;
+            v[i] = (g < G4) ? __ldcg(reinterpret_cast<const float4*>(z + (size_t)r * V_D) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+        const float mean = s * (1.0f / V_D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            if (i * 32 + c.lane < G4) {
+                const float a0 = v[i].x - mean, a1 = v[i].y - mean, a2 = v[i].z - mean, a3 = v[i].w - mean;
+                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
+        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        unsigned char* tiles = actg + (size_t)(r / SB) * SLAB_TILE_BYTES;
+        const int rb = r % SB;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            const int g = i * 32 + c.lane, d = g * 4;
+            if (g < G4) {
+                const uint2 w = *reinterpret_cast<const uint2*>(prm + d);
+                const uint2 bb = *reinterpret_cast<const uint2*>(prm + V_D + d);
+                float4 o;
+                o.x = (v[i].x - mean) * rs * h_lo(w.x) + h_lo(bb.x);
+                o.y = (v[i].y - mean) * rs * h_hi(w.x) + h_hi(bb.x);
+                o.z = (v[i].z - mean) * rs * h_lo(w.y) + h_lo(bb.y);
+                o.w = (v[i].w - mean) * rs * h_hi(w.y) + h_hi(bb.y);
+                act_store4(tiles, rb, d, o);
+                if (init) {
+                    const uint2 ib = *reinterpret_cast<const uint2*>(prm + 2 * V_D + d);
+                    *reinterpret_cast<float4*>(init + (size_t)r * V_D + d) =
+                        make_float4(v[i].x + h_lo(ib.x), v[i].y + h_hi(ib.x), v[i].z + h_lo(ib.y), v[i].w + h_hi(ib.y));
+                }
+            }
+        }
+    }
+}
+__device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __restrict__ tiles, unsigned char* act) {
+#pragma unroll 1
+    for (int i = c.tid; i < SLAB_TILE_BYTES / 16; i += NCONS) cp16(act + (size_t)i * 16, tiles + (size_t)i * 16);
+    cp_wait();
+    cons_sync();
 }
 
 // Attention output for the fold range [k0*16, (k0+nk)*16) of the projection, merged from the
@@ -777,6 +841,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
     float* qbuf = a.S + V_OFF_Q;
     float* part = a.S + V_OFF_PART;
     float* logit = a.S + V_OFF_LOGIT;
+    unsigned char* actg = reinterpret_cast<unsigned char*>(a.S + V_OFF_ACTG);
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
@@ -811,23 +876,36 @@ __device__ __forceinline__ void step_body(const Args& a) {
             attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos);
         } else {
             // LN1 phase clears z2 (the MLP adds into it two barriers later); LN2 phase clears zin for the next layer
-            float* clr = (first == PH_QKV) ? z2 : (first == PH_FC) ? zin : (float*)0;
+            // (not needed with the distributed LayerNorm, which starts those vectors with a plain store)
+            float* clr = V_LN_DIST ? (float*)0 : (first == PH_QKV) ? z2 : (first == PH_FC) ? zin : (float*)0;
             if (clr) {
 #pragma unroll 1
                 for (int i = gtid; i < V_B * V_D; i += gthreads) clr[i] = 0.f;
             }
         }
 
+#if V_LN_DIST
+        if (first == PH_QKV || first == PH_FC || first == PH_LOGITS) {
+            ln_rows_to_global(c, (first == PH_FC) ? z1 : zin, (first == PH_QKV) ? z1 : (first == PH_FC) ? z2 : (float*)0, actg);
+            phase_end(c);
+            phase_wait(c);
+        }
+#endif
 #pragma unroll 1
         for (int slab = 0; slab < ((first == PH_ATT) ? 0 : NSLAB); slab++) {
             const int row0 = slab * SB, nrows = min(SB, V_B - row0);
 #pragma unroll 1
             for (int kind = first; kind <= last; kind++) {
                 // ---- prologue: what the contraction reads from other CTAs, into operand tiles
-                if (kind == PH_QKV || kind == PH_FC || kind == PH_LOGITS)
+                if (kind == PH_QKV || kind == PH_FC || kind == PH_LOGITS) {
                     // LN1 (starts z1 = z + ob) | LN2 (starts z2 = z1 + pb) | LNf
+#if V_LN_DIST
+                    load_act_tiles(c, actg + (size_t)slab * SLAB_TILE_BYTES, act);
+#else
                     ln_to_act(c, ((kind == PH_FC) ? z1 : zin) + (size_t)row0 * V_D,
                               (kind == PH_QKV) ? z1 + (size_t)row0 * V_D : (kind == PH_FC) ? z2 + (size_t)row0 * V_D : (float*)0, act, nrows);
+#endif
+                }
                 else if (kind == PH_PROJ && P[PT_PROJ_NJ])
                     merge_to_act(c, part, P[PT_PROJ_K0], P[PT_PROJ_NK], act, row0, nrows);
                 TRACE(10 + kind);

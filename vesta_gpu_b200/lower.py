@@ -353,8 +353,12 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     KT_D = D // 16
     budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
 
+    # batches of more than two batch tiles normalise each row once, on one warp of the grid, and pass the
+    # operand tiles through global memory; smaller ones let every CTA normalise the rows itself (one barrier less)
+    ln_dist = bool(tune.get('ln_dist', B > 16)) if tune else B > 16
+
     def smem_fixed(nb):
-        return (2 * 2 * NW * 16 * 144 + KT_D * nb * 512 + WN_MAX * nb * 512 + 8 * (D + 8) * 4 + NW * nb * 512
+        return (2 * 2 * NW * 16 * 144 + KT_D * nb * 512 + WN_MAX * nb * 512 + (0 if ln_dist else 8 * (D + 8) * 4) + NW * nb * 512
                 + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
@@ -380,7 +384,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     tune = dict(tune or {})
     nch = int(tune.get('nch', nch))
     off_part = off_q + up(B * D)
-    off_best = off_part + up(B * H * nch * (E + 2))
+    off_actg = off_part + up(B * H * nch * (E + 2))
+    off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * 128) if ln_dist else 0)
     scratch_floats = off_best + up(2 * B)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
@@ -399,7 +404,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
@@ -452,7 +457,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
         + ['logits', 'finish']
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
-                  barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
+                  barriers_per_launch=1 + 4 * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
                   dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes), roles=roles)
     return low
