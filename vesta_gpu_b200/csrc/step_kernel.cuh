@@ -594,18 +594,18 @@ __device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int nc
     if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
 }
 
-// request the rows [a.s, min(a.hi, a.s + KV_POS)) of the item into a stage, except position `skip`
+// request the rows [a.s, min(a.hi, a.s + KV_POS)) of the item into a stage, except position `skip`.
+// Thread i copies the same 16-byte piece of rows i/16, i/16 + NCONS/16, ...: one address, then a constant step.
 __device__ __forceinline__ void att_fetch(Ctx& c, const AttIter& a, const u16* __restrict__ keys, const u16* __restrict__ vals, int l,
                                           unsigned char* stage, int skip) {
     const int cnt = min(KV_POS, a.hi - a.s);
-    const size_t row0 = ((size_t)(a.b * V_L + l) * V_TMAX) * V_D + (size_t)a.h * V_E;
-#pragma unroll 1
-    for (int i = c.tid; i < cnt * 16; i += NCONS) {
-        const int pos = i >> 4, piece = i & 15;
-        if (a.s + pos == skip) continue;
-        const u16* src = ((piece & 8) ? vals : keys) + row0 + (size_t)(a.s + pos) * V_D + (piece & 7) * 8;
-        cp16(stage + (piece >> 3) * (KV_POS * KV_ROW) + pos * KV_ROW + (piece & 7) * 16, src);
-    }
+    const int piece = c.tid & 15;
+    int pos = c.tid >> 4;
+    const u16* src = ((piece & 8) ? vals : keys) + ((size_t)(a.b * V_L + l) * V_TMAX + a.s + pos) * V_D + (size_t)a.h * V_E + (piece & 7) * 8;
+    unsigned char* dst = stage + (piece >> 3) * (KV_POS * KV_ROW) + pos * KV_ROW + (piece & 7) * 16;
+#pragma unroll 2
+    for (; pos < cnt; pos += NCONS / 16, src += (size_t)(NCONS / 16) * V_D, dst += (NCONS / 16) * KV_ROW)
+        if (a.s + pos != skip) cp16(dst, src);
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
 
