@@ -43,6 +43,8 @@ typedef unsigned short u16;
 #define TPW 2                         // output tiles a warp owns in a WIDE group
 #define WG (TPW * NW)                  // output tiles per WIDE group
 #define G4 (V_D / 4)                  // float4 groups per activation row
+#define ALB (V_ACT_LO ? 16 : 8)        // bytes per lane of an operand tile: fp16 head (b0, b1) and, if kept, the fp16 remainder
+#define ATILE (32 * ALB)              // bytes per operand tile (16 fold indices x 8 batch rows)
 
 // bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter
 #define BAR_STATUS 0
@@ -86,6 +88,15 @@ __device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u3
 __device__ __forceinline__ void cp16(void* dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) { return *reinterpret_cast<const uint4*>(p); }
+// one lane's part of an operand tile: (b0, b1) of the head and, if kept, (b0, b1) of the remainder
+__device__ __forceinline__ uint4 lds_act(const unsigned char* p) {
+#if V_ACT_LO
+    return *reinterpret_cast<const uint4*>(p);
+#else
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    return make_uint4(v.x, v.y, 0u, 0u);
+#endif
+}
 
 // orderable key of (value, index): larger value wins, then the lower index
 __device__ __forceinline__ u64 best_key(float v, u32 n) {
@@ -149,8 +160,8 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define SM_RING 0
 #define SM_KV (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)             // K/V tiles of the attention phase
 #define SM_ACT (SM_KV + 2 * 2 * NW * 16 * 144)                    // B operands of the current contraction
-#define SM_GACT (SM_ACT + KT_D * V_NB * FRAG_BYTES)               // B operands of the MLP projection (GELU output)
-#define SM_ZS (SM_GACT + WN_MAX * V_NB * FRAG_BYTES)              // eight fp32 rows staged for LayerNorm
+#define SM_GACT (SM_ACT + KT_D * V_NB * ATILE)                    // B operands of the MLP projection (GELU output)
+#define SM_ZS (SM_GACT + WN_MAX * V_NB * ATILE)                   // eight fp32 rows staged for LayerNorm
 #define SM_RED (SM_ZS + (V_LN_DIST ? 0 : 8 * (V_D + 8) * 4))          // NARROW partial sums, one tile per warp
 #define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
 #define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
@@ -308,7 +319,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
                 if (own1) a1 = lds128(tp + NW * FRAG_BYTES);
 #pragma unroll
                 for (int nb = 0; nb < V_NB; nb++) {
-                    const uint4 b = lds128(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * 16);
+                    const uint4 b = lds_act(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * ALB);
                     if (own0) { mma16816(acc[0][nb], a0, b.x, b.y); if (V_ACT_LO) mma16816(lo[0][nb], a0, b.z, b.w); }
                     if (own1) { mma16816(acc[1][nb], a1, b.x, b.y); if (V_ACT_LO) mma16816(lo[1][nb], a1, b.z, b.w); }
                 }
@@ -334,7 +345,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
                 const uint4 a = lds128(tiles + (size_t)f * FRAG_BYTES);
 #pragma unroll
                 for (int nb = 0; nb < V_NB; nb++) {
-                    const uint4 b = lds128(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * 16);
+                    const uint4 b = lds_act(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * ALB);
                     mma16816(acc[0][nb], a, b.x, b.y);
                     if (V_ACT_LO) mma16816(lo[0][nb], a, b.z, b.w);
                 }
@@ -358,22 +369,25 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
 // remainder), half k%2
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void act_store4(unsigned char* act, int b, int k, float4 v) {
-    // k is a multiple of 4: two words of the same register index
+    // k is a multiple of 4: two lanes of the tile, the same register index in both
     const u32 h0 = pack_h2(v.x, v.y), h1 = pack_h2(v.z, v.w);
-    const u32 l0 = pack_h2(v.x - h_lo(h0), v.y - h_hi(h0)), l1 = pack_h2(v.z - h_lo(h1), v.w - h_hi(h1));
     const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1;
-    u32* base = reinterpret_cast<u32*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4) * 16);
-    base[t * 4 + reg] = h0;
-    base[t * 4 + 2 + reg] = l0;
-    base[(t + 1) * 4 + reg] = h1;
-    base[(t + 1) * 4 + 2 + reg] = l1;
+    u32* base = reinterpret_cast<u32*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4 + t) * ALB);
+    base[reg] = h0;
+    base[ALB / 4 + reg] = h1;
+#if V_ACT_LO
+    base[2 + reg] = pack_h2(v.x - h_lo(h0), v.y - h_hi(h0));
+    base[ALB / 4 + 2 + reg] = pack_h2(v.z - h_lo(h1), v.w - h_hi(h1));
+#endif
 }
 __device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, float v) {
-    const u16 hi = f2h(v), lo = f2h(v - h2f(hi));
+    const u16 hi = f2h(v);
     const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1, half = kk & 1;
-    u16* base = reinterpret_cast<u16*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4 + t) * 16);
+    u16* base = reinterpret_cast<u16*>(act + ((size_t)(kt * V_NB + (b >> 3)) * 32 + (b & 7) * 4 + t) * ALB);
     base[reg * 2 + half] = hi;
-    base[(2 + reg) * 2 + half] = lo;
+#if V_ACT_LO
+    base[(2 + reg) * 2 + half] = f2h(v - h2f(hi));
+#endif
 }
 
 // Parameters of the next LayerNorm phase into shared memory: gain, shift, the bias added when the
@@ -459,7 +473,11 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
                     red_add(dst + 8, v1.x + h_lo(i1)); red_add(dst + 9, v1.y + h_hi(i1));
                 }
             }
-            *reinterpret_cast<uint4*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * 16) = out;
+#if V_ACT_LO
+            *reinterpret_cast<uint4*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * ALB) = out;
+#else
+            *reinterpret_cast<uint2*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * ALB) = make_uint2(out.x, out.y);
+#endif
         }
         cons_sync();
     }
@@ -472,7 +490,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
 // (init[r] = z[r] + bias, a plain store: nothing has been added to it yet). After a grid barrier every
 // CTA copies the tiles of the slab it works on into shared memory.
 #define LNV ((G4 + 31) / 32)
-#define SLAB_TILE_BYTES (KT_D * V_NB * FRAG_BYTES)
+#define SLAB_TILE_BYTES (KT_D * V_NB * ATILE)
 __device__ __forceinline__ void ln_rows_to_global(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* __restrict__ actg) {
     const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
 #pragma unroll 1

@@ -357,8 +357,14 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     # operand tiles through global memory; smaller ones let every CTA normalise the rows itself (one barrier less)
     ln_dist = bool(tune.get('ln_dist', B > 16)) if tune else B > 16
 
+    # with the distributed LayerNorm the operand tiles keep only the fp16 head of the activations (half the
+    # shared memory, twice the rows per slab); smaller batches keep head + remainder (fp32-accurate products)
+    if act_lo is None:
+        act_lo = not ln_dist
+    atile = 512 if act_lo else 256
+
     def smem_fixed(nb):
-        return (2 * 2 * NW * 16 * 144 + KT_D * nb * 512 + WN_MAX * nb * 512 + (0 if ln_dist else 8 * (D + 8) * 4) + NW * nb * 512
+        return (2 * 2 * NW * 16 * 144 + KT_D * nb * atile + WN_MAX * nb * atile + (0 if ln_dist else 8 * (D + 8) * 4) + NW * nb * 512
                 + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
@@ -366,8 +372,6 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         NB = min(NB, int(slab_tiles))
     while NB > 1 and (budget - smem_fixed(NB) - 1024) // (CHUNK_TILES * 512 + 16) < 3:
         NB -= 1
-    if act_lo is None:
-        act_lo = True
     rec, tiles, notes = place_step(dims, grid)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
@@ -385,7 +389,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     nch = int(tune.get('nch', nch))
     off_part = off_q + up(B * D)
     off_actg = off_part + up(B * H * nch * (E + 2))
-    off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * 128) if ln_dist else 0)
+    off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * atile // 4) if ln_dist else 0)
     scratch_floats = off_best + up(2 * B)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
