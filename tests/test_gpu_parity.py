@@ -124,14 +124,21 @@ def test_against_oracle_other_batches(batch):
     m.k.check()
 
 
-@pytest.mark.parametrize('batch,slab_tiles', [(20, 1), (20, None), (9, 1), (33, 2)])
-def test_batches_above_one_slab(batch, slab_tiles):
-    """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged)"""
+@pytest.mark.parametrize('batch,slab_tiles,tune', [
+    (20, 1, None), (20, None, None), (9, 1, None), (33, 2, None),
+    (20, 1, dict(ln_dist=True, act_lo=True)),          # rows normalised once on the grid, tiles through global memory
+    (33, 2, dict(ln_dist=True, act_lo=False)),         # ... with fp16-head operand tiles (the large-batch mode)
+    (5, None, dict(ln_dist=True)),                     # ... at a batch below one tile
+    (20, 1, dict(ln_dist=False, act_lo=True)),         # every CTA normalises its slab, head + remainder
+])
+def test_batches_above_one_slab(batch, slab_tiles, tune):
+    """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged), in both
+    LayerNorm modes and both operand precisions"""
     from oracle import gpt2_numpy as O
     from vesta_gpu_b200.shapes import TINY3
     from vesta_gpu_b200.synth import make_prompts
     steps = 5
-    m, hf = model(TINY3, 11, 'rich', batch, steps, slab_tiles=slab_tiles)
+    m, hf = model(TINY3, 11, 'rich', batch, steps, slab_tiles=slab_tiles, tune=tune)
     W = O.upcast(hf.weights)
     feed = make_prompts(TINY3, batch, steps, seed=batch)
     caches = [O.new_cache(TINY3, steps) for _ in range(batch)]

@@ -353,14 +353,16 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     KT_D = D // 16
     budget = SMEM_LIMIT - (8192 if timing else 0)      # the timing build keeps its event trace in static shared memory
 
-    # batches of more than two batch tiles normalise each row once, on one warp of the grid, and pass the
-    # operand tiles through global memory; smaller ones let every CTA normalise the rows itself (one barrier less)
-    ln_dist = bool(tune.get('ln_dist', B > 16)) if tune else B > 16
-
-    # with the distributed LayerNorm the operand tiles keep only the fp16 head of the activations (half the
-    # shared memory, twice the rows per slab); smaller batches keep head + remainder (fp32-accurate products)
+    # Where the per-CTA LayerNorm is expensive (many rows, or wide rows) each row is normalised once, on one
+    # warp of the grid, and the operand tiles pass through global memory (one more barrier per LayerNorm);
+    # measured on B200: better from batch 12 at width 768 and at every batch at width 1600.
+    tune = dict(tune or {})
+    ln_dist = bool(tune.get('ln_dist', B * D >= 12 * 768 or D > 1024))
+    # Operand tiles hold the fp16 head and the fp16 remainder of the activations (fp32-accurate products) up to
+    # 16 rows (8 at widths above 1024); larger batches keep the head only: half the shared memory per row, twice
+    # the rows per slab, logits still within 2e-3 of the reference in the parity tests.
     if act_lo is None:
-        act_lo = not ln_dist
+        act_lo = bool(tune.get('act_lo', B <= 8 or (B <= 16 and D <= 1024)))
     atile = 512 if act_lo else 256
 
     def smem_fixed(nb):
