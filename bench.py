@@ -142,6 +142,7 @@ def main():
     ap.add_argument('--steps', type=int, default=256)
     ap.add_argument('--warmup', type=int, default=8)
     ap.add_argument('--repeats', type=int, default=5)
+    ap.add_argument('--per-launch', type=int, default=16, help='decode steps inside one kernel launch (1: a launch per step)')
     ap.add_argument('--workload', default='cfg2', choices=sorted(WORKLOADS))
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -224,7 +225,7 @@ def main():
             mark = sampler.mark()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        m.step(K)                                   # K launches back to back; the kernel feeds x and t itself
+        m.k.launch(K, per_launch=args.per_launch)   # launches of per_launch steps back to back; the kernel feeds x and t itself
         e1.record()
         sync_all()
         times.append(e0.elapsed_time(e1) * 1e-3)
@@ -287,14 +288,14 @@ def main():
     line = dict(metric=METRIC, value=B * world * K / med, unit=UNIT, n_gpus=world, steps=K, warmup=Wm,
                 ms_per_step=1e3 * med / K, higher_is_better=True, scaling='strong' if total else 'weak', vs_baseline=None,
                 dtype='f16 weights and KV, f32 accumulate', data='synthetic',
-                config=dict(workload=args.workload, **{k: v for k, v in wl.items() if k != 'total'}, batch_per_gpu=B, repeats=args.repeats,
+                config=dict(workload=args.workload, **{k: v for k, v in wl.items() if k != 'total'}, batch_per_gpu=B, repeats=args.repeats, steps_per_launch=min(args.per_launch, K),
                             l2='weights + KV read per step (%.0f MB) exceed the 126 MB L2' % (bytes_per_step / 1e6),
                             cv=round(statistics.pstdev(times) / statistics.mean(times), 4)),
-                clocks=clocks, gpu_launches=K,
+                clocks=clocks, gpu_launches=-(-K // args.per_launch),
                 e2e=dict(value=B * world * K / e2e_med, unit=UNIT, h2d_bytes_per_step=B * 4, d2h_bytes_per_step=B * 4,
                          tokens_match_device_loop=e2e_ok),
                 roofline=dict(bound='hbm', achieved=achieved, peak=peak, unit='GB/s', frac=achieved / peak, traffic=NCU_TRAFFIC.get(args.workload),
-                              peak_source=peak_src, bytes_per_launch=bytes_per_step, kernel='vesta_step',
+                              peak_source=peak_src, bytes_per_step=bytes_per_step, bytes_per_launch=bytes_per_step * min(args.per_launch, K), kernel='vesta_step',
                               frac_of_8tbs=achieved / 8000.0))
     if not args.no_cpu_baseline and world == 1:
         from oracle import gpt2_numpy as O

@@ -67,6 +67,10 @@ int vesta_launch_cluster(void* function, unsigned grid, unsigned block, unsigned
 int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
                     int n_args, const unsigned long long* device_pointers, void** bound);
 int vesta_step_run(void* bound, void* stream, int steps);
+/* The same, with up to `per_launch` decode steps inside one launch (the kernel's last parameter is the number
+ * of steps; it feeds its own token and position between them). The bound argument list must end with that
+ * parameter. No counterpart in the reference, which launches once per step. */
+int vesta_step_run_fused(void* bound, void* stream, int steps, int per_launch);
 void vesta_step_release(void* bound);
 
 /* No counterpart in the reference: one decode step for callers that must not allocate device

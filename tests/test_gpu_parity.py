@@ -252,6 +252,50 @@ def test_multi_step_launch_and_reset():
     m.k.check()
 
 
+@pytest.mark.parametrize('per_launch', [1, 3, 7, 20])
+def test_steps_inside_one_launch_equal_separate_launches(per_launch):
+    """several decode steps inside one launch (the kernel feeds itself and waits on its step flag) against
+    one launch per step: same tokens, same positions, same cache; ragged prompts fed on the device included"""
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import make_ragged_prompts
+    B, steps = 5, 20
+    lens, toks = make_ragged_prompts(TINY3, B, 1, 6, seed=5)
+    pmax = int(lens.max())
+    m, _ = model(TINY3, 7, 'rich', B, steps + 1, per_sequence_t=True, prompt_len=pmax)
+    def run(per):
+        m.reset(); m.k.bar.zero_()
+        m.prompt.copy_(torch.from_numpy(toks[:, :pmax].copy())); m.plen.copy_(torch.from_numpy(lens))
+        start = (lens - pmax).astype(np.int32)
+        m.t.copy_(torch.from_numpy(start)); m.x.copy_(torch.from_numpy(np.where(start == 0, toks[:, 0], 0).astype(np.int32)))
+        m.k.launch(steps, per_launch=per)
+        m.k.check()
+        return m.x.cpu().numpy().copy(), m.t.cpu().numpy().copy(), m.logits().cpu().numpy().copy(), m.keys.float().cpu().numpy().copy()
+    a, b = run(1), run(per_launch)
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    assert np.abs(a[2] - b[2]).max() < 2e-3 and np.abs(a[3] - b[3]).max() < 2e-3
+    assert int(m.k.bar[3]) == 0 and int(m.k.bar[32]) == 0           # step flag and barrier counter left clear
+
+
+def test_launch_of_many_steps_stops_at_the_end_of_the_cache():
+    """a launch asked for more steps than the cache has room for stops after the last step that fits and
+    says so; the steps before it are complete and the kernel is usable again afterwards"""
+    from vesta_gpu_b200.shapes import TINY
+    m, _ = model(TINY, 3, 'rich', 2, 8)
+    m.reset(); m.x.fill_(3)
+    m.k.launch(7, per_launch=1)
+    want_x, want_logits = m.x.clone(), m.logits().clone()
+    m.k.launch(1)                                   # the 8th step fills the cache: t becomes 8
+    full_x = m.x.clone()
+    m.reset(); m.x.fill_(3)
+    m.k.launch(20, per_launch=20)
+    assert 'out of range' in str(m.k.status())
+    assert int(m.t.cpu()[0]) == 8 and torch.equal(m.x, full_x)
+    m.k.bar.zero_(); m.reset(); m.x.fill_(3)
+    m.k.launch(7, per_launch=7)
+    m.k.check()
+    assert torch.equal(m.x, want_x) and (m.logits() - want_logits).abs().max() < 2e-3
+
+
 def test_out_of_range_inputs_are_refused_not_executed():
     from vesta_gpu_b200.shapes import TINY
     m, _ = model(TINY, 3, 'rich', 2, 8)

@@ -46,10 +46,11 @@ typedef unsigned short u16;
 #define ALB (V_ACT_LO ? 16 : 8)        // bytes per lane of an operand tile: fp16 head (b0, b1) and, if kept, the fp16 remainder
 #define ATILE (32 * ALB)              // bytes per operand tile (16 fold indices x 8 batch rows)
 
-// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [32] barrier counter
+// bar[] layout (u32): [0] status, [1] arrivals of the last phase, [2] abort flag, [3] steps done, [32] barrier counter
 #define BAR_STATUS 0
 #define BAR_DONE 1
 #define BAR_ABORT 2
+#define BAR_STEP 3                      // steps finished in this launch (0xffffffff: stop), cleared by its last step
 #define BAR_COUNT 32
 
 // every wait gives up after WAIT_NS nanoseconds (a step takes well under a millisecond)
@@ -70,6 +71,12 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint4& a, u32 b0, 
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void cons_sync() { asm volatile("bar.sync 1, %0;" :: "n"(NCONS) : "memory"); }
+// number of consumer threads with a non-zero predicate (a barrier over the consumer warps)
+__device__ __forceinline__ int __syncthreads_count_cons(int pred) {
+    int n;
+    asm volatile("{.reg .pred p; setp.ne.s32 p, %1, 0; bar.red.popc.u32 %0, 1, %2, p;}" : "=r"(n) : "r"(pred), "n"(NCONS) : "memory");
+    return n;
+}
 __device__ __forceinline__ u32 ld_acquire(const u32* p) { u32 v; asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ u32 ld_relaxed(const u32* p) { u32 v; asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
 __device__ __forceinline__ void red_add(float* p, float v) { asm volatile("red.relaxed.gpu.global.add.f32 [%0], %1;" :: "l"(p), "f"(v) : "memory"); }
@@ -171,6 +178,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define MISC_POS (MISC_BEST + SB * NW * 8)                        // V_B ints
 #define MISC_STAT (MISC_POS + V_B * 4)                            // 8 x 2 floats
 #define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
+#define MISC_STOP (MISC_FLAG + 4)                                 // one int: the consumers are leaving
 #define SM_MISC_BYTES (MISC_FLAG + 16)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
 #define SM_TOTAL (SM_BARS + 2 * V_NSLOT * 8)
@@ -202,10 +210,11 @@ __device__ __noinline__ void give_up(u32* bar, u32 where, int cta) {
 }
 
 // slow path of a shared-memory barrier wait; returns false when the wait was abandoned
-__device__ __noinline__ bool mbar_wait_slow(u32* bar, u32 mbar, u32 parity, u32 where, int cta) {
+__device__ __noinline__ bool mbar_wait_slow(u32* bar, u32 mbar, u32 parity, u32 where, int cta, const volatile int* stop) {
     const u64 t0 = now_ns();
     u32 spins = 0;
     while (!mbar_try(mbar, parity)) {
+        if (*stop) return false;                      // the consumers of this CTA have left (the launch ended early)
         if ((++spins & 63u) == 0) {
             if (ld_relaxed(bar + BAR_ABORT)) return false;
             if (now_ns() - t0 > WAIT_NS) { give_up(bar, where, cta); return false; }
@@ -215,7 +224,7 @@ __device__ __noinline__ bool mbar_wait_slow(u32* bar, u32 mbar, u32 parity, u32 
 }
 __device__ __forceinline__ void wait_mbar(Ctx& c, u32 mbar, u32 parity, u32 where) {
     if (c.dead || mbar_try(mbar, parity)) return;
-    if (!mbar_wait_slow(c.bar, mbar, parity, where, c.cta)) c.dead = true;
+    if (!mbar_wait_slow(c.bar, mbar, parity, where, c.cta, reinterpret_cast<const volatile int*>(c.smem + SM_MISC + MISC_STOP))) c.dead = true;
 }
 
 // Grid barrier for the consumer warps of all CTAs, in two halves so that loads that do not depend
@@ -250,14 +259,14 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 // ---------------------------------------------------------------------------------------------
 // producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
-__device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta) {
+__device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta, int nsteps) {
     Ctx c;
     c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta;
     const unsigned char* base = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
 #pragma unroll 1
-    for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
-        const int l = ph / PH_PER_LAYER;
-        const int first = (l == V_L) ? PH_LOGITS : (ph - l * PH_PER_LAYER == 3 ? PH_FC : ph - l * PH_PER_LAYER);
+    for (int ph = 0; ph < nsteps * (V_L * PH_PER_LAYER + 1); ph++) {          // every step reads the same stream again
+        const int l = (ph % (V_L * PH_PER_LAYER + 1)) / PH_PER_LAYER, pl = ph % (V_L * PH_PER_LAYER + 1);
+        const int first = (l == V_L) ? PH_LOGITS : (pl - l * PH_PER_LAYER == 3 ? PH_FC : pl - l * PH_PER_LAYER);
         if (first == PH_ATT) continue;
         const int last = (first == PH_FC) ? PH_P2 : first;
 #pragma unroll 1
@@ -274,7 +283,15 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
                     for (int r = 0; r < s.rows; r += rpc) {
                         const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
                         wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
-                        if (c.dead) return;
+                        if (c.dead) {
+                            // leaving early: first let the copies still in flight land (bounded), so that none
+                            // writes into shared memory after the CTA has gone
+                            for (u32 k = c.chunk > V_NSLOT ? c.chunk - V_NSLOT : 0u; k < c.chunk; k++) {
+                                const u64 t0 = now_ns();
+                                while (!mbar_try(full_bar(c, k % V_NSLOT), (k / V_NSLOT) & 1u) && now_ns() - t0 < WAIT_NS) { }
+                            }
+                            return;
+                        }
                         const u32 bytes = (u32)(min(rpc, s.rows - r) * width) * FRAG_BYTES;
                         mbar_expect(full_bar(c, slot), bytes);
                         bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, bytes, full_bar(c, slot));
@@ -793,6 +810,7 @@ struct Args {
     const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
+    int nsteps;                                 // decode steps in this launch (the kernel feeds itself between them)
 };
 
 #if V_TIMING
@@ -824,7 +842,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         int bad = 0;
 #pragma unroll 1
         for (int b = c.tid; b < V_B; b += NTHREADS) {
-            const int tb = a.t[b * V_TSTRIDE], xb = a.x[b];
+            const int tb = __ldcg(a.t + b * V_TSTRIDE), xb = __ldcg(a.x + b);
             bad |= (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
             s_pos[b] = tb;
         }
@@ -833,7 +851,12 @@ __device__ __forceinline__ void step_body(const Args& a) {
             return;
         }
     }
+    const int nsteps = max(a.nsteps, 1);
+    int* flag = reinterpret_cast<int*>(smem + SM_MISC + MISC_FLAG);
+    volatile int* stop = reinterpret_cast<volatile int*>(smem + SM_MISC + MISC_STOP);
     if (c.tid == 0) {
+        *stop = 0;
+        if (c.cta == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(0u) : "memory");   // nobody reads it before the first barrier
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -845,7 +868,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
     const int* P = a.PT + c.cta * PT_STRIDE;
     if (c.warp == NW) {
-        if (c.lane == 0) producer(smem, a.bar, P, a.WP, c.cta);
+        if (c.lane == 0) producer(smem, a.bar, P, a.WP, c.cta, nsteps);
         return;
     }
 
@@ -864,11 +887,19 @@ __device__ __forceinline__ void step_body(const Args& a) {
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
 
+#pragma unroll 1
+  for (int step = 0; step < nsteps; step++) {
+    if (step > 0) {
+        // positions as the previous step of this launch left them (published before the step flag)
+#pragma unroll 1
+        for (int b = c.tid; b < V_B; b += NCONS) s_pos[b] = __ldcg(a.t + b * V_TSTRIDE);
+        cons_sync();
+    }
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
 #pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
         const int b = i / V_D, d = i - b * V_D;
-        Z[i] = h2f(a.wte[(size_t)a.x[b] * V_D + d]) + h2f(a.wpe[(size_t)max(s_pos[b], 0) * V_D + d]);
+        Z[i] = h2f(a.wte[(size_t)__ldcg(a.x + b) * V_D + d]) + h2f(a.wpe[(size_t)max(s_pos[b], 0) * V_D + d]);
         Z[ZS + i] = 0.f;
     }
     TICK(0);
@@ -1040,16 +1071,18 @@ __device__ __forceinline__ void step_body(const Args& a) {
     }
     TICK(10);
 
-    // ---- the last CTA to arrive publishes next, feeds it (or the next prompt token) back into x, advances t
-    int* flag = reinterpret_cast<int*>(smem + SM_MISC + MISC_FLAG);
+    // ---- the last CTA to arrive publishes next, feeds it (or the next prompt token) back into x, advances t;
+    //      between the steps of one launch everybody then waits for its step flag
+    const bool final_step = step + 1 == nsteps;
     cons_sync();
     if (c.tid == 0) {
         __threadfence();
-        *flag = (atomicAdd(a.bar + BAR_DONE, 1u) == (u32)c.ncta - 1);
+        flag[0] = (atomicAdd(a.bar + BAR_DONE, 1u) == (u32)c.ncta - 1);
         __threadfence();
     }
     cons_sync();
-    if (*flag) {
+    if (flag[0]) {
+        int bad = 0;
 #pragma unroll 1
         for (int b = c.tid; b < V_B; b += NCONS) {
             const u64 k = atomicExch(gbest + b, 0ull);
@@ -1057,23 +1090,49 @@ __device__ __forceinline__ void step_body(const Args& a) {
             a.S[V_OFF_NEXT + b] = (float)n;
 #if V_FEEDBACK
             int nx = (int)n;
-#if V_PLEN
             const int tn = s_pos[b] + V_TSTEP;
+#if V_PLEN
             if (tn >= 0 && tn < a.plen[b]) nx = a.prompt[(size_t)b * V_PLEN + tn];
 #endif
             a.x_out[b] = (nx < 0 || nx >= V_N) ? 0 : nx;
-            if (V_TSTRIDE) a.t_out[b] = s_pos[b] + V_TSTEP;
+            if (V_TSTRIDE) a.t_out[b] = tn;
+            bad |= (tn >= V_TMAX) | (tn >= V_CPOS);
 #endif
         }
 #if V_FEEDBACK
         if (!V_TSTRIDE && c.tid == 0) a.t_out[0] = s_pos[0] + V_TSTEP;
+#else
+        bad = 0;
 #endif
-        cons_sync();
+        bad = __syncthreads_count_cons(bad);
         if (c.tid == 0) {
-            atomicExch(a.bar + BAR_COUNT, 0u);     // every CTA is past its last barrier
+            const bool stop_now = !final_step && (bad || !V_FEEDBACK || c.dead);        // the next step would leave the cache or the tables
+            if (stop_now && bad) atomicCAS(a.bar + BAR_STATUS, 0u, 0x900u);
             atomicExch(a.bar + BAR_DONE, 0u);
+            if (final_step || stop_now) atomicExch(a.bar + BAR_COUNT, 0u);     // every CTA is past its last barrier
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(final_step ? 0u : (stop_now ? 0xFFFFFFFFu : (u32)(step + 1))) : "memory");
         }
     }
+    if (!final_step) {
+        if (c.tid == 0) {
+            u32 v = 0;
+            if (!c.dead) {
+                const u64 t0 = now_ns();
+                u32 spins = 0;
+                while ((v = ld_acquire(a.bar + BAR_STEP)) != (u32)(step + 1) && v != 0xFFFFFFFFu) {
+                    if ((++spins & 63u) == 0) {
+                        if (ld_relaxed(a.bar + BAR_ABORT)) { v = 0xFFFFFFFFu; break; }
+                        if (now_ns() - t0 > WAIT_NS) { give_up(a.bar, 0x400u, c.cta); v = 0xFFFFFFFFu; break; }
+                    }
+                }
+            } else v = 0xFFFFFFFFu;
+            if (v == 0xFFFFFFFFu) *stop = 1;        // read by the other consumer warps below and by the producer warp
+        }
+        cons_sync();
+        if (*stop) break;
+    }
+  }
     TICK(11);
 #if V_TIMING
     if (c.cta == V_TIMING - 1 && c.lane == 0)

@@ -103,7 +103,7 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(std::string("clear_static_scratch: ") + cudaGetErrorString(e));
 
-    // the step kernel's parameters: residues, then S, bar, TS, packed weights, plan table
+    // the step kernel's parameters: residues, then S, bar, TS, packed weights, plan table, steps per launch
     unsigned long long vals[64];
     void* args[64];
     int n = 0;
@@ -113,6 +113,7 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     vals[n++] = (unsigned long long)(base + COUNTER_WORDS * 4);         // TS
     vals[n++] = packed_weights;
     vals[n++] = plan_table;
+    vals[n++] = 1ull;                                                   // one decode step per launch
     for (int i = 0; i < n; i++) args[i] = &vals[i];
     if (vesta_launch_cooperative(function, grid, block, dynamic_smem, stream, args) != 0)
         return fail(std::string("vesta_step_static: ") + vesta_last_error());

@@ -290,6 +290,22 @@ int vesta_step_run(void* bound, void* stream, int steps) {
     return 0;
 }
 
+int vesta_step_run_fused(void* bound, void* stream, int steps, int per_launch) {
+    if (!bound) return fail(-1, "vesta_step_run_fused: not bound");
+    if (int e = driver()) return e;
+    Bound* b = (Bound*)bound;
+    if (b->vals.empty() || per_launch < 1) return fail(-1, "vesta_step_run_fused: bad argument");
+    while (steps > 0) {
+        const int n = steps < per_launch ? steps : per_launch;
+        b->vals.back() = (unsigned long long)(unsigned)n;          // the kernel's last parameter: steps in this launch
+        CUresult r = g_cu.LaunchCooperative(b->fn, b->grid, 1, 1, b->block, 1, 1, b->smem, (CUstream)stream, b->ptrs.data());
+        if (r != CUDA_SUCCESS) return cu(r, "cuLaunchCooperativeKernel");
+        steps -= n;
+    }
+    b->vals.back() = 1ull;
+    return 0;
+}
+
 void vesta_step_release(void* bound) { delete (Bound*)bound; }
 
 }  // extern "C"

@@ -50,6 +50,7 @@ def lib():
         L.vesta_launch.argtypes = [vp, cu, cu, cu, vp, ctypes.POINTER(vp)]
         L.vesta_step_bind.argtypes = [vp, cu, cu, cu, ci, ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(vp)]
         L.vesta_step_run.argtypes = [vp, vp, ci]
+        L.vesta_step_run_fused.argtypes = [vp, vp, ci, ci]
         L.vesta_step_release.argtypes = [vp]
         L.vesta_step_release.restype = None
         _lib = L
@@ -95,7 +96,7 @@ def compile_cubin(src, arch=ARCH, cache=True):
     return data
 
 
-STATUS_WHERE = {0x100: 'grid barrier', 0x200: 'weight stream (producer)', 0x300: 'weight stream (consumer)',
+STATUS_WHERE = {0x100: 'grid barrier', 0x200: 'weight stream (producer)', 0x300: 'weight stream (consumer)', 0x400: 'step flag',
                 0x900: 'token or position out of range'}
 
 
@@ -144,6 +145,8 @@ class Kernel:
             self.PT = torch.from_numpy(np.ascontiguousarray(lowered.place)).to(self.device)
             self.WP = torch.empty(max(lowered.packed_bytes, 512), dtype=torch.uint8, device=self.device)
             self.args, self.keep, self._bound = None, None, None
+            self.fuse = 16                                       # decode steps per launch in launch(steps > 1)
+            self.feeds_back = '#define V_FEEDBACK 1' in lowered.src
             self.launches = 0
 
     def view(self, name):
@@ -162,7 +165,7 @@ class Kernel:
             assert t.is_cuda and t.dtype == TORCH_DT[dt] and t.is_contiguous(), (name, t.dtype, dt)
             assert t.device == self.device, (name, t.device)
             vals.append(t.data_ptr())
-        vals += [self.S.data_ptr(), self.bar.data_ptr(), self.TS.data_ptr(), self.WP.data_ptr(), self.PT.data_ptr()]
+        vals += [self.S.data_ptr(), self.bar.data_ptr(), self.TS.data_ptr(), self.WP.data_ptr(), self.PT.data_ptr(), 1]
         self.args = (tuple(vals), tuple([ctypes.c_void_p] * len(vals)))
         self.keep = residue
         if self._bound:
@@ -184,10 +187,18 @@ class Kernel:
         with torch.cuda.device(self.device):
             ok(L.vesta_launch(self.pack_fn, nblk, 256, 0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ptrs))
 
-    def launch(self, steps=1):
-        """`steps` decode steps, back to back on the current stream"""
-        ok(lib().vesta_step_run(self._bound, ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream), steps))
-        self.launches += steps
+    def launch(self, steps=1, per_launch=None):
+        """`steps` decode steps on the current stream. With feedback on, up to `per_launch` steps (default
+        Kernel.fuse) run inside one launch: the kernel feeds its own token and position between them, which saves
+        the gap between launches; without feedback every step is its own launch."""
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        per = per_launch or self.fuse
+        if steps > 1 and per > 1 and self.feeds_back:
+            ok(lib().vesta_step_run_fused(self._bound, stream, steps, per))
+            self.launches += -(-steps // per)
+        else:
+            ok(lib().vesta_step_run(self._bound, stream, steps))
+            self.launches += steps
 
     def __call__(self, residue):
         self.bind(residue)

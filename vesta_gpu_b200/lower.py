@@ -424,7 +424,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
     R = {k: 'R_' + v for k, v in roles.items()}
     step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
-                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
+                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT', 'int nsteps'])
     fill = [f'a.x = {R["x"]}; a.t = {R["t"]};']
     for k in ('wte', 'wpe', 'ln1w', 'ln1b', 'qkvb', 'ob', 'ln2w', 'ln2b', 'fcb', 'pb', 'lnfw', 'lnfb'):
         fill.append(f'a.{k} = {R[k]};')
@@ -434,7 +434,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     else:
         fill.append('a.x_out = 0; a.t_out = 0;')
     fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
-    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT;')
+    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.nsteps = nsteps;')
     pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
     pack_params = [roles[k] for k in pack_roles]
     pack_sig = ', '.join([f'const unsigned short* __restrict__ R_{roles[k]}' for k in pack_roles]
