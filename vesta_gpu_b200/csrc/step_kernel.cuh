@@ -168,8 +168,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define SM_KV (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)             // K/V tiles of the attention phase
 #define SM_ACT (SM_KV + 2 * 2 * NW * 16 * 144)                    // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * ATILE)                    // B operands of the MLP projection (GELU output)
-#define SM_ZS (SM_GACT + WN_MAX * V_NB * ATILE)                   // eight fp32 rows staged for LayerNorm
-#define SM_RED (SM_ZS + (V_LN_DIST ? 0 : 8 * (V_D + 8) * 4))          // NARROW partial sums, one tile per warp
+#define SM_RED (SM_GACT + WN_MAX * V_NB * ATILE)                  // NARROW partial sums, one tile per warp
 #define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
 #define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
 #define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
@@ -195,7 +194,7 @@ struct Ctx {
 #endif
 };
 #if V_TIMING
-#define TRACE_EVENTS 56
+#define TRACE_EVENTS 96
 #define TRACE(id) do { if (c.tron && c.lane == 0 && c.trn < TRACE_EVENTS) c.trbuf[c.warp * TRACE_EVENTS + c.trn++] = ((u64)(id) << 48) | ((u64)clock64() & 0xFFFFFFFFFFFFull); } while (0)
 #else
 #define TRACE(id) do { } while (0)
@@ -252,6 +251,7 @@ __device__ __noinline__ bool grid_wait_slow(u32* bar, u32 gen, int cta) {
 }
 __device__ __forceinline__ void phase_wait(Ctx& c) {
     if (c.tid == 0 && !c.dead) grid_wait_slow(c.bar, c.gen, c.cta);
+    cp_wait();                                 // this thread's share of the parameters (and of a first K/V tile) has landed
     cons_sync();
     if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
 }
@@ -326,6 +326,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
         for (int base = 0; base < total; base += per) {
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
             wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            TRACE(53);
             const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) + (size_t)c.lane * 16;
             const int nr = c.dead ? 0 : min(rpc, rows - row);
 #pragma unroll 2
@@ -355,6 +356,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
         for (int base = 0; base < total; base += per) {
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
             wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            TRACE(53);
             const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES + (size_t)c.lane * 16;
             const int lim = c.dead ? 0 : min(base + per, total);
 #pragma unroll 2
@@ -422,82 +424,87 @@ __device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* g
 }
 
 // LayerNorm of `nrows` rows of z (global, fp32, row stride V_D: one slab) into the operand tiles; gain and shift come
-// from the parameter block in shared memory. The rows are staged in shared memory (row stride
-// ZS_STRIDE floats, which spreads the rows over the banks), one warp per row computes mean and
-// variance (two passes), then every warp converts whole operand tiles: lane (b, t) of a tile
-// produces exactly its 16 bytes (head and remainder of the elements 2t, 2t+1, 2t+8, 2t+9 of row b),
-// one conflict-free 128-bit store. The same pass starts the vector the following projection is
-// combined into: init[b][d] += z[b][d] + bias[d], the fold tiles dealt over the CTAs (init was
-// zeroed a phase earlier).
-#define ZS_STRIDE (V_D + 8)
+// from the parameter block in shared memory. One warp per row, the row held in registers: lane (u, t) loads the
+// elements 2t, 2t+1, 2t+8, 2t+9 of the fold tiles u, u + 8, ... (all loads independent: one round trip to L2),
+// mean and variance by two warp reductions, then the lane writes exactly the 16 bytes that thread (row, t) of the
+// contraction reads from each of its tiles (head and remainder of its four elements). Rows of the slab beyond
+// `nrows` are written as zeros. The same pass starts the vector the following projection is combined into:
+// init[b][d] += z[b][d] + bias[d], the fold tiles dealt over the CTAs (init was zeroed a phase earlier).
+#define LNI ((KT_D + 7) / 8)
 __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* act, int nrows) {
     const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
-    float* zs = reinterpret_cast<float*>(c.smem + SM_ZS);
-    float* stat = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_STAT);
-    const int bl = c.lane >> 2, t = c.lane & 3;
-    // eight rows (one batch tile of the operand) at a time
+    const int u = c.lane >> 2, t = c.lane & 3;
 #pragma unroll 1
-    for (int nb = 0; nb < V_NB; nb++) {
-        const int r0 = nb * 8, nr = min(8, nrows - r0);        // nr <= 0: the tile is written as zeros
-#pragma unroll 1
-        for (int i = c.tid; i < nr * G4; i += NCONS) {
-            const int b = i / G4, g = i - b * G4;
-            cp16(zs + b * ZS_STRIDE + g * 4, z + (size_t)(r0 + b) * V_D + g * 4);
-        }
-        cp_wait();
-        cons_sync();
-        TRACE(40);
-#pragma unroll 1
-        for (int b = c.warp; b < nr; b += NW) {
-            const float4* row = reinterpret_cast<const float4*>(zs + b * ZS_STRIDE);
-            float s = 0.f;
-#pragma unroll 4
-            for (int g = c.lane; g < G4; g += 32) { const float4 v = row[g]; s += (v.x + v.y) + (v.z + v.w); }
+    for (int rb = c.warp; rb < SB; rb += NW) {
+        unsigned char* dst = act + ((size_t)(rb >> 3) * 32 + (rb & 7) * 4 + t) * ALB;
+        if (rb >= nrows) {
 #pragma unroll
-            for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
-            const float mean = s * (1.0f / V_D);
-            float q = 0.f;
-#pragma unroll 4
-            for (int g = c.lane; g < G4; g += 32) {
-                const float4 v = row[g];
-                const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
-                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
-            }
-#pragma unroll
-            for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-            if (c.lane == 0) { stat[2 * b] = mean; stat[2 * b + 1] = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS); }
-        }
-        cons_sync();
-        TRACE(41);
-#pragma unroll 2
-        for (int kt = c.warp; kt < KT_D; kt += NW) {
-            const int k = kt * 16 + 2 * t;
-            uint4 out = make_uint4(0, 0, 0, 0);
-            if (bl < nr) {
-                const float2 v0 = *reinterpret_cast<const float2*>(zs + bl * ZS_STRIDE + k);
-                const float2 v1 = *reinterpret_cast<const float2*>(zs + bl * ZS_STRIDE + k + 8);
-                const float mean = stat[2 * bl], rs = stat[2 * bl + 1];
-                const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
-                const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
-                const float o0 = (v0.x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0.y - mean) * rs * h_hi(w0) + h_hi(s0);
-                const float o2 = (v1.x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1.y - mean) * rs * h_hi(w1) + h_hi(s1);
-                out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
-                out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
-                if (init && (kt % c.ncta) == c.cta) {
-                    const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
-                    float* dst = init + (size_t)(r0 + bl) * V_D + k;
-                    red_add(dst, v0.x + h_lo(i0)); red_add(dst + 1, v0.y + h_hi(i0));
-                    red_add(dst + 8, v1.x + h_lo(i1)); red_add(dst + 9, v1.y + h_hi(i1));
+            for (int i = 0; i < LNI; i++) {
+                const int kt = u + 8 * i;
+                if (kt < KT_D) {
+#if V_ACT_LO
+                    *reinterpret_cast<uint4*>(dst + (size_t)kt * V_NB * ATILE) = make_uint4(0, 0, 0, 0);
+#else
+                    *reinterpret_cast<uint2*>(dst + (size_t)kt * V_NB * ATILE) = make_uint2(0, 0);
+#endif
                 }
             }
-#if V_ACT_LO
-            *reinterpret_cast<uint4*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * ALB) = out;
-#else
-            *reinterpret_cast<uint2*>(act + ((size_t)(kt * V_NB + nb) * 32 + c.lane) * ALB) = make_uint2(out.x, out.y);
-#endif
+            continue;
         }
-        cons_sync();
+        const float* row = z + (size_t)rb * V_D + 2 * t;
+        float2 v0[LNI], v1[LNI];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNI; i++) {
+            const int kt = u + 8 * i;
+            v0[i] = make_float2(0.f, 0.f); v1[i] = make_float2(0.f, 0.f);
+            if (kt < KT_D) {
+                v0[i] = __ldcg(reinterpret_cast<const float2*>(row + kt * 16));
+                v1[i] = __ldcg(reinterpret_cast<const float2*>(row + kt * 16 + 8));
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < LNI; i++) s += (v0[i].x + v0[i].y) + (v1[i].x + v1[i].y);
+#pragma unroll
+        for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+        const float mean = s * (1.0f / V_D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNI; i++) {
+            if (u + 8 * i < KT_D) {
+                const float a0 = v0[i].x - mean, a1 = v0[i].y - mean, a2 = v1[i].x - mean, a3 = v1[i].y - mean;
+                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
+        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+#pragma unroll
+        for (int i = 0; i < LNI; i++) {
+            const int kt = u + 8 * i, k = kt * 16 + 2 * t;
+            if (kt < KT_D) {
+                const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
+                const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
+                const float o0 = (v0[i].x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0[i].y - mean) * rs * h_hi(w0) + h_hi(s0);
+                const float o2 = (v1[i].x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1[i].y - mean) * rs * h_hi(w1) + h_hi(s1);
+                uint4 out;
+                out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
+#if V_ACT_LO
+                out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
+                *reinterpret_cast<uint4*>(dst + (size_t)kt * V_NB * ATILE) = out;
+#else
+                *reinterpret_cast<uint2*>(dst + (size_t)kt * V_NB * ATILE) = make_uint2(out.x, out.y);
+#endif
+                if (init && (kt % c.ncta) == c.cta) {
+                    const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
+                    float* o = init + (size_t)rb * V_D + k;
+                    red_add(o, v0[i].x + h_lo(i0)); red_add(o + 1, v0[i].y + h_hi(i0));
+                    red_add(o + 8, v1[i].x + h_lo(i1)); red_add(o + 9, v1[i].y + h_hi(i1));
+                }
+            }
+        }
     }
+    cons_sync();
 }
 
 // Distributed LayerNorm (batches of more than two batch tiles): instead of every CTA normalising every row
@@ -863,7 +870,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
     // operand tiles and K/V stages start as zero: rows of a batch tile beyond the batch stay zero for the whole
     // launch, and staged rows past the end of a chunk only ever meet a weight of zero
 #pragma unroll 1
-    for (int i = c.tid; i < (SM_ZS - SM_KV) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_KV)[i] = make_uint4(0, 0, 0, 0);
+    for (int i = c.tid; i < (SM_RED - SM_KV) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_KV)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
     const int* P = a.PT + c.cta * PT_STRIDE;
@@ -968,13 +975,16 @@ __device__ __forceinline__ void step_body(const Args& a) {
                 for (int j = 0; j < sg.nj; j += (sg.wide ? WG : WN_MAX * 4)) {
                     const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
                     float acc[TPW][V_NB][4];
+                    TRACE(50);
                     gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
+                    TRACE(51);
                     if (!sg.wide) {
                         // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
 #pragma unroll
                         for (int nb = 0; nb < V_NB; nb++)
                             *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[0][nb][0], acc[0][nb][1], acc[0][nb][2], acc[0][nb][3]);
                         cons_sync();
+                        TRACE(52);
 #pragma unroll 1
                         for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
                             const int jj = o / (V_NB * 128), r = o - jj * (V_NB * 128);

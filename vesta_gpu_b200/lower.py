@@ -366,7 +366,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     atile = 512 if act_lo else 256
 
     def smem_fixed(nb):
-        return (2 * 2 * NW * 16 * 144 + KT_D * nb * atile + WN_MAX * nb * atile + (0 if ln_dist else 8 * (D + 8) * 4) + NW * nb * 512
+        return (2 * 2 * NW * 16 * 144 + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
                 + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
