@@ -14,6 +14,7 @@ def stream_tiles(rec, dims, cta):
     D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
     KT_D, JT_D = D // 16, D // 16
     base, layer, qj0, qnj, pj0, pnj, pk0, pnk, fj0, fnj, lj0, lnj = [int(v) for v in rec[cta][:12]]
+    WG = dims['WG']                                  # output tiles per WIDE group of this lowering
 
     def narrow(kind, l, j0, nj, kt):
         return [(kind, l, j0 + i % nj, i // nj) for i in range(nj * kt)]
@@ -21,10 +22,10 @@ def stream_tiles(rec, dims, cta):
     def wide(kind, l, j0, nj, k0, nk):
         out = []
         for i in range(nj * nk):
-            grp = i // (lw.WG * nk)
-            width = min(lw.WG, nj - grp * lw.WG)
-            r = i - grp * lw.WG * nk
-            out.append((kind, l, j0 + grp * lw.WG + r % width, k0 + r // width))
+            grp = i // (WG * nk)
+            width = min(WG, nj - grp * WG)
+            r = i - grp * WG * nk
+            out.append((kind, l, j0 + grp * WG + r % width, k0 + r // width))
         return out
     tiles = []
     for l in range(L):

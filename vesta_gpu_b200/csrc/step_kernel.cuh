@@ -40,7 +40,9 @@ typedef unsigned short u16;
 #define JT_D (V_D / 16)
 #define FRAG_BYTES 512
 #define WN_MAX 4                      // widest NARROW placement (output tiles per CTA)
-#define TPW 2                         // output tiles a warp owns in a WIDE group
+#define TPW V_TPW                     // output tiles a warp owns in a WIDE group (more where the batch is small:
+                                      // independent accumulators hide the latency of the tensor pipe)
+#define NT (V_NB <= 2 ? 4 : 2)        // NARROW: tiles of a chunk a warp loads before it starts their products
 #define WG (TPW * NW)                  // output tiles per WIDE group
 #define G4 (V_D / 4)                  // float4 groups per activation row
 #define ALB (V_ACT_LO ? 16 : 8)        // bytes per lane of an operand tile: fp16 head (b0, b1) and, if kept, the fp16 remainder
@@ -320,7 +322,9 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             for (int i = 0; i < 4; i++) { acc[t][nb][i] = 0.f; lo[t][nb][i] = 0.f; }
     const int rpc = V_CH / width, per = rpc * width, total = rows * width;
     if (wide) {
-        const bool own0 = c.warp < width, own1 = c.warp + NW < width;
+        bool own[TPW];
+#pragma unroll
+        for (int t = 0; t < TPW; t++) own[t] = c.warp + t * NW < width;
         int row = 0;
 #pragma unroll 1
         for (int base = 0; base < total; base += per) {
@@ -332,15 +336,16 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
 #pragma unroll 2
             for (int r = 0; r < nr; r++) {
                 const unsigned char* tp = tiles + (size_t)(r * width + c.warp) * FRAG_BYTES;
-                uint4 a0 = make_uint4(0, 0, 0, 0), a1 = make_uint4(0, 0, 0, 0);
-                if (own0) a0 = lds128(tp);
-                if (own1) a1 = lds128(tp + NW * FRAG_BYTES);
+                uint4 a[TPW], b[V_NB];
 #pragma unroll
-                for (int nb = 0; nb < V_NB; nb++) {
-                    const uint4 b = lds_act(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * ALB);
-                    if (own0) { mma16816(acc[0][nb], a0, b.x, b.y); if (V_ACT_LO) mma16816(lo[0][nb], a0, b.z, b.w); }
-                    if (own1) { mma16816(acc[1][nb], a1, b.x, b.y); if (V_ACT_LO) mma16816(lo[1][nb], a1, b.z, b.w); }
-                }
+                for (int t = 0; t < TPW; t++) a[t] = own[t] ? lds128(tp + t * NW * FRAG_BYTES) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int nb = 0; nb < V_NB; nb++) b[nb] = lds_act(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * ALB);
+#pragma unroll
+                for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
+                    for (int t = 0; t < TPW; t++)
+                        if (own[t]) { mma16816(acc[t][nb], a[t], b[nb].x, b[nb].y); if (V_ACT_LO) mma16816(lo[t][nb], a[t], b[nb].z, b[nb].w); }
             }
             row += rpc;
             __syncwarp();
@@ -359,16 +364,31 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             TRACE(53);
             const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES + (size_t)c.lane * 16;
             const int lim = c.dead ? 0 : min(base + per, total);
-#pragma unroll 2
-            for (; f < lim; f += stride, row += cnt) {
-                const uint4 a = lds128(tiles + (size_t)f * FRAG_BYTES);
+            int mine = f < lim ? (lim - f + stride - 1) / stride : 0;            // this warp's tiles in the chunk
+#pragma unroll 1
+            for (; mine > 0; mine -= NT, f += NT * stride, row += NT * cnt) {
+                // all loads of up to NT tiles first, then their products: the loads and the first product's latency overlap
+                uint4 a[NT], b[NT][V_NB];
 #pragma unroll
-                for (int nb = 0; nb < V_NB; nb++) {
-                    const uint4 b = lds_act(act + ((size_t)(row * V_NB + nb) * 32 + c.lane) * ALB);
-                    mma16816(acc[0][nb], a, b.x, b.y);
-                    if (V_ACT_LO) mma16816(lo[0][nb], a, b.z, b.w);
+                for (int i = 0; i < NT; i++) {
+                    if (i < mine) {
+                        a[i] = lds128(tiles + (size_t)(f + i * stride) * FRAG_BYTES);
+#pragma unroll
+                        for (int nb = 0; nb < V_NB; nb++) b[i][nb] = lds_act(act + ((size_t)((row + i * cnt) * V_NB + nb) * 32 + c.lane) * ALB);
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < NT; i++) {
+                    if (i < mine) {
+#pragma unroll
+                        for (int nb = 0; nb < V_NB; nb++) {
+                            mma16816(acc[0][nb], a[i], b[i][nb].x, b[i][nb].y);
+                            if (V_ACT_LO) mma16816(lo[0][nb], a[i], b[i][nb].z, b[i][nb].w);
+                        }
+                    }
                 }
             }
+            if (mine < 0) { f += mine * stride; row += mine * cnt; }             // the last batch was not full
             __syncwarp();
             if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
             c.chunk++;
@@ -468,6 +488,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
 #pragma unroll
         for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
         const float mean = s * (1.0f / V_D);
+        TRACE(40);
         float q = 0.f;
 #pragma unroll
         for (int i = 0; i < LNI; i++) {
@@ -479,6 +500,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
 #pragma unroll
         for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
         const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        TRACE(41);
 #pragma unroll
         for (int i = 0; i < LNI; i++) {
             const int kt = u + 8 * i, k = kt * 16 + 2 * t;
@@ -503,6 +525,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
                 }
             }
         }
+        TRACE(42);
     }
     cons_sync();
 }
@@ -717,8 +740,10 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
             fresh = false;
         }
+        TRACE(44);
         asm volatile("cp.async.wait_group 1;" ::: "memory");       // this tile has landed; the next one may be in flight
         cons_sync();
+        TRACE(45);
         const unsigned char* kt = c.smem + SM_KV + stage * KV_STAGE_BYTES;
         const unsigned char* vt = kt + KV_POS * KV_ROW;
         const int cnt = min(KV_POS, cur.hi - cur.s);
@@ -768,6 +793,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 mma_r(o[mt], a, b0, b1);
             }
         }
+        TRACE(46);
         const bool last = cur.s + KV_POS >= cur.hi;
         float* out = part + (size_t)cur.it * PART_STRIDE;
         float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);

@@ -33,8 +33,8 @@ KERNEL_TEXT = Path(__file__).resolve().parent / 'csrc' / 'step_kernel.cuh'
 
 CTYPE = {'f32': 'float', 'f16': 'unsigned short', 'i32': 'int'}
 NW = 8                 # consumer warps per CTA (one more warp streams the weights)
-WG = 2 * NW            # output tiles per WIDE group: two per consumer warp
-CHUNK_TILES = 32       # 16 KB ring slots
+WG = 2 * NW            # output tiles per unit of the attention projection (placement)
+CHUNK_TILES = 32       # ring slots of at least 16 KB (a slot holds at least one row of a WIDE group)
 WN_MAX = 4             # widest NARROW placement
 PT_STRIDE = 16
 SMEM_LIMIT = 227 * 1024
@@ -374,6 +374,11 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         NB = min(NB, int(slab_tiles))
     while NB > 1 and (budget - smem_fixed(NB) - 1024) // (CHUNK_TILES * 512 + 16) < 3:
         NB -= 1
+    # WIDE groups: output tiles per warp. More than two (tried: six at batch <= 8) gave nothing on B200: the
+    # contractions of a small batch are bound by the latency of their few dependent steps, not by issue slots.
+    tpw = int(tune.get('tpw', 2))
+    wg = tpw * NW
+    ch = max(CHUNK_TILES, wg)
     rec, tiles, notes = place_step(dims, grid)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
@@ -396,18 +401,18 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     fixed = smem_fixed(NB)
-    nslot = (budget - fixed - 1024) // (CHUNK_TILES * 512 + 16)
+    nslot = (budget - fixed - 1024) // (ch * 512 + 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget at this batch')
     nslot = min(nslot, 16)
-    shared = fixed + nslot * (CHUNK_TILES * 512 + 16) + 512
+    shared = fixed + nslot * (ch * 512 + 16) + 512
 
     def f32(v):
         return repr(float(np.float32(v))) + 'f'
     scale = dims['scale']
     defs = dict(V_NW=NW, V_B=B, V_NB=NB, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
                 V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
-                V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=CHUNK_TILES, V_ACT_LO=int(bool(act_lo)),
+                V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
                 V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
@@ -465,5 +470,5 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                   barriers_per_launch=1 + 4 * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
-                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes), roles=roles)
+                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch), roles=roles)
     return low
