@@ -66,6 +66,13 @@ int vesta_launch_cluster(void* function, unsigned grid, unsigned block, unsigned
  * decode steps back to back on `stream` without returning to the caller in between. */
 int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
                     int n_args, const unsigned long long* device_pointers, void** bound);
+/* A TMA descriptor (128 bytes, written to `out` in host memory; copy it to 64-byte aligned device memory) for a
+ * cache of fp16 rows laid out [planes][rows][row_elems]: one copy brings `box_rows` consecutive rows of 64
+ * elements (128 bytes, one head) of one plane into shared memory with the 128-byte swizzle. The step kernel
+ * reads its K and V tiles through four of these (K and V, boxes of 128 and of 32 rows). No counterpart in the
+ * reference, whose generated folds read the cache with ordinary vector loads (vesta/lower.py:947-956). */
+int vesta_tensor_map_rows(void* out, const void* base, unsigned long long row_elems, unsigned long long rows,
+                          unsigned long long planes, unsigned box_elems, unsigned box_rows);
 int vesta_step_run(void* bound, void* stream, int steps);
 /* The same, with up to `per_launch` decode steps inside one launch (the kernel's last parameter is the number
  * of steps; it feeds its own token and position between them). The bound argument list must end with that
@@ -79,7 +86,8 @@ void vesta_step_release(void* bound);
  * vesta_launch_cooperative would, but with the kernel's work space (fp32 scratch, counters, timing
  * sums, normally allocated by the caller) in a fixed array inside the library's device image,
  * vesta_static_scratch_bytes() bytes (4 MiB) per GPU for the life of the process. The caller passes
- * the residues (inputs, the KV cache), the packed weights and the plan table it already owns, the
+ * the residues (inputs, the KV cache), the packed weights, the plan table and the four K/V cache
+ * descriptors (vesta_tensor_map_rows, in device memory) it already owns, the
  * sizes the lowering reported (scratch_floats, counters) and where the logits and next lie in the
  * scratch; the results are copied to logits_out / next_out (device or pinned host memory) on
  * `stream`. Allocates nothing; a step that needs more scratch than the array holds is refused with
@@ -92,6 +100,7 @@ const char* vesta_static_last_error(void);
 int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
                       int n_residues, const unsigned long long* residue_pointers,
                       unsigned long long packed_weights, unsigned long long plan_table,
+                      unsigned long long tensor_maps,
                       size_t scratch_floats, size_t counters,
                       size_t logit_offset, size_t logit_count, float* logits_out,
                       size_t next_offset, size_t next_count, float* next_out,

@@ -130,6 +130,8 @@ def test_against_oracle_other_batches(batch):
     (33, 2, dict(ln_dist=True, act_lo=False)),         # ... with fp16-head operand tiles (the large-batch mode)
     (5, None, dict(ln_dist=True)),                     # ... at a batch below one tile
     (20, 1, dict(ln_dist=False, act_lo=True)),         # every CTA normalises its slab, head + remainder
+    (60, None, None),                                  # more (sequence, head) items than CTAs: several per CTA
+    (60, None, dict(kv_stages=2, nch=2)),              # ... with two K/V stages and two position chunks per item
 ])
 def test_batches_above_one_slab(batch, slab_tiles, tune):
     """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged), in both

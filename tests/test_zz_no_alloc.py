@@ -21,7 +21,7 @@ from helpers import TIGHT
 pytestmark = pytest.mark.gpu
 
 
-def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=None):
+def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=None, tmaps=None):
     low = k.lowered
     ptrs = [residues[name].data_ptr() for name, _, _ in low.params]
     arr = (ctypes.c_ulonglong * len(ptrs))(*ptrs)
@@ -29,6 +29,7 @@ def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=N
     no, _, nshape = low.scratch['next']
     return lib.vesta_step_static(k.fn, k.grid, k.block, k.smem, len(ptrs), arr,
                                  ctypes.c_ulonglong(k.WP.data_ptr()), ctypes.c_ulonglong(k.PT.data_ptr()),
+                                 ctypes.c_ulonglong(tmaps.data_ptr()),
                                  ctypes.c_size_t(low.scratch_floats if scratch_floats is None else scratch_floats),
                                  ctypes.c_size_t(low.counters),
                                  ctypes.c_size_t(lo), ctypes.c_size_t(int(np.prod(lshape))), ctypes.c_void_p(logits_out.data_ptr()),
@@ -59,13 +60,14 @@ def test_static_scratch_step_matches_the_allocating_path():
     mine['t'] = torch.zeros_like(m.t)
     mine['keys'] = torch.zeros_like(m.keys)
     mine['vals'] = torch.zeros_like(m.vals)
+    tmaps = m.k.tensor_maps(mine)                # the caller's own descriptors of its own cache
     logits = torch.empty(B, TINY3.N, dtype=torch.float32, device='cuda')
     nxt = torch.empty(B, dtype=torch.float32, device='cuda')
     stream = torch.cuda.current_stream().cuda_stream
 
     for step in range(2):                       # two calls in a row: the second one finds the first one's leftovers
         m.step()
-        rc = static_step(lib, m.k, mine, stream, logits, nxt)
+        rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps)
         assert rc == 0, lib.vesta_static_last_error()
         torch.cuda.synchronize()
         assert torch.allclose(logits, m.logits(), atol=TIGHT, rtol=0), step
@@ -76,7 +78,7 @@ def test_static_scratch_step_matches_the_allocating_path():
 
     # a step that needs more work space than the library holds is refused, with a message, and launches nothing
     before = logits.clone()
-    rc = static_step(lib, m.k, mine, stream, logits, nxt, scratch_floats=(4 << 20))
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, scratch_floats=(4 << 20), tmaps=tmaps)
     assert rc != 0 and b'static scratch holds' in lib.vesta_static_last_error()
     torch.cuda.synchronize()
     assert torch.equal(before, logits)

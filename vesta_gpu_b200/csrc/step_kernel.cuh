@@ -168,27 +168,29 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 // ---------------------------------------------------------------------------------------------
 #define SM_RING 0
 #define SM_KV (SM_RING + V_NSLOT * V_CH * FRAG_BYTES)             // K/V tiles of the attention phase
-#define SM_ACT (SM_KV + 2 * 2 * NW * 16 * 144)                    // B operands of the current contraction
+#define SM_ACT (SM_KV + V_KVST * 2 * NW * 16 * 128)                // B operands of the current contraction
 #define SM_GACT (SM_ACT + KT_D * V_NB * ATILE)                    // B operands of the MLP projection (GELU output)
 #define SM_RED (SM_GACT + WN_MAX * V_NB * ATILE)                  // NARROW partial sums, one tile per warp
 #define SM_PRM (SM_RED + NW * V_NB * 512)                         // LayerNorm gain, shift, residual bias, tile bias
 #define SM_PRM_BYTES ((3 * V_D + WN_MAX * 16) * 2)
 #define SM_MISC ((SM_PRM + SM_PRM_BYTES + 15) & ~15)
-#define MISC_ATT 0                                                // NW x (V_E + 2) floats
-#define MISC_BEST (((NW * (V_E + 2) * 4) + 7) & ~7)               // SB x NW u64
+#define MISC_ATT 0                                                // 2 x NW x (V_E + 2) floats (items alternate)
+#define MISC_BEST (((2 * NW * (V_E + 2) * 4) + 15) & ~15)         // SB x NW u64
 #define MISC_POS (MISC_BEST + SB * NW * 8)                        // V_B ints
-#define MISC_STAT (MISC_POS + V_B * 4)                            // 8 x 2 floats
+#define MISC_STAT ((MISC_POS + V_B * 4 + 15) & ~15)                // 8 x 2 floats
 #define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
 #define MISC_STOP (MISC_FLAG + 4)                                 // one int: the consumers are leaving
-#define SM_MISC_BYTES (MISC_FLAG + 16)
+#define MISC_SIDE (MISC_FLAG + 16)                                // per K/V stage: the K row and the V row of the current position
+#define SM_MISC_BYTES (MISC_SIDE + V_KVST * 256)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
-#define SM_TOTAL (SM_BARS + 2 * V_NSLOT * 8)
+#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + V_KVST) * 8)
 
 struct Ctx {
     unsigned char* smem;
     u32* bar;          // global counters
     u32 gen;           // barrier generation x CTAs
     u32 chunk;         // stream chunks consumed so far (same value in every consumer warp and the producer)
+    u32 kvi, kvn;      // K/V tiles requested / used so far (stage = count % V_KVST)
     int cta, ncta, tid, warp, lane;
     bool dead;         // a bounded wait expired somewhere: skip waits from now on
 #if V_TIMING
@@ -626,10 +628,13 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 
 // ---------------------------------------------------------------------------------------------
 // attention: this CTA's work items are (sequence, head, chunk of the positions); an item is processed
-// in tiles of KV_POS positions whose K and V rows (128 B each per head) are copied into shared memory
-// with cp.async, two tiles ahead of the arithmetic, so that the cache streams while the softmax runs.
-// The first tile is requested before the grid barrier that ends the QKV phase; the row of the current
-// position (written during that phase by another CTA) is fetched after the barrier.
+// in tiles of KV_POS positions. A tile's K rows and V rows (128 B per position and head) come into shared
+// memory by TMA: one thread issues two tensor copies (cp.async.bulk.tensor, box = KV_POS rows of one head,
+// or KV_SMALL rows when that covers what is left of the item) that complete on the stage's mbarrier; the
+// 128-byte swizzle of the copy spreads the rows over the banks for ldmatrix. V_KVST stages are in flight.
+// The first V_KVST tiles are requested before the grid barrier that ends the QKV phase; the row of the
+// current position, which another CTA writes during that phase, is fetched after the barrier with ordinary
+// asynchronous copies and put in its place before the tile is used.
 // Arithmetic on the tensor pipe: a warp takes 16 positions of the tile. Scores: A = the K rows
 // (ldmatrix, 16 positions x 16 dims per step), B = the query, its fp16 head in column 0 and its fp16
 // remainder in column 1, so that column 0 + column 1 is the fp32-accurate dot product. Online softmax
@@ -638,47 +643,59 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // Result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
 #define KV_POS (NW * 16)                         // positions per tile: sixteen per warp
-#define KV_ROW 144                               // bytes per staged row: 128 of data, 16 of padding (ldmatrix without bank conflicts)
-#define KV_STAGE_BYTES (2 * KV_POS * KV_ROW)     // K rows then V rows
-#define KV_STAGES 2
+#define KV_SMALL 32                              // rows of the small box
+#define KV_TILE_BYTES (KV_POS * 128)             // K (or V) rows of one tile
+#define KV_STAGE_BYTES (2 * KV_TILE_BYTES)       // K rows then V rows
+#define TMAP_BYTES 128                           // descriptors at TM: K, V (boxes of KV_POS rows), K, V (boxes of KV_SMALL rows)
 
 struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
 
 __device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int ncta) {
-    while (a.it < V_B * V_H * V_NCH) {
+    if (a.it < V_B * V_H * V_NCH) {
         const int ch = a.it % V_NCH, bh = a.it / V_NCH;
         a.b = bh / V_H; a.h = bh - a.b * V_H;
         const int n = s_pos[a.b] + 1, cs = (max(n, 1) + V_NCH - 1) / V_NCH;
         a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
-        return;
     }
 }
 __device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < V_B * V_H * V_NCH; }
+__device__ __forceinline__ bool att_has_rows(const AttIter& a) { return a.hi > a.s; }      // an empty chunk is a tile without data
 __device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int ncta) {
     a.s += KV_POS;
     if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
 }
+__device__ __forceinline__ u32 kv_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + stage) * 8; }
+// byte offset of the 16-byte piece `piece` of row `row` in a swizzled tile
+__device__ __forceinline__ int kv_off(int row, int piece) { return row * 128 + ((piece ^ (row & 7)) << 4); }
 
-// request the rows [a.s, min(a.hi, a.s + KV_POS)) of the item into a stage, except position `skip`.
-// Thread i copies the same 16-byte piece of rows i/16, i/16 + NCONS/16, ...: one address, then a constant step.
-__device__ __forceinline__ void att_fetch(Ctx& c, const AttIter& a, const u16* __restrict__ keys, const u16* __restrict__ vals, int l,
-                                          unsigned char* stage, int skip) {
-    const int cnt = min(KV_POS, a.hi - a.s);
-    const int piece = c.tid & 15;
-    int pos = c.tid >> 4;
-    const u16* src = ((piece & 8) ? vals : keys) + ((size_t)(a.b * V_L + l) * V_TMAX + a.s + pos) * V_D + (size_t)a.h * V_E + (piece & 7) * 8;
-    unsigned char* dst = stage + (piece >> 3) * (KV_POS * KV_ROW) + pos * KV_ROW + (piece & 7) * 16;
-#pragma unroll 2
-    for (; pos < cnt; pos += NCONS / 16, src += (size_t)(NCONS / 16) * V_D, dst += (NCONS / 16) * KV_ROW)
-        if (a.s + pos != skip) cp16(dst, src);
-    asm volatile("cp.async.commit_group;" ::: "memory");
+__device__ __forceinline__ void tma_rows(u32 dst, const unsigned char* tmap, int x, int row, int plane, u32 bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 :: "r"(dst), "l"(tmap), "r"(x), "r"(row), "r"(plane), "r"(bar) : "memory");
 }
 
-// the first tile of this CTA, before the barrier: everything but the row of the current position
-__device__ __forceinline__ void attention_prefetch(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, int l, const int* s_pos) {
+// request the tile [a.s, a.s + KV_POS) of item a into the next stage (one thread; every thread counts it)
+__device__ __forceinline__ void att_issue(Ctx& c, const AttIter& a, int l, const unsigned char* __restrict__ TM) {
+    if (c.tid == 0) {
+        const u32 stage = c.kvi % V_KVST;
+        const bool small = a.hi - a.s <= KV_SMALL;
+        const u32 bar = kv_bar(c, stage), dst = smem_u32(c.smem + SM_KV + stage * KV_STAGE_BYTES);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the stage was last written and read with ordinary accesses
+        mbar_expect(bar, small ? 2 * KV_SMALL * 128 : KV_STAGE_BYTES);
+        tma_rows(dst, TM + (small ? 2 : 0) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+        tma_rows(dst + KV_TILE_BYTES, TM + (small ? 3 : 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+    }
+    c.kvi++;
+}
+
+// the first tiles of this CTA, before the barrier (their row of the current position is stale: see attention_phase)
+__device__ __forceinline__ void attention_prefetch(Ctx& c, int l, const int* s_pos, const unsigned char* __restrict__ TM) {
     AttIter a; a.it = c.cta;
     att_load_item(a, s_pos, c.ncta);
-    if (att_valid(a)) att_fetch(c, a, keys, vals, l, c.smem + SM_KV, s_pos[a.b]);
+#pragma unroll 1
+    while (att_valid(a) && c.kvi - c.kvn < V_KVST) {
+        if (att_has_rows(a)) att_issue(c, a, l, TM);
+        att_advance(a, s_pos, c.ncta);
+    }
 }
 
 __device__ __forceinline__ void ldsm4(u32 (&r)[4], const unsigned char* p) {
@@ -692,111 +709,145 @@ __device__ __forceinline__ void mma_r(float (&c)[4], const u32 (&a)[4], u32 b0, 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// B operand of the scores: the query of (b, h), head in column 0 (lanes with g == 0), remainder in column 1 (g == 1)
+__device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* __restrict__ qbuf, int b, int h, int g, int t) {
+    const float* qp = qbuf + (size_t)b * V_D + h * V_E;
+    const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
+#pragma unroll
+    for (int kq = 0; kq < V_E / 16; kq++) {
+        bq[kq][0] = 0; bq[kq][1] = 0;
+        if (g < 2) {
+            const float2 a0 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
+            const float2 a1 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
+            const u32 h0 = pack_h2(a0.x * sc, a0.y * sc), h1 = pack_h2(a1.x * sc, a1.y * sc);
+            bq[kq][0] = g == 0 ? h0 : pack_h2(a0.x * sc - h_lo(h0), a0.y * sc - h_hi(h0));
+            bq[kq][1] = g == 0 ? h1 : pack_h2(a1.x * sc - h_lo(h1), a1.y * sc - h_hi(h1));
+        }
+    }
+}
+
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
-                                                float* __restrict__ part, int l, const int* s_pos) {
+                                                float* __restrict__ part, int l, const int* s_pos, const unsigned char* __restrict__ TM) {
     const int g = c.lane >> 2, t = c.lane & 3;
     AttIter cur, pf;
     cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
     if (!att_valid(cur)) return;
+    // rows written by other CTAs during the QKV phase are read by the copies below through the async proxy
+    if (c.tid == 0) asm volatile("fence.proxy.async.global;" ::: "memory");
+    // The tiles requested before the barrier: where one holds the current position of its sequence, that row is
+    // fetched now into a side buffer (one per stage) and moved into the tile when the tile is used.
+    unsigned char* side = c.smem + SM_MISC + MISC_SIDE;
+    u32 patch = 0;
     pf = cur;
-    // the row that was left out before the barrier
     {
-        const int tp = s_pos[cur.b];
-        if (tp >= cur.s && tp < min(cur.hi, cur.s + KV_POS) && c.tid < 16) {
-            const size_t row0 = ((size_t)(cur.b * V_L + l) * V_TMAX) * V_D + (size_t)cur.h * V_E;
-            const u16* src = ((c.tid & 8) ? vals : keys) + row0 + (size_t)tp * V_D + (c.tid & 7) * 8;
-            cp16(c.smem + SM_KV + (c.tid >> 3) * (KV_POS * KV_ROW) + (tp - cur.s) * KV_ROW + (c.tid & 7) * 16, src);
+        u32 n = c.kvn;
+#pragma unroll 1
+        while (n != c.kvi && att_valid(pf)) {
+            if (att_has_rows(pf)) {
+                const int tp = s_pos[pf.b];
+                if (tp >= pf.s && tp < min(pf.hi, pf.s + KV_POS)) {
+                    const u32 stage = n % V_KVST;
+                    patch |= 1u << stage;
+                    if (c.tid < 16) {
+                        const u16* src = ((c.tid & 8) ? vals : keys) + ((size_t)(pf.b * V_L + l) * V_TMAX + tp) * V_D + (size_t)pf.h * V_E + (c.tid & 7) * 8;
+                        cp16(side + stage * 256 + c.tid * 16, src);
+                    }
+                }
+                n++;
+            }
+            att_advance(pf, s_pos, c.ncta);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
-    att_advance(pf, s_pos, c.ncta);
-    if (att_valid(pf)) att_fetch(c, pf, keys, vals, l, c.smem + SM_KV + KV_STAGE_BYTES, -1);
-    else asm volatile("cp.async.commit_group;" ::: "memory");
 
-    int stage = 0;
-    u32 bq[V_E / 16][2];                             // B operand of the scores: the query, head (column 0) / remainder (column 1)
+    u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
+#pragma unroll
+    for (int kq = 0; kq < V_E / 16; kq++) { bqn[kq][0] = 0; bqn[kq][1] = 0; }
+    att_load_q(bq, qbuf, cur.b, cur.h, g, t);
     float m = -3.0e38f, den = 0.f, o[V_E / 16][4];   // o[mt]: dims mt*16 + g (regs 0+1) and mt*16 + g + 8 (regs 2+3), lanes t == 0
-    bool fresh = true;                               // the next tile starts an item
+    int item = 0;                                    // items finished by this CTA in this phase
+#pragma unroll
+    for (int mt = 0; mt < V_E / 16; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
 #pragma unroll 1
     while (att_valid(cur)) {
-        if (fresh) {
-            const float* qp = qbuf + (size_t)cur.b * V_D + cur.h * V_E;
-            const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
-#pragma unroll
-            for (int kq = 0; kq < V_E / 16; kq++) {
-                bq[kq][0] = 0; bq[kq][1] = 0;
-                if (g < 2) {
-                    const float2 a0 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
-                    const float2 a1 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
-                    const u32 h0 = pack_h2(a0.x * sc, a0.y * sc), h1 = pack_h2(a1.x * sc, a1.y * sc);
-                    bq[kq][0] = g == 0 ? h0 : pack_h2(a0.x * sc - h_lo(h0), a0.y * sc - h_hi(h0));
-                    bq[kq][1] = g == 0 ? h1 : pack_h2(a1.x * sc - h_lo(h1), a1.y * sc - h_hi(h1));
-                }
-            }
-            m = -3.0e38f; den = 0.f;
-#pragma unroll
-            for (int mt = 0; mt < V_E / 16; mt++)
-#pragma unroll
-                for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
-            fresh = false;
-        }
         TRACE(44);
-        asm volatile("cp.async.wait_group 1;" ::: "memory");       // this tile has landed; the next one may be in flight
-        cons_sync();
-        TRACE(45);
-        const unsigned char* kt = c.smem + SM_KV + stage * KV_STAGE_BYTES;
-        const unsigned char* vt = kt + KV_POS * KV_ROW;
+        const bool last = cur.s + KV_POS >= cur.hi;
+        const int next_it = cur.it + c.ncta;
+        if (last && next_it < V_B * V_H * V_NCH) {
+            // the next item's query is requested now and used after this tile
+            const int bh = next_it / V_NCH, nb_ = bh / V_H;
+            att_load_q(bqn, qbuf, nb_, bh - nb_ * V_H, g, t);
+        }
         const int cnt = min(KV_POS, cur.hi - cur.s);
-        const int p0 = c.warp * 16;                                 // this warp's positions of the tile
-        if (p0 < cnt) {
-            // scores of 16 positions: rows g and g + 8 of the tile slice, in the lanes with t == 0
-            float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int kq = 0; kq < V_E / 16; kq++) {
-                u32 a[4];
-                ldsm4(a, kt + (p0 + (c.lane & 15)) * KV_ROW + kq * 32 + (c.lane >> 4) * 16);
-                mma_r(sacc, a, bq[kq][0], bq[kq][1]);
+        if (cnt > 0) {
+            const u32 stage = c.kvn % V_KVST;
+            wait_mbar(c, kv_bar(c, stage), (c.kvn / V_KVST) & 1u, 0x500u);
+            unsigned char* kt = c.smem + SM_KV + stage * KV_STAGE_BYTES;
+            unsigned char* vt = kt + KV_TILE_BYTES;
+            if (patch & (1u << stage)) {
+                patch &= ~(1u << stage);
+                cp_wait();                              // the thread that fetched a piece is the one that places it
+                if (c.tid < 16) {
+                    const int r = s_pos[cur.b] - cur.s;
+                    *reinterpret_cast<uint4*>(((c.tid & 8) ? vt : kt) + kv_off(r, c.tid & 7)) = *reinterpret_cast<const uint4*>(side + stage * 256 + c.tid * 16);
+                }
+                cons_sync();
             }
-            float s0 = sacc[0] + sacc[1], s1 = sacc[2] + sacc[3];
-            if (!V_SCALE_IS_POW2) { s0 = s0 / V_SCALE; s1 = s1 / V_SCALE; }
-            if (t != 0 || p0 + g >= cnt) s0 = -3.0e38f;
-            if (t != 0 || p0 + g + 8 >= cnt) s1 = -3.0e38f;
-            float mx = fmaxf(s0, s1);
+            TRACE(45);
+            const int p0 = c.warp * 16;                                 // this warp's positions of the tile
+            if (p0 < cnt && !c.dead) {
+                // scores of 16 positions: rows g and g + 8 of the tile slice, in the lanes with t == 0
+                float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int x = 4; x <= 16; x <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
-            mx = __shfl_sync(0xffffffffu, mx, 0);                   // lanes with t != 0 saw only their own minus infinity
-            const float mn = fmaxf(m, mx);
-            const float corr = fast_exp(m - mn);
-            const float pa = (s0 > -1.0e38f) ? fast_exp(s0 - mn) : 0.f, pb = (s1 > -1.0e38f) ? fast_exp(s1 - mn) : 0.f;
-            float ps = pa + pb;
+                for (int kq = 0; kq < V_E / 16; kq++) {
+                    u32 a[4];
+                    ldsm4(a, kt + kv_off(p0 + (c.lane & 15), kq * 2 + (c.lane >> 4)));
+                    mma_r(sacc, a, bq[kq][0], bq[kq][1]);
+                }
+                float s0 = sacc[0] + sacc[1], s1 = sacc[2] + sacc[3];
+                if (!V_SCALE_IS_POW2) { s0 = s0 / V_SCALE; s1 = s1 / V_SCALE; }
+                if (t != 0 || p0 + g >= cnt) s0 = -3.0e38f;
+                if (t != 0 || p0 + g + 8 >= cnt) s1 = -3.0e38f;
+                float mx = fmaxf(s0, s1);
 #pragma unroll
-            for (int x = 4; x <= 16; x <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
-            ps = __shfl_sync(0xffffffffu, ps, 0);
-            den = den * corr + ps;
-            m = mn;
+                for (int x = 4; x <= 16; x <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
+                mx = __shfl_sync(0xffffffffu, mx, 0);                   // lanes with t != 0 saw only their own minus infinity
+                const float mn = fmaxf(m, mx);
+                const float corr = fast_exp(m - mn);
+                const float pa = (s0 > -1.0e38f) ? fast_exp(s0 - mn) : 0.f, pb = (s1 > -1.0e38f) ? fast_exp(s1 - mn) : 0.f;
+                float ps = pa + pb;
 #pragma unroll
-            for (int mt = 0; mt < V_E / 16; mt++)
+                for (int x = 4; x <= 16; x <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
+                ps = __shfl_sync(0xffffffffu, ps, 0);
+                den = den * corr + ps;
+                m = mn;
 #pragma unroll
-                for (int i = 0; i < 4; i++) o[mt][i] *= corr;
-            // weights as the B operand: lane (g, t) holds positions 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1); the weight
-            // of position r < 8 is `pa` of lane 4r, that of position r + 8 is `pb` of lane 4r
-            const float w00 = __shfl_sync(0xffffffffu, pa, 8 * t), w01 = __shfl_sync(0xffffffffu, pa, 8 * t + 4);
-            const float w10 = __shfl_sync(0xffffffffu, pb, 8 * t), w11 = __shfl_sync(0xffffffffu, pb, 8 * t + 4);
-            u32 b0 = pack_h2(w00, w01), b1 = pack_h2(w10, w11);
-            if (g == 1) { b0 = pack_h2(w00 - h_lo(b0), w01 - h_hi(b0)); b1 = pack_h2(w10 - h_lo(b1), w11 - h_hi(b1)); }
-            if (g > 1) { b0 = 0; b1 = 0; }
+                for (int mt = 0; mt < V_E / 16; mt++)
 #pragma unroll
-            for (int mt = 0; mt < V_E / 16; mt++) {
-                u32 a[4];
-                const int j = c.lane >> 3;
-                ldsm4t(a, vt + (p0 + (c.lane & 7) + ((j >> 1) ? 8 : 0)) * KV_ROW + mt * 32 + ((j & 1) ? 16 : 0));
-                mma_r(o[mt], a, b0, b1);
+                    for (int i = 0; i < 4; i++) o[mt][i] *= corr;
+                // weights as the B operand: lane (g, t) holds positions 2t, 2t+1 (b0) and 2t+8, 2t+9 (b1); the weight
+                // of position r < 8 is `pa` of lane 4r, that of position r + 8 is `pb` of lane 4r
+                const float w00 = __shfl_sync(0xffffffffu, pa, 8 * t), w01 = __shfl_sync(0xffffffffu, pa, 8 * t + 4);
+                const float w10 = __shfl_sync(0xffffffffu, pb, 8 * t), w11 = __shfl_sync(0xffffffffu, pb, 8 * t + 4);
+                u32 b0 = pack_h2(w00, w01), b1 = pack_h2(w10, w11);
+                if (g == 1) { b0 = pack_h2(w00 - h_lo(b0), w01 - h_hi(b0)); b1 = pack_h2(w10 - h_lo(b1), w11 - h_hi(b1)); }
+                if (g > 1) { b0 = 0; b1 = 0; }
+#pragma unroll
+                for (int mt = 0; mt < V_E / 16; mt++) {
+                    u32 a[4];
+                    const int j = c.lane >> 3;
+                    ldsm4t(a, vt + kv_off(p0 + (c.lane & 7) + ((j >> 1) ? 8 : 0), mt * 2 + (j & 1)));
+                    mma_r(o[mt], a, b0, b1);
+                }
             }
         }
         TRACE(46);
-        const bool last = cur.s + KV_POS >= cur.hi;
         float* out = part + (size_t)cur.it * PART_STRIDE;
-        float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT);
+        // the warps' partial results of an item meet in shared memory; consecutive items use alternate buffers, so
+        // that a warp that is already done with the next item does not overwrite what the merge is still reading
+        float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT) + (item & 1) * (NW * (V_E + 2));
         if (last) {
             // per warp (m, den, o[V_E]) into shared memory
             float* w = ms + c.warp * (V_E + 2);
@@ -807,28 +858,41 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
             }
         }
         cons_sync();                                   // everybody is done with this stage (and ms is written)
-        if (last && c.tid < V_E) {
-            float M = -3.0e38f;
+        if (cnt > 0) {
+            c.kvn++;
+            // the stage is free: the tile V_KVST ahead goes into it
 #pragma unroll 1
-            for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
-            float num = 0.f, dd = 0.f;
-#pragma unroll 1
-            for (int w = 0; w < NW; w++) {
-                const float sc = fast_exp(ms[w * (V_E + 2)] - M);
-                dd += ms[w * (V_E + 2) + 1] * sc;
-                num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
-            }
-            out[2 + c.tid] = num;
-            if (c.tid == 0) { out[0] = M; out[1] = dd; }
+            while (att_valid(pf) && !att_has_rows(pf)) att_advance(pf, s_pos, c.ncta);
+            if (att_valid(pf) && !c.dead) { att_issue(c, pf, l, TM); att_advance(pf, s_pos, c.ncta); }
         }
-        fresh = last;
+        if (last) {
+            if (c.tid < V_E) {
+                float M = -3.0e38f;
+#pragma unroll
+                for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
+                float num = 0.f, dd = 0.f;
+#pragma unroll
+                for (int w = 0; w < NW; w++) {
+                    const float sc = fast_exp(ms[w * (V_E + 2)] - M);
+                    dd += ms[w * (V_E + 2) + 1] * sc;
+                    num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
+                }
+                out[2 + c.tid] = num;
+                if (c.tid == 0) { out[0] = M; out[1] = dd; }
+            }
+            // start the next item
+            item++;
+#pragma unroll
+            for (int kq = 0; kq < V_E / 16; kq++) { bq[kq][0] = bqn[kq][0]; bq[kq][1] = bqn[kq][1]; }
+            m = -3.0e38f; den = 0.f;
+#pragma unroll
+            for (int mt = 0; mt < V_E / 16; mt++)
+#pragma unroll
+                for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
+        }
         att_advance(cur, s_pos, c.ncta);
-        att_advance(pf, s_pos, c.ncta);
-        if (att_valid(pf)) att_fetch(c, pf, keys, vals, l, c.smem + SM_KV + stage * KV_STAGE_BYTES, -1);
-        else asm volatile("cp.async.commit_group;" ::: "memory");
-        stage ^= 1;
     }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    cp_wait();
     cons_sync();                                       // ms may be reused by the next phase
 }
 
@@ -843,6 +907,7 @@ struct Args {
     const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
+    const unsigned char* TM;                    // four TMA descriptors of the K/V cache
     int nsteps;                                 // decode steps in this launch (the kernel feeds itself between them)
 };
 
@@ -856,7 +921,7 @@ struct Args {
 __device__ __forceinline__ void step_body(const Args& a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Ctx c;
-    c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false;
+    c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false; c.kvi = 0; c.kvn = 0;
     c.cta = blockIdx.x; c.ncta = gridDim.x; c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
 #if V_TIMING
     __shared__ u64 trace_[(V_NW + 1) * TRACE_EVENTS];
@@ -891,6 +956,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         *stop = 0;
         if (c.cta == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(0u) : "memory");   // nobody reads it before the first barrier
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
+        for (int s = 0; s < V_KVST; s++) mbar_init(kv_bar(c, s), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // operand tiles and K/V stages start as zero: rows of a batch tile beyond the batch stay zero for the whole
@@ -955,7 +1021,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         TRACE(1 + first);
 
         if (first == PH_ATT) {
-            attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos);
+            attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos, a.TM);
         } else {
             // LN1 phase clears z2 (the MLP adds into it two barriers later); LN2 phase clears zin for the next layer
             // (not needed with the distributed LayerNorm, which starts those vectors with a plain store)
@@ -1100,7 +1166,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
             else
                 fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
         }
-        if (first == PH_QKV) attention_prefetch(c, a.keys, a.vals, l, s_pos);
+        if (first == PH_QKV) attention_prefetch(c, l, s_pos, a.TM);
         TRACE(30 + first);
         phase_wait(c);
         TICK(3 + 2 * (ph - l * PH_PER_LAYER));

@@ -78,6 +78,7 @@ size_t vesta_static_scratch_bytes(void) { return VESTA_STATIC_SCRATCH_BYTES; }
 int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
                       int n_residues, const unsigned long long* residue_pointers,
                       unsigned long long packed_weights, unsigned long long plan_table,
+                      unsigned long long tensor_maps,
                       size_t scratch_floats, size_t counters,
                       size_t logit_offset, size_t logit_count, float* logits_out,
                       size_t next_offset, size_t next_count, float* next_out,
@@ -103,7 +104,7 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(std::string("clear_static_scratch: ") + cudaGetErrorString(e));
 
-    // the step kernel's parameters: residues, then S, bar, TS, packed weights, plan table, steps per launch
+    // the step kernel's parameters: residues, then S, bar, TS, packed weights, plan table, K/V descriptors, steps per launch
     unsigned long long vals[64];
     void* args[64];
     int n = 0;
@@ -113,6 +114,7 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     vals[n++] = (unsigned long long)(base + COUNTER_WORDS * 4);         // TS
     vals[n++] = packed_weights;
     vals[n++] = plan_table;
+    vals[n++] = tensor_maps;
     vals[n++] = 1ull;                                                   // one decode step per launch
     for (int i = 0; i < n; i++) args[i] = &vals[i];
     if (vesta_launch_cooperative(function, grid, block, dynamic_smem, stream, args) != 0)

@@ -40,6 +40,9 @@ struct Driver {
     CUresult (*Launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                        CUstream, void**, void**) = nullptr;
     CUresult (*LaunchEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
 };
 Driver g_cu;
 
@@ -61,7 +64,7 @@ int driver() {
               sym(lib, "cuModuleGetFunction", d.ModuleGetFunction) && sym(lib, "cuFuncSetAttribute", d.FuncSetAttribute) &&
               sym(lib, "cuOccupancyMaxActiveBlocksPerMultiprocessor", d.Occupancy) &&
               sym(lib, "cuLaunchCooperativeKernel", d.LaunchCooperative) && sym(lib, "cuLaunchKernel", d.Launch) &&
-              sym(lib, "cuLaunchKernelEx", d.LaunchEx);
+              sym(lib, "cuLaunchKernelEx", d.LaunchEx) && sym(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled);
     if (!ok) return fail(-1, "libcuda.so.1 lacks a required driver entry point");
     d.lib = lib;
     g_cu = d;
@@ -287,6 +290,27 @@ int vesta_step_run(void* bound, void* stream, int steps) {
         CUresult r = g_cu.LaunchCooperative(b->fn, b->grid, 1, 1, b->block, 1, 1, b->smem, (CUstream)stream, b->ptrs.data());
         if (r != CUDA_SUCCESS) return cu(r, "cuLaunchCooperativeKernel");
     }
+    return 0;
+}
+
+int vesta_tensor_map_rows(void* out, const void* base, unsigned long long row_elems, unsigned long long rows,
+                          unsigned long long planes, unsigned box_elems, unsigned box_rows) {
+    if (!out || !base) return fail(-1, "vesta_tensor_map_rows: null argument");
+    if (int e = driver()) return e;
+    if (box_elems * 2u != 128u || box_rows == 0 || box_rows > 256u || (row_elems * 2ull) % 16ull)
+        return fail(-1, "vesta_tensor_map_rows: the box must be 128 bytes wide, at most 256 rows, rows a multiple of 16 bytes");
+    // fp16 [planes][rows][row_elems]; box = box_rows rows of 64 elements of one plane; 128-byte swizzle: the 16-byte
+    // piece c of row r lands at piece c ^ (r % 8) of its 128-byte row in shared memory
+    const cuuint64_t dims[3] = {row_elems, rows, planes};
+    const cuuint64_t strides[2] = {row_elems * 2ull, rows * row_elems * 2ull};
+    const cuuint32_t box[3] = {box_elems, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUtensorMap tm;
+    CUresult r = g_cu.TensorMapEncodeTiled(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return cu(r, "cuTensorMapEncodeTiled");
+    memcpy(out, &tm, sizeof(tm));
     return 0;
 }
 

@@ -51,6 +51,7 @@ def lib():
         L.vesta_step_bind.argtypes = [vp, cu, cu, cu, ci, ctypes.POINTER(ctypes.c_ulonglong), ctypes.POINTER(vp)]
         L.vesta_step_run.argtypes = [vp, vp, ci]
         L.vesta_step_run_fused.argtypes = [vp, vp, ci, ci]
+        L.vesta_tensor_map_rows.argtypes = [vp, vp, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_uint, ctypes.c_uint]
         L.vesta_step_release.argtypes = [vp]
         L.vesta_step_release.restype = None
         _lib = L
@@ -96,7 +97,7 @@ def compile_cubin(src, arch=ARCH, cache=True):
     return data
 
 
-STATUS_WHERE = {0x100: 'grid barrier', 0x200: 'weight stream (producer)', 0x300: 'weight stream (consumer)', 0x400: 'step flag',
+STATUS_WHERE = {0x100: 'grid barrier', 0x200: 'weight stream (producer)', 0x300: 'weight stream (consumer)', 0x400: 'step flag', 0x500: 'K/V tile',
                 0x900: 'token or position out of range'}
 
 
@@ -165,7 +166,8 @@ class Kernel:
             assert t.is_cuda and t.dtype == TORCH_DT[dt] and t.is_contiguous(), (name, t.dtype, dt)
             assert t.device == self.device, (name, t.device)
             vals.append(t.data_ptr())
-        vals += [self.S.data_ptr(), self.bar.data_ptr(), self.TS.data_ptr(), self.WP.data_ptr(), self.PT.data_ptr(), 1]
+        self.TM = self.tensor_maps(residue)
+        vals += [self.S.data_ptr(), self.bar.data_ptr(), self.TS.data_ptr(), self.WP.data_ptr(), self.PT.data_ptr(), self.TM.data_ptr(), 1]
         self.args = (tuple(vals), tuple([ctypes.c_void_p] * len(vals)))
         self.keep = residue
         if self._bound:
@@ -175,6 +177,17 @@ class Kernel:
         ok(L.vesta_step_bind(self.fn, self.grid, self.block, self.smem, len(vals), arr, ctypes.byref(bound)))
         self._bound = bound
         self.pack(residue)
+
+    def tensor_maps(self, residue):
+        """the four TMA descriptors the attention phase reads the caches through: K and V with boxes of 128
+        rows, K and V with boxes of 32 rows (vesta_tensor_map_rows), in device memory"""
+        d = self.lowered.dims
+        host = torch.zeros(4 * 128, dtype=torch.uint8)
+        for i, (role, rows) in enumerate((('keys', 128), ('vals', 128), ('keys', 32), ('vals', 32))):
+            t = residue[self.lowered.roles[role]]
+            ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * i), ctypes.c_void_p(t.data_ptr()),
+                                           d['D'], d['tmax'], d['B'] * d['L'], 64, rows))
+        return host.to(self.device)
 
     def pack(self, residue=None):
         """(re)build the packed weight streams from the bound weights; call again after changing them"""

@@ -365,9 +365,12 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         act_lo = bool(tune.get('act_lo', B <= 8 or (B <= 16 and D <= 1024)))
     atile = 512 if act_lo else 256
 
+    # K/V tiles in flight per CTA in the attention phase (32 KB each)
+    kvst = int(tune.get('kv_stages', 3))
+
     def smem_fixed(nb):
-        return (2 * 2 * NW * 16 * 144 + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
-                + (3 * D + WN_MAX * 16) * 2 + 16 + NW * (E + 2) * 4 + 8 + 8 * nb * NW * 8 + B * 4 + 8 * 8 + 16 + 16)
+        return (kvst * (2 * NW * 16 * 128 + 256 + 8) + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
+                + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 + 16 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
     if slab_tiles:
@@ -412,7 +415,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     scale = dims['scale']
     defs = dict(V_NW=NW, V_B=B, V_NB=NB, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
                 V_EPS=f32(dims['eps']), V_SCALE=f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5), V_GELU_A=f32(dims['gelu'][0]), V_GELU_B=f32(dims['gelu'][1]),
-                V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_ACT_LO=int(bool(act_lo)),
+                V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
                 V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
@@ -429,7 +432,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
     R = {k: 'R_' + v for k, v in roles.items()}
     step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
-                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT', 'int nsteps'])
+                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT',
+                                'const unsigned char* __restrict__ TM', 'int nsteps'])
     fill = [f'a.x = {R["x"]}; a.t = {R["t"]};']
     for k in ('wte', 'wpe', 'ln1w', 'ln1b', 'qkvb', 'ob', 'ln2w', 'ln2b', 'fcb', 'pb', 'lnfw', 'lnfb'):
         fill.append(f'a.{k} = {R[k]};')
@@ -439,7 +443,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     else:
         fill.append('a.x_out = 0; a.t_out = 0;')
     fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
-    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.nsteps = nsteps;')
+    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.TM = TM; a.nsteps = nsteps;')
     pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
     pack_params = [roles[k] for k in pack_roles]
     pack_sig = ', '.join([f'const unsigned short* __restrict__ R_{roles[k]}' for k in pack_roles]
