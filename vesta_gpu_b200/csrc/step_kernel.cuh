@@ -810,18 +810,14 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 if (!V_SCALE_IS_POW2) { s0 = s0 / V_SCALE; s1 = s1 / V_SCALE; }
                 if (t != 0 || p0 + g >= cnt) s0 = -3.0e38f;
                 if (t != 0 || p0 + g + 8 >= cnt) s1 = -3.0e38f;
-                float mx = fmaxf(s0, s1);
-#pragma unroll
-                for (int x = 4; x <= 16; x <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, x));
-                mx = __shfl_sync(0xffffffffu, mx, 0);                   // lanes with t != 0 saw only their own minus infinity
+                // the warp's maximum in one instruction: floats compare like integers once the negative ones are flipped
+                int km = __float_as_int(fmaxf(s0, s1));
+                km = __reduce_max_sync(0xffffffffu, km >= 0 ? km : km ^ 0x7fffffff);
+                const float mx = __int_as_float(km >= 0 ? km : km ^ 0x7fffffff);
                 const float mn = fmaxf(m, mx);
                 const float corr = fast_exp(m - mn);
                 const float pa = (s0 > -1.0e38f) ? fast_exp(s0 - mn) : 0.f, pb = (s1 > -1.0e38f) ? fast_exp(s1 - mn) : 0.f;
-                float ps = pa + pb;
-#pragma unroll
-                for (int x = 4; x <= 16; x <<= 1) ps += __shfl_xor_sync(0xffffffffu, ps, x);
-                ps = __shfl_sync(0xffffffffu, ps, 0);
-                den = den * corr + ps;
+                den = den * corr + (pa + pb);                           // per lane: summed over the warp when the item ends
                 m = mn;
 #pragma unroll
                 for (int mt = 0; mt < V_E / 16; mt++)
@@ -851,6 +847,8 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         if (last) {
             // per warp (m, den, o[V_E]) into shared memory
             float* w = ms + c.warp * (V_E + 2);
+#pragma unroll
+            for (int x = 16; x; x >>= 1) den += __shfl_xor_sync(0xffffffffu, den, x);
             if (c.lane == 0) { w[0] = m; w[1] = den; }
             if (t == 0) {
 #pragma unroll
