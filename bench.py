@@ -48,9 +48,11 @@ WORKLOADS = {
     'tiny': dict(shape='tiny3', batch=2, prompt=8, gen=16),
 }
 METRIC, UNIT = 'decode tokens/s', 'tokens/s'
-# DRAM bytes (read + write) of one vesta_step launch from the ncu capture summarised in
-# profiles/vesta_step_gpt2_small_b8.md (context ~135); null for workloads that were not captured
-NCU_TRAFFIC = {'cfg2': 254.6e6}
+# DRAM bytes (read + write) of one decode step from the ncu capture summarised in
+# profiles/vesta_step_gpt2_small_b8.md, taken at the given context (attended positions per sequence). The bench's
+# launches attend more positions: the K/V part is scaled by the positions, the weights are read once either way.
+# Workloads that were not captured report null.
+NCU_CAPTURE = {'cfg2': dict(bytes=290.9e6, positions=130)}
 
 
 def peaks():
@@ -285,6 +287,12 @@ def main():
     bytes_per_step = sum(sh.weight_bytes() + sh.kv_bytes_per_pos() * sum(c) / world for c in ctx_lens) / K
     peak, peak_src = peaks()
     achieved = bytes_per_step / (med / K) / 1e9
+    spl = min(args.per_launch, K)
+    cap = NCU_CAPTURE.get(args.workload) if world == 1 else None
+    traffic = None
+    if cap:
+        mean_pos = sum(sum(c) for c in ctx_lens) / K / (B * world)
+        traffic = (cap['bytes'] + B * (mean_pos - cap['positions']) * sh.kv_bytes_per_pos()) * spl
     line = dict(metric=METRIC, value=B * world * K / med, unit=UNIT, n_gpus=world, steps=K, warmup=Wm,
                 ms_per_step=1e3 * med / K, higher_is_better=True, scaling='strong' if total else 'weak', vs_baseline=None,
                 dtype='f16 weights and KV, f32 accumulate', data='synthetic',
@@ -294,8 +302,8 @@ def main():
                 clocks=clocks, gpu_launches=-(-K // args.per_launch),
                 e2e=dict(value=B * world * K / e2e_med, unit=UNIT, h2d_bytes_per_step=B * 4, d2h_bytes_per_step=B * 4,
                          tokens_match_device_loop=e2e_ok),
-                roofline=dict(bound='hbm', achieved=achieved, peak=peak, unit='GB/s', frac=achieved / peak, traffic=NCU_TRAFFIC.get(args.workload),
-                              peak_source=peak_src, bytes_per_step=bytes_per_step, bytes_per_launch=bytes_per_step * min(args.per_launch, K), kernel='vesta_step',
+                roofline=dict(bound='hbm', achieved=achieved, peak=peak, unit='GB/s', frac=achieved / peak, traffic=traffic,
+                              peak_source=peak_src, bytes_per_step=bytes_per_step, bytes_per_launch=bytes_per_step * spl, kernel='vesta_step',
                               frac_of_8tbs=achieved / 8000.0))
     if not args.no_cpu_baseline and world == 1:
         from oracle import gpt2_numpy as O
