@@ -132,6 +132,9 @@ def test_against_oracle_other_batches(batch):
     (20, 1, dict(ln_dist=False, act_lo=True)),         # every CTA normalises its slab, head + remainder
     (60, None, None),                                  # more (sequence, head) items than CTAs: several per CTA
     (60, None, dict(kv_stages=2, nch=2)),              # ... with two K/V stages and two position chunks per item
+    (64, None, dict(tc=True)),                         # 64 sequences and more: logits on tcgen05 / tensor memory
+    (70, None, dict(tc=True)),                                # ... two slabs of 64 sequences, the second ragged
+    (70, None, dict(tc=False)),                        # ... and the same batch on the mma.sync path
 ])
 def test_batches_above_one_slab(batch, slab_tiles, tune):
     """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged), in both
@@ -235,6 +238,29 @@ def test_batch_rows_are_independent_at_full_size():
     assert np.abs(l8 - l8[0:1]).max() < 1e-4
     assert np.abs(l8[0] - outs[1][1][0]).max() < 1e-4
     assert np.array_equal(t8[0], outs[1][0][0])
+
+
+def test_tensor_core_logits_at_full_size_equal_the_mma_path():
+    """GPT-2 small, 64 sequences, one step on a filled cache: the tcgen05 logits (128 x 64 tiles of the whole
+    vocabulary, every CTA's range ragged at its end) against the mma.sync path on the same inputs, and the
+    arg-max of each sequence against its own logits"""
+    from vesta_gpu_b200.shapes import GPT2_SMALL
+    B, ctx = 64, 40
+    outs = []
+    for tc in (True, False):
+        m, _ = model(GPT2_SMALL, 0, 'rich', B, ctx + 2, tune=dict(tc=tc))
+        assert bool(m.low.dims['tc']) == tc
+        m.reset()
+        g = torch.Generator(device='cuda').manual_seed(3)
+        m.keys[:, :, :ctx].copy_((torch.randn(m.keys[:, :, :ctx].shape, generator=g, device='cuda') * 0.3).half())
+        m.vals[:, :, :ctx].copy_((torch.randn(m.vals[:, :, :ctx].shape, generator=g, device='cuda') * 0.3).half())
+        m.t.fill_(ctx); m.x.copy_(torch.arange(B, dtype=torch.int32, device='cuda') * 97 + 11)
+        m.step(); m.k.check()
+        lg, nx = m.logits().cpu().numpy().copy(), m.next().cpu().numpy().copy()
+        assert np.array_equal(nx.astype(np.int64), lg.argmax(1))
+        outs.append(lg)
+        del m
+    assert np.abs(outs[0] - outs[1]).max() < TIGHT
 
 
 def test_multi_step_launch_and_reset():

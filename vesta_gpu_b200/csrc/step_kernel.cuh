@@ -180,10 +180,11 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define MISC_STAT ((MISC_POS + V_B * 4 + 15) & ~15)                // 8 x 2 floats
 #define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
 #define MISC_STOP (MISC_FLAG + 4)                                 // one int: the consumers are leaving
+#define MISC_TMEM (MISC_FLAG + 8)                                 // one u32: base address of this CTA's tensor memory (V_TC)
 #define MISC_SIDE (MISC_FLAG + 16)                                // per K/V stage: the K row and the V row of the current position
 #define SM_MISC_BYTES (MISC_SIDE + V_KVST * 256)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
-#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + V_KVST) * 8)
+#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + V_KVST + 2) * 8)        // + operand-loaded and products-done barriers of the tensor-core logits
 
 struct Ctx {
     unsigned char* smem;
@@ -191,6 +192,7 @@ struct Ctx {
     u32 gen;           // barrier generation x CTAs
     u32 chunk;         // stream chunks consumed so far (same value in every consumer warp and the producer)
     u32 kvi, kvn;      // K/V tiles requested / used so far (stage = count % V_KVST)
+    u32 tcl, tcd;      // tensor-core logits: operand loads / accumulator tiles finished so far (barrier parities)
     int cta, ncta, tid, warp, lane;
     bool dead;         // a bounded wait expired somewhere: skip waits from now on
 #if V_TIMING
@@ -263,7 +265,17 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 // ---------------------------------------------------------------------------------------------
 // producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
-__device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta, int nsteps) {
+#define TC_SLABS_P ((V_B + 63) / 64)
+// leaving early: first let the copies still in flight land (bounded), so that none writes into shared memory
+// after the CTA has gone
+__device__ __noinline__ void producer_drain(Ctx& c) {
+    for (u32 k = c.chunk > V_NSLOT ? c.chunk - V_NSLOT : 0u; k < c.chunk; k++) {
+        const u64 t0 = now_ns();
+        while (!mbar_try(full_bar(c, k % V_NSLOT), (k / V_NSLOT) & 1u) && now_ns() - t0 < WAIT_NS) { }
+    }
+}
+__device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP,
+                                      const unsigned char* __restrict__ TM, int cta, int nsteps) {
     Ctx c;
     c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta;
     const unsigned char* base = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
@@ -272,6 +284,25 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
         const int l = (ph % (V_L * PH_PER_LAYER + 1)) / PH_PER_LAYER, pl = ph % (V_L * PH_PER_LAYER + 1);
         const int first = (l == V_L) ? PH_LOGITS : (pl - l * PH_PER_LAYER == 3 ? PH_FC : pl - l * PH_PER_LAYER);
         if (first == PH_ATT) continue;
+#if V_TC
+        if (first == PH_LOGITS) {
+            // 128 rows x 64 k of the embedding table per slot, by tensor copy; once per slab of 64 sequences
+            const int rows = P[PT_LOG_NJ] * 16, mtiles = (rows + 127) / 128;
+#pragma unroll 1
+            for (int i = 0; i < TC_SLABS_P * mtiles * (V_D / 64); i++) {
+                const int kb = i % (V_D / 64), mt = (i / (V_D / 64)) % mtiles;
+                const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+                wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
+                if (c.dead) { producer_drain(c); return; }
+                mbar_expect(full_bar(c, slot), 128 * 128);
+                asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                             :: "r"(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES)), "l"(TM + 4 * 128), "r"(kb * 64), "r"(P[PT_LOG_J0] * 16 + mt * 128), "r"(0),
+                                "r"(full_bar(c, slot)) : "memory");
+                c.chunk++;
+            }
+            continue;
+        }
+#endif
         const int last = (first == PH_FC) ? PH_P2 : first;
 #pragma unroll 1
         for (int slab = 0; slab < NSLAB; slab++)
@@ -287,15 +318,7 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
                     for (int r = 0; r < s.rows; r += rpc) {
                         const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
                         wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
-                        if (c.dead) {
-                            // leaving early: first let the copies still in flight land (bounded), so that none
-                            // writes into shared memory after the CTA has gone
-                            for (u32 k = c.chunk > V_NSLOT ? c.chunk - V_NSLOT : 0u; k < c.chunk; k++) {
-                                const u64 t0 = now_ns();
-                                while (!mbar_try(full_bar(c, k % V_NSLOT), (k / V_NSLOT) & 1u) && now_ns() - t0 < WAIT_NS) { }
-                            }
-                            return;
-                        }
+                        if (c.dead) { producer_drain(c); return; }
                         const u32 bytes = (u32)(min(rpc, s.rows - r) * width) * FRAG_BYTES;
                         mbar_expect(full_bar(c, slot), bytes);
                         bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, bytes, full_bar(c, slot));
@@ -895,6 +918,169 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Logits on the 5th-generation tensor cores (V_TC: batches of 64 and more, where the contraction is dense).
+// D[n][b] = sum_k wte[n][k] * y[b][k] per tile of 128 vocabulary rows x 64 batch rows, accumulated in tensor
+// memory by tcgen05.mma (M = 128, N = 64, K = 16 per instruction, fp16 operands, fp32 accumulators):
+//   A = 128 rows of the embedding table, 64 k at a time: the table is row-major, i.e. K-major, so the TMA
+//       box (64 k x 128 rows, 128-byte swizzle) is the operand layout itself; 16 KB = one slot of the weight ring,
+//       requested by the producer warp;
+//   B = the normalised final state of 64 sequences, fp16, written by the distributed LayerNorm to global memory
+//       in the same K-major swizzled layout (blocks of 64 k: 64 rows x 128 B) and copied into the K/V stages,
+//       which are idle in this phase;
+//   one thread issues the products of a block as soon as its slot is full and commits them to the slot's
+//   empty barrier; after the last block of a tile it commits to the "done" barrier, and the eight consumer
+//   warps read the accumulators (tcgen05.ld, a warp reads the lanes of its quarter), store the logits and
+//   reduce the arg-max per sequence.
+// ---------------------------------------------------------------------------------------------
+#define TC_M 128
+#define TC_N 64
+#define TC_KB 64                                  // k per block (128 bytes of fp16)
+#define TC_NKB (V_D / TC_KB)
+#define TC_SLABS ((V_B + TC_N - 1) / TC_N)
+#define TC_B_BYTES (TC_N * V_D * 2)               // operand B of one slab
+#define TC_COLS 64                                // tensor-memory columns: one accumulator tile
+__device__ __forceinline__ u32 tc_load_bar(const Ctx& c) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST) * 8; }
+__device__ __forceinline__ u32 tc_done_bar(const Ctx& c) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST + 1) * 8; }
+
+// shared-memory matrix descriptor of a K-major operand in the 128-byte swizzle: rows of 128 bytes, groups of 8 rows
+// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (128-byte swizzle)
+__device__ __forceinline__ u64 tc_desc(u32 smem_addr) {
+    return (u64)((smem_addr & 0x3FFFFu) >> 4) | ((u64)1 << 16) | ((u64)(1024 >> 4) << 32) | ((u64)1 << 46) | ((u64)2 << 61);
+}
+// instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 64, M = 128
+#define TC_IDESC ((1u << 4) | ((u32)(TC_N >> 3) << 17) | ((u32)(TC_M >> 4) << 24))
+
+__device__ __forceinline__ void tc_mma(u32 d_tmem, u64 adesc, u64 bdesc, u32 accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_commit(u32 bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+
+// the normalised rows of the final state as operand B in global memory: row r of slab r / 64, block k / 64,
+// 16-byte piece (k % 64) / 8 stored at piece ^ (row % 8) of its 128-byte row
+__device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ z, unsigned char* __restrict__ tcg) {
+    const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
+#pragma unroll 1
+    for (int r = c.cta * NW + c.warp; r < TC_SLABS * TC_N; r += c.ncta * NW) {
+        float4 v[LNV];
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            const int g = i * 32 + c.lane;
+            v[i] = (g < G4 && r < V_B) ? __ldcg(reinterpret_cast<const float4*>(z + (size_t)r * V_D) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) s += __shfl_xor_sync(0xffffffffu, s, m);
+        const float mean = s * (1.0f / V_D);
+        float q = 0.f;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            if (i * 32 + c.lane < G4) {
+                const float a0 = v[i].x - mean, a1 = v[i].y - mean, a2 = v[i].z - mean, a3 = v[i].w - mean;
+                q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
+        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        const int rb = r % TC_N;
+        unsigned char* dst = tcg + (size_t)(r / TC_N) * TC_B_BYTES + rb * 128;
+#pragma unroll
+        for (int i = 0; i < LNV; i++) {
+            const int g = i * 32 + c.lane, d = g * 4;
+            if (g < G4) {
+                uint2 o = make_uint2(0, 0);                 // rows beyond the batch are zero
+                if (r < V_B) {
+                    const uint2 w = *reinterpret_cast<const uint2*>(prm + d);
+                    const uint2 bb = *reinterpret_cast<const uint2*>(prm + V_D + d);
+                    o.x = pack_h2((v[i].x - mean) * rs * h_lo(w.x) + h_lo(bb.x), (v[i].y - mean) * rs * h_hi(w.x) + h_hi(bb.x));
+                    o.y = pack_h2((v[i].z - mean) * rs * h_lo(w.y) + h_lo(bb.y), (v[i].w - mean) * rs * h_hi(w.y) + h_hi(bb.y));
+                }
+                const int kb = d / TC_KB, piece = (d % TC_KB) >> 3;
+                *reinterpret_cast<uint2*>(dst + (size_t)kb * (TC_N * 128) + ((piece ^ (rb & 7)) << 4) + ((d & 4) ? 8 : 0)) = o;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, const unsigned char* __restrict__ tcg,
+                                          float* __restrict__ logit, u64* __restrict__ gbest) {
+    const u32 tmem = *reinterpret_cast<const volatile u32*>(c.smem + SM_MISC + MISC_TMEM);
+    const int rows = P[PT_LOG_NJ] * 16, n0 = P[PT_LOG_J0] * 16;
+    const int mtiles = (rows + TC_M - 1) / TC_M;
+    const int quarter = c.warp & 3, col0 = (c.warp >> 2) * 32;       // this warp reads lanes 32*quarter.., columns col0..col0+31
+#pragma unroll 1
+    for (int slab = 0; slab < TC_SLABS; slab++) {
+        // operand B of the slab: one bulk copy per block of 64 k into the K/V stages
+        if (c.tid == 0 && mtiles > 0) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect(tc_load_bar(c), TC_B_BYTES);
+#pragma unroll 1
+            for (int kb = 0; kb < TC_NKB; kb++)
+                bulk_g2s(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128), tcg + (size_t)slab * TC_B_BYTES + (size_t)kb * (TC_N * 128), TC_N * 128, tc_load_bar(c));
+        }
+        if (mtiles > 0) { wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u); c.tcl++; }
+        u64 mybest = 0;                                              // best (value, index) of sequence slab*64 + col0 + lane in this CTA's rows
+#pragma unroll 1
+        for (int mt = 0; mt < mtiles; mt++) {
+#pragma unroll 1
+            for (int kb = 0; kb < TC_NKB; kb++) {
+                const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+                wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+                if (c.warp == 0) {
+                    if (c.lane == 0 && !c.dead) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const u64 ad = tc_desc(smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES));
+                        const u64 bd = tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128));
+#pragma unroll
+                        for (int k = 0; k < TC_KB / 16; k++) tc_mma(tmem, ad + 2 * k, bd + 2 * k, (kb | k) ? 1u : 0u);   // 32 bytes further per step of 16 k
+                        tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
+                        if (kb == TC_NKB - 1) tc_commit(tc_done_bar(c));
+                    } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+                    __syncwarp();
+                } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+                c.chunk++;
+            }
+            // the accumulators of this tile: thread = vocabulary row, registers = 32 sequences
+            wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u); c.tcd++;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            u32 r[32];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                           "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                           "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                         : "r"(tmem + ((u32)(quarter * 32) << 16) + (u32)col0) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int nl = mt * TC_M + quarter * 32 + c.lane, n = n0 + nl;       // this thread's vocabulary row
+            const bool live = nl < rows && n < V_N && !c.dead;
+#pragma unroll
+            for (int i = 0; i < 32; i++) {
+                const int b = slab * TC_N + col0 + i;
+                const float v = __uint_as_float(r[i]);
+                if (live && b < V_B) logit[(size_t)b * V_N + n] = v;
+                // the warp's best row for sequence b: maximum by redux, lowest row among the equal ones by ballot
+                int kv = __float_as_int(live ? v : -3.0e38f);
+                kv = kv >= 0 ? kv : kv ^ 0x7fffffff;
+                const int km = __reduce_max_sync(0xffffffffu, kv);
+                const u32 who = __ballot_sync(0xffffffffu, kv == km && live);
+                if (who && c.lane == i) {
+                    const u64 k = best_key(__int_as_float(km >= 0 ? km : km ^ 0x7fffffff), (u32)(n - c.lane + (__ffs(who) - 1)));
+                    if (k > mybest) mybest = k;
+                }
+            }
+            // every warp is done reading before the next tile's first product overwrites the accumulators
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            cons_sync();
+        }
+        const int b = slab * TC_N + col0 + c.lane;
+        if (mybest && b < V_B) atomicMax(gbest + b, mybest);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
 // the step
 // ---------------------------------------------------------------------------------------------
 struct Args {
@@ -919,7 +1105,7 @@ struct Args {
 __device__ __forceinline__ void step_body(const Args& a) {
     extern __shared__ __align__(1024) unsigned char smem[];
     Ctx c;
-    c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false; c.kvi = 0; c.kvn = 0;
+    c.smem = smem; c.bar = a.bar; c.chunk = 0; c.dead = false; c.kvi = 0; c.kvn = 0; c.tcl = 0; c.tcd = 0;
     c.cta = blockIdx.x; c.ncta = gridDim.x; c.tid = threadIdx.x; c.warp = threadIdx.x >> 5; c.lane = threadIdx.x & 31;
 #if V_TIMING
     __shared__ u64 trace_[(V_NW + 1) * TRACE_EVENTS];
@@ -955,6 +1141,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (c.cta == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(0u) : "memory");   // nobody reads it before the first barrier
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
         for (int s = 0; s < V_KVST; s++) mbar_init(kv_bar(c, s), 1);
+        mbar_init(tc_load_bar(c), 1); mbar_init(tc_done_bar(c), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // operand tiles and K/V stages start as zero: rows of a batch tile beyond the batch stay zero for the whole
@@ -963,9 +1150,19 @@ __device__ __forceinline__ void step_body(const Args& a) {
     for (int i = c.tid; i < (SM_RED - SM_KV) / 16; i += NTHREADS) reinterpret_cast<uint4*>(smem + SM_KV)[i] = make_uint4(0, 0, 0, 0);
     __syncthreads();
 
+#if V_TC
+    // tensor memory for one accumulator tile; released by the same warp at the end of the kernel
+    if (c.warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(smem + SM_MISC + MISC_TMEM)), "n"(TC_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#endif
     const int* P = a.PT + c.cta * PT_STRIDE;
     if (c.warp == NW) {
-        if (c.lane == 0) producer(smem, a.bar, P, a.WP, c.cta, nsteps);
+        if (c.lane == 0) producer(smem, a.bar, P, a.WP, a.TM, c.cta, nsteps);
         return;
     }
 
@@ -980,6 +1177,9 @@ __device__ __forceinline__ void step_body(const Args& a) {
     float* part = a.S + V_OFF_PART;
     float* logit = a.S + V_OFF_LOGIT;
     unsigned char* actg = reinterpret_cast<unsigned char*>(a.S + V_OFF_ACTG);
+#if V_TC
+    unsigned char* tcg = reinterpret_cast<unsigned char*>(a.S + V_OFF_TC);
+#endif
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
@@ -1032,10 +1232,17 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
 #if V_LN_DIST
         if (first == PH_QKV || first == PH_FC || first == PH_LOGITS) {
+#if V_TC
+            if (first == PH_LOGITS) ln_rows_to_tc(c, zin, tcg);
+            else
+#endif
             ln_rows_to_global(c, (first == PH_FC) ? z1 : zin, (first == PH_QKV) ? z1 : (first == PH_FC) ? z2 : (float*)0, actg);
             phase_end(c);
             phase_wait(c);
         }
+#endif
+#if V_TC
+        if (first == PH_LOGITS) { logits_tc(c, P, tcg, logit, gbest); break; }
 #endif
 #pragma unroll 1
         for (int slab = 0; slab < ((first == PH_ATT) ? 0 : NSLAB); slab++) {
@@ -1233,6 +1440,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (*stop) break;
     }
   }
+#if V_TC
+    cons_sync();
+    if (c.warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(*reinterpret_cast<const volatile u32*>(smem + SM_MISC + MISC_TMEM)), "n"(TC_COLS) : "memory");
+#endif
     TICK(11);
 #if V_TIMING
     if (c.cta == V_TIMING - 1 && c.lane == 0)

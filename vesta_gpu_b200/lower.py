@@ -400,7 +400,14 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     off_part = off_q + up(B * D)
     off_actg = off_part + up(B * H * nch * (E + 2))
     off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * atile // 4) if ln_dist else 0)
-    scratch_floats = off_best + up(2 * B)
+    # Logits on tcgen05 tensor cores with accumulators in tensor memory, where the contraction is dense (64
+    # sequences and more): 128 vocabulary rows x 64 sequences per tile. The fp16 operand of 64 sequences
+    # (64 x D x 2 bytes) takes the place of the K/V stages, and a 128 x 64 tile of the table one ring slot.
+    tc_default = False          # until its parity run on the device has been seen
+    tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0 and 64 * D * 2 <= kvst * 2 * NW * 16 * 128
+                       and ch * 512 == 16384))
+    off_tc = off_best + up(2 * B)
+    scratch_floats = off_tc + (up(((B + 63) // 64) * 64 * D * 2 // 4) if tc else 0)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     fixed = smem_fixed(NB)
@@ -418,7 +425,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
@@ -474,5 +481,5 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                   barriers_per_launch=1 + 4 * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
-                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch), roles=roles)
+                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc), roles=roles)
     return low
