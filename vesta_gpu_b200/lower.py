@@ -404,8 +404,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     # sequences and more): 128 vocabulary rows x 64 sequences per tile. The fp16 operand of 64 sequences
     # (64 x D x 2 bytes) takes the place of the K/V stages, and a 128 x 64 tile of the table one ring slot.
     tc_default = False          # until its parity run on the device has been seen
-    tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0 and 64 * D * 2 <= kvst * 2 * NW * 16 * 128
-                       and ch * 512 == 16384))
+    tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
+              and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
     off_tc = off_best + up(2 * B)
     scratch_floats = off_tc + (up(((B + 63) // 64) * 64 * D * 2 // 4) if tc else 0)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
