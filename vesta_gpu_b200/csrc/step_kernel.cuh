@@ -623,23 +623,33 @@ __device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __re
 // per-chunk partial results (m, sum, unnormalised o[V_E]) of the attention phase, into operand
 // tiles 0..nk-1.
 #define PART_STRIDE (V_E + 2)
+#define ATT_MAXCH (V_NCH > V_TS ? V_NCH : V_TS)
+// work items of the attention phase: V_NCH position chunks for each of the first V_TAIL_BH (sequence, head) pairs,
+// V_TS chunks for each of the rest (the pairs left over after whole rounds of the grid: split so that the last
+// round is a fraction of an item for every CTA instead of a whole item for some)
+#define ATT_ITEMS (V_TAIL_BH * V_NCH + (V_B * V_H - V_TAIL_BH) * V_TS)
 __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, int row0, int nrows) {
     const int cols = nk * 16;
 #pragma unroll 1
     for (int i = c.tid; i < nrows * cols; i += NCONS) {
         const int b = i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
-        const float* p = part + (size_t)(((row0 + b) * V_H + h) * V_NCH) * PART_STRIDE;
+        // the chunks of (sequence, head): V_NCH of them, or V_TS for the items of the last, split round
+        const int bh = (row0 + b) * V_H + h;
+        const bool tail = bh >= V_TAIL_BH;
+        const int nchunks = tail ? V_TS : V_NCH;
+        const float* p = part + (size_t)(tail ? V_TAIL_BH * V_NCH + (bh - V_TAIL_BH) * V_TS : bh * V_NCH) * PART_STRIDE;
         // all loads first (independent, one round trip), then the arithmetic
-        float mm[V_NCH], dd[V_NCH], oo[V_NCH], M = -3.0e38f;
+        float mm[ATT_MAXCH], dd[ATT_MAXCH], oo[ATT_MAXCH], M = -3.0e38f;
 #pragma unroll
-        for (int ch = 0; ch < V_NCH; ch++) {
-            mm[ch] = __ldcg(p + ch * PART_STRIDE); dd[ch] = __ldcg(p + ch * PART_STRIDE + 1); oo[ch] = __ldcg(p + ch * PART_STRIDE + 2 + e);
+        for (int ch = 0; ch < ATT_MAXCH; ch++) {
+            mm[ch] = -3.0e38f; dd[ch] = 0.f; oo[ch] = 0.f;
+            if (ch < nchunks) { mm[ch] = __ldcg(p + ch * PART_STRIDE); dd[ch] = __ldcg(p + ch * PART_STRIDE + 1); oo[ch] = __ldcg(p + ch * PART_STRIDE + 2 + e); }
         }
 #pragma unroll
-        for (int ch = 0; ch < V_NCH; ch++) M = fmaxf(M, mm[ch]);
+        for (int ch = 0; ch < ATT_MAXCH; ch++) M = fmaxf(M, mm[ch]);
         float num = 0.f, den = 0.f;
 #pragma unroll
-        for (int ch = 0; ch < V_NCH; ch++) {
+        for (int ch = 0; ch < ATT_MAXCH; ch++) {
             const float w = fast_exp(mm[ch] - M);
             den += w * dd[ch];
             num += w * oo[ch];
@@ -673,15 +683,22 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 
 struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
 
+// (sequence, head), chunk and chunk count of item `it`
+__device__ __forceinline__ void att_item(int it, int& b, int& h, int& ch, int& nch) {
+    int bh;
+    if (it < V_TAIL_BH * V_NCH) { bh = it / V_NCH; ch = it - bh * V_NCH; nch = V_NCH; }
+    else { const int j = it - V_TAIL_BH * V_NCH; bh = V_TAIL_BH + j / V_TS; ch = j % V_TS; nch = V_TS; }
+    b = bh / V_H; h = bh - b * V_H;
+}
 __device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int ncta) {
-    if (a.it < V_B * V_H * V_NCH) {
-        const int ch = a.it % V_NCH, bh = a.it / V_NCH;
-        a.b = bh / V_H; a.h = bh - a.b * V_H;
-        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + V_NCH - 1) / V_NCH;
+    if (a.it < ATT_ITEMS) {
+        int ch, nch;
+        att_item(a.it, a.b, a.h, ch, nch);
+        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + nch - 1) / nch;
         a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
     }
 }
-__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < V_B * V_H * V_NCH; }
+__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < ATT_ITEMS; }
 __device__ __forceinline__ bool att_has_rows(const AttIter& a) { return a.hi > a.s; }      // an empty chunk is a tile without data
 __device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int ncta) {
     a.s += KV_POS;
@@ -798,10 +815,11 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         TRACE(44);
         const bool last = cur.s + KV_POS >= cur.hi;
         const int next_it = cur.it + c.ncta;
-        if (last && next_it < V_B * V_H * V_NCH) {
+        if (last && next_it < ATT_ITEMS) {
             // the next item's query is requested now and used after this tile
-            const int bh = next_it / V_NCH, nb_ = bh / V_H;
-            att_load_q(bqn, qbuf, nb_, bh - nb_ * V_H, g, t);
+            int nb_, nh_, ch_, nch_;
+            att_item(next_it, nb_, nh_, ch_, nch_);
+            att_load_q(bqn, qbuf, nb_, nh_, g, t);
         }
         const int cnt = min(KV_POS, cur.hi - cur.s);
         if (cnt > 0) {
@@ -1016,6 +1034,7 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
     for (int slab = 0; slab < TC_SLABS; slab++) {
         // operand B of the slab: one bulk copy per block of 64 k into the K/V stages
         if (c.tid == 0 && mtiles > 0) {
+            asm volatile("fence.proxy.async.global;" ::: "memory");          // the operand was written by other CTAs with ordinary stores
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect(tc_load_bar(c), TC_B_BYTES);
 #pragma unroll 1

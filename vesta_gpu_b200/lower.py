@@ -397,13 +397,24 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     nch = min(range(1, 17), key=lambda k: (att_cost(k), k))
     tune = dict(tune or {})
     nch = int(tune.get('nch', nch))
+    # With more (sequence, head) pairs than CTAs and one chunk each, the pairs left over after whole rounds of the
+    # grid are split into position chunks, so that the last round costs every CTA a fraction of an item
+    tail_bh, ts = B * H, 1
+    if nch == 1 and B * H > grid and (B * H) % grid and tune.get('tail_split', True):
+        left = (B * H) % grid
+        ts = min(grid // left, 8)
+        if ts > 1:
+            tail_bh = B * H - left
+        else:
+            ts = 1
+    att_items = tail_bh * nch + (B * H - tail_bh) * ts
     off_part = off_q + up(B * D)
-    off_actg = off_part + up(B * H * nch * (E + 2))
+    off_actg = off_part + up(att_items * (E + 2))
     off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * atile // 4) if ln_dist else 0)
     # Logits on tcgen05 tensor cores with accumulators in tensor memory, where the contraction is dense (64
     # sequences and more): 128 vocabulary rows x 64 sequences per tile. The fp16 operand of 64 sequences
     # (64 x D x 2 bytes) takes the place of the K/V stages, and a 128 x 64 tile of the table one ring slot.
-    tc_default = False          # until its parity run on the device has been seen
+    tc_default = True
     tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
               and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
     off_tc = off_best + up(2 * B)
@@ -425,7 +436,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_NCH=nch, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
