@@ -148,6 +148,7 @@ def main():
     ap.add_argument('--workload', default='cfg2', choices=sorted(WORKLOADS))
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--tune', default=None, help='JSON object of lowering options to override (experiments), e.g. {"kv_stages": 2}')
     args = ap.parse_args()
     from vesta_gpu_b200.shapes import SHAPES
     wl = dict(WORKLOADS[args.workload])
@@ -177,6 +178,7 @@ def main():
     if tmax > sh.C:
         raise SystemExit(f'prompt + steps = {tmax} exceeds the position table ({sh.C})')
     hf = SynthGPT2(sh, seed=0)
+    tune = json.loads(args.tune) if args.tune else None
     ragged = wl.get('ragged')
     if ragged:
         from vesta_gpu_b200.synth import make_ragged_prompts
@@ -184,7 +186,7 @@ def main():
         lens_all, toks_all = make_ragged_prompts(sh, B * world, ragged[0], ragged[1], seed=1)
         mine = partition(lens_all, world)[rank]
         lens, prompts = lens_all[mine], toks_all[mine]
-        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local, per_sequence_t=True, prompt_len=P)
+        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local, per_sequence_t=True, prompt_len=P, tune=tune)
         m.prompt.copy_(torch.from_numpy(prompts[:, :P].copy()))
         m.plen.copy_(torch.from_numpy(lens))
         start = torch.from_numpy((lens - P).astype(np.int32)).cuda()         # <= 0: every prompt ends at step P
@@ -193,7 +195,7 @@ def main():
     else:
         mine = list(range(rank * B, (rank + 1) * B))
         prompts = make_prompts(sh, B * world, P, seed=1)[rank * B:(rank + 1) * B]      # every rank its own sequences
-        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local)
+        m = VestaGPT2(hf, batch=B, tmax=tmax, device=local, tune=tune)
         pd = torch.from_numpy(prompts.copy()).cuda()
         ctx_lens = [[P + i + 1] * (B * world) for i in range(K)]
 
@@ -296,7 +298,7 @@ def main():
     line = dict(metric=METRIC, value=B * world * K / med, unit=UNIT, n_gpus=world, steps=K, warmup=Wm,
                 ms_per_step=1e3 * med / K, higher_is_better=True, scaling='strong' if total else 'weak', vs_baseline=None,
                 dtype='f16 weights and KV, f32 accumulate', data='synthetic',
-                config=dict(workload=args.workload, **{k: v for k, v in wl.items() if k != 'total'}, batch_per_gpu=B, repeats=args.repeats, steps_per_launch=min(args.per_launch, K),
+                config=dict(workload=args.workload, **{k: v for k, v in wl.items() if k != 'total'}, batch_per_gpu=B, repeats=args.repeats, steps_per_launch=min(args.per_launch, K), **({'tune': tune} if tune else {}),
                             l2='weights + KV read per step (%.0f MB) exceed the 126 MB L2' % (bytes_per_step / 1e6),
                             cv=round(statistics.pstdev(times) / statistics.mean(times), 4)),
                 clocks=clocks, gpu_launches=-(-K // args.per_launch),

@@ -131,6 +131,7 @@ def test_against_oracle_other_batches(batch):
     (5, None, dict(ln_dist=True)),                     # ... at a batch below one tile
     (20, 1, dict(ln_dist=False, act_lo=True)),         # every CTA normalises its slab, head + remainder
     (60, None, None),                                  # more (sequence, head) items than CTAs: several per CTA
+    (60, None, dict(tail_split=4)),                    # ... the items of the last round split into four position chunks
     (60, None, dict(kv_stages=2, nch=2)),              # ... with two K/V stages and two position chunks per item
     (64, None, dict(tc=True)),                         # 64 sequences and more: logits on tcgen05 / tensor memory
     (70, None, dict(tc=True)),                                # ... two slabs of 64 sequences, the second ragged

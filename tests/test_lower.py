@@ -160,3 +160,45 @@ def test_slabs_and_device_side_prompts():
     assert [p[0] for p in low.params][-2:] == ['prompt', 'plen'] and '#define V_PLEN 9' in low.src
     low = lower_for(TINY, 4, 16, feedback=False, prompt_len=9)            # nothing to feed back into
     assert [p[0] for p in low.params][-1] == 'vals' and '#define V_PLEN 0' in low.src
+
+
+def define(low, name):
+    for line in low.src.split('\n'):
+        if line.startswith(f'#define {name} '):
+            return int(line.split()[2])
+    raise KeyError(name)
+
+
+def test_tensor_core_logits_are_chosen_where_the_contraction_is_dense():
+    """64 sequences and more, fp16-head operands, an operand of 64 sequences that fits the K/V stages"""
+    assert define(lower_for(GPT2_SMALL, 64, 1025), 'V_TC') == 1
+    assert define(lower_for(GPT2_SMALL, 256, 640), 'V_TC') == 1
+    assert define(lower_for(GPT2_SMALL, 63, 64), 'V_TC') == 0
+    assert define(lower_for(GPT2_SMALL, 8, 384), 'V_TC') == 0
+    assert define(lower_for(GPT2_XL, 64, 64), 'V_TC') == 0              # 64 x 1600 halves exceed the stages
+    assert define(lower_for(GPT2_SMALL, 64, 64, tune=dict(tc=False)), 'V_TC') == 0
+    low = lower_for(GPT2_SMALL, 64, 1025)
+    assert low.scratch_floats * 4 >= define(low, 'V_OFF_TC') * 4 + 64 * 768 * 2
+
+
+def test_attention_items_cover_every_sequence_head_and_position():
+    """the item arithmetic of the attention phase (att_item / att_load_item in csrc/step_kernel.cuh) restated: whole
+    rounds of one item per (sequence, head), then the leftover pairs split into position chunks"""
+    for sh, B, tmax, tune in ((GPT2_SMALL, 64, 1025, None), (GPT2_SMALL, 1, 384, None), (TINY3, 60, 6, dict(tail_split=4)),
+                              (GPT2_SMALL, 64, 400, None)):
+        low = lower_for(sh, B, tmax, tune=tune)
+        nch, tail_bh, ts, H = define(low, 'V_NCH'), define(low, 'V_TAIL_BH'), define(low, 'V_TS'), low.dims['H']
+        items = tail_bh * nch + (B * H - tail_bh) * ts
+        for n in (1, 5, tmax):                                           # attended positions of every sequence
+            seen = np.zeros((B * H, n), np.int32)
+            for it in range(items):
+                if it < tail_bh * nch:
+                    bh, ch, k = it // nch, it % nch, nch
+                else:
+                    j = it - tail_bh * nch
+                    bh, ch, k = tail_bh + j // ts, j % ts, ts
+                cs = (max(n, 1) + k - 1) // k
+                seen[bh, ch * cs: min(n, (ch + 1) * cs)] += 1
+            assert seen.min() == 1 and seen.max() == 1
+        if sh is GPT2_SMALL and B == 64 and tmax == 1025:
+            assert ts == 4 and tail_bh == 740 and items <= 6 * 148        # five whole rounds and one of quarter items

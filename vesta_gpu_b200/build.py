@@ -49,13 +49,13 @@ def residue_spec(sh: Shape, batch, tmax, per_sequence_t=False):
     return spec
 
 
-def lower_for(sh: Shape, batch, tmax, feedback=True, timing=False, per_sequence_t=False, grid=148, prompt_len=0, slab_tiles=None):
+def lower_for(sh: Shape, batch, tmax, feedback=True, timing=False, per_sequence_t=False, grid=148, prompt_len=0, slab_tiles=None, tune=None):
     from .lower import lower
     from .program_text import decode_program
     per_token = ('x', 'keys', 'vals') + (('t',) if per_sequence_t else ())
     return lower(decode_program(sh), residue_spec(sh, batch, tmax, per_sequence_t), {'s': tmax}, batch=batch,
                  per_token=per_token, outputs=('logit', 'next'),
-                 feedback={'x': 'next', 't': 1} if feedback else None, timing=timing, grid=grid, prompt_len=prompt_len, slab_tiles=slab_tiles)
+                 feedback={'x': 'next', 't': 1} if feedback else None, timing=timing, grid=grid, prompt_len=prompt_len, slab_tiles=slab_tiles, tune=tune)
 
 
 def prebuild(sh: Shape, batch, tmax, verbose=False, **kw):
