@@ -69,7 +69,8 @@ int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dyna
 /* A TMA descriptor (128 bytes, written to `out` in host memory; copy it to 64-byte aligned device memory) for a
  * cache of fp16 rows laid out [planes][rows][row_elems]: one copy brings `box_rows` consecutive rows of 64
  * elements (128 bytes, one head) of one plane into shared memory with the 128-byte swizzle. The step kernel
- * reads its K and V tiles through four of these (K and V, boxes of 128 and of 32 rows). No counterpart in the
+ * reads its K and V tiles through eight of these (K and V, boxes of 32, 64, 96 and 128 rows) and the embedding
+ * table through a ninth (boxes of 128 rows). No counterpart in the
  * reference, whose generated folds read the cache with ordinary vector loads (vesta/lower.py:947-956). */
 int vesta_tensor_map_rows(void* out, const void* base, unsigned long long row_elems, unsigned long long rows,
                           unsigned long long planes, unsigned box_elems, unsigned box_rows);
@@ -86,7 +87,7 @@ void vesta_step_release(void* bound);
  * vesta_launch_cooperative would, but with the kernel's work space (fp32 scratch, counters, timing
  * sums, normally allocated by the caller) in a fixed array inside the library's device image,
  * vesta_static_scratch_bytes() bytes (4 MiB) per GPU for the life of the process. The caller passes
- * the residues (inputs, the KV cache), the packed weights, the plan table and the four K/V cache
+ * the residues (inputs, the KV cache), the packed weights, the plan table and the nine TMA
  * descriptors (vesta_tensor_map_rows, in device memory) it already owns, the
  * sizes the lowering reported (scratch_floats, counters) and where the logits and next lie in the
  * scratch; the results are copied to logits_out / next_out (device or pinned host memory) on

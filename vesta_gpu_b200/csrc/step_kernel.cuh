@@ -266,6 +266,7 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 // producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
 #define TC_SLABS_P ((V_B + 63) / 64)
+#define TMAP_WTE 8                               // index of the embedding table's descriptor at TM (after the eight of K and V)
 // leaving early: first let the copies still in flight land (bounded), so that none writes into shared memory
 // after the CTA has gone
 __device__ __noinline__ void producer_drain(Ctx& c) {
@@ -296,7 +297,7 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
                 if (c.dead) { producer_drain(c); return; }
                 mbar_expect(full_bar(c, slot), 128 * 128);
                 asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                             :: "r"(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES)), "l"(TM + 4 * 128), "r"(kb * 64), "r"(P[PT_LOG_J0] * 16 + mt * 128), "r"(0),
+                             :: "r"(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES)), "l"(TM + TMAP_WTE * 128), "r"(kb * 64), "r"(P[PT_LOG_J0] * 16 + mt * 128), "r"(0),
                                 "r"(full_bar(c, slot)) : "memory");
                 c.chunk++;
             }
@@ -662,8 +663,8 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // ---------------------------------------------------------------------------------------------
 // attention: this CTA's work items are (sequence, head, chunk of the positions); an item is processed
 // in tiles of KV_POS positions. A tile's K rows and V rows (128 B per position and head) come into shared
-// memory by TMA: one thread issues two tensor copies (cp.async.bulk.tensor, box = KV_POS rows of one head,
-// or KV_SMALL rows when that covers what is left of the item) that complete on the stage's mbarrier; the
+// memory by TMA: one thread issues two tensor copies (cp.async.bulk.tensor, box = the rows of one head that are
+// left of the item, rounded up to 32, at most KV_POS) that complete on the stage's mbarrier; the
 // 128-byte swizzle of the copy spreads the rows over the banks for ldmatrix. V_KVST stages are in flight.
 // The first V_KVST tiles are requested before the grid barrier that ends the QKV phase; the row of the
 // current position, which another CTA writes during that phase, is fetched after the barrier with ordinary
@@ -676,10 +677,10 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // Result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
 #define KV_POS (NW * 16)                         // positions per tile: sixteen per warp
-#define KV_SMALL 32                              // rows of the small box
+#define KV_SMALL 32                              // boxes of 32, 64, 96 and 128 rows
 #define KV_TILE_BYTES (KV_POS * 128)             // K (or V) rows of one tile
 #define KV_STAGE_BYTES (2 * KV_TILE_BYTES)       // K rows then V rows
-#define TMAP_BYTES 128                           // descriptors at TM: K, V (boxes of KV_POS rows), K, V (boxes of KV_SMALL rows)
+#define TMAP_BYTES 128                           // descriptors at TM: K, V with boxes of 32 rows, of 64, of 96, of 128; then the embedding table
 
 struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
 
@@ -717,12 +718,13 @@ __device__ __forceinline__ void tma_rows(u32 dst, const unsigned char* tmap, int
 __device__ __forceinline__ void att_issue(Ctx& c, const AttIter& a, int l, const unsigned char* __restrict__ TM) {
     if (c.tid == 0) {
         const u32 stage = c.kvi % V_KVST;
-        const bool small = a.hi - a.s <= KV_SMALL;
+        // the smallest box that covers what is left of the item: 32, 64, 96 or 128 rows
+        const int q = min((a.hi - a.s + KV_SMALL - 1) / KV_SMALL, KV_POS / KV_SMALL) - 1;
         const u32 bar = kv_bar(c, stage), dst = smem_u32(c.smem + SM_KV + stage * KV_STAGE_BYTES);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the stage was last written and read with ordinary accesses
-        mbar_expect(bar, small ? 2 * KV_SMALL * 128 : KV_STAGE_BYTES);
-        tma_rows(dst, TM + (small ? 2 : 0) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
-        tma_rows(dst + KV_TILE_BYTES, TM + (small ? 3 : 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+        mbar_expect(bar, 2 * (q + 1) * KV_SMALL * 128);
+        tma_rows(dst, TM + (2 * q) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+        tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
     }
     c.kvi++;
 }
@@ -1110,7 +1112,7 @@ struct Args {
     const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
-    const unsigned char* TM;                    // four TMA descriptors of the K/V cache
+    const unsigned char* TM;                    // TMA descriptors: eight of the K/V cache, one of the embedding table
     int nsteps;                                 // decode steps in this launch (the kernel feeds itself between them)
 };
 

@@ -180,17 +180,18 @@ class Kernel:
 
     def tensor_maps(self, residue):
         """the TMA descriptors of the step kernel, in device memory: the caches as the attention phase reads
-        them (K and V with boxes of 128 rows, K and V with boxes of 32 rows), and the embedding table in boxes
-        of 128 rows x 64 columns for the tensor-core logits (vesta_tensor_map_rows)"""
+        them (K and V with boxes of 32, 64, 96 and 128 rows of one head), then the embedding table in boxes of
+        128 rows x 64 columns for the tensor-core logits (vesta_tensor_map_rows)"""
         d = self.lowered.dims
-        host = torch.zeros(5 * 128, dtype=torch.uint8)
+        host = torch.zeros(9 * 128, dtype=torch.uint8)
+        for q, rows in enumerate((32, 64, 96, 128)):
+            for j, role in enumerate(('keys', 'vals')):
+                t = residue[self.lowered.roles[role]]
+                ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * (2 * q + j)), ctypes.c_void_p(t.data_ptr()),
+                                               d['D'], d['tmax'], d['B'] * d['L'], 64, rows))
         wte = residue[self.lowered.roles['wte']]
-        ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * 4), ctypes.c_void_p(wte.data_ptr()),
+        ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * 8), ctypes.c_void_p(wte.data_ptr()),
                                        d['D'], d['N'], 1, 64, 128))
-        for i, (role, rows) in enumerate((('keys', 128), ('vals', 128), ('keys', 32), ('vals', 32))):
-            t = residue[self.lowered.roles[role]]
-            ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * i), ctypes.c_void_p(t.data_ptr()),
-                                           d['D'], d['tmax'], d['B'] * d['L'], 64, rows))
         return host.to(self.device)
 
     def pack(self, residue=None):

@@ -365,8 +365,9 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         act_lo = bool(tune.get('act_lo', B <= 8 or (B <= 16 and D <= 1024)))
     atile = 512 if act_lo else 256
 
-    # K/V tiles in flight per CTA in the attention phase (32 KB each)
-    kvst = int(tune.get('kv_stages', 3))
+    # K/V tiles in flight per CTA in the attention phase (32 KB each): three where a CTA streams several (sequence,
+    # head) items per layer, two (and a deeper weight ring) where it has at most one (measured on B200)
+    kvst = int(tune.get('kv_stages', 3 if B * H > grid else 2))
 
     def smem_fixed(nb):
         return (kvst * (2 * NW * 16 * 128 + 256 + 8) + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
