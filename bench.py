@@ -254,10 +254,8 @@ def main():
         e0.record()
         seen = []
         for _ in range(K):
-            m.x.copy_(hx, non_blocking=True)        # host -> device: this step's input tokens
-            m.step()
-            hn.copy_(m.next(), non_blocking=True)   # device -> host: the chosen tokens
-            torch.cuda.current_stream().synchronize()
+            # host -> device: this step's input tokens; one launch; device -> host: the chosen tokens; synchronise
+            m.step_host(hx, hn)
             hx.copy_(hn.to(torch.int32))
             seen.append(hx.clone())
         e1.record()

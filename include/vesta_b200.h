@@ -79,6 +79,13 @@ int vesta_step_run(void* bound, void* stream, int steps);
  * of steps; it feeds its own token and position between them). The bound argument list must end with that
  * parameter. No counterpart in the reference, which launches once per step. */
 int vesta_step_run_fused(void* bound, void* stream, int steps, int per_launch);
+/* One decode step for a caller whose tokens live in host memory: copies `tokens_bytes` bytes from tokens_host to
+ * the device address tokens_dev (the residue x), launches the bound step once, copies `result_bytes` bytes from
+ * result_dev (e.g. the `next` values in the scratch) to result_host and waits for the stream. One call instead of
+ * the copy / step / read-back / synchronise sequence of the reference's host loop (bench/g0_bench.py:175-177 with
+ * the token copied from and to the host). Either copy is skipped when its host pointer is null. */
+int vesta_step_host(void* bound, void* stream, unsigned long long tokens_dev, const void* tokens_host, size_t tokens_bytes,
+                    unsigned long long result_dev, void* result_host, size_t result_bytes);
 void vesta_step_release(void* bound);
 
 /* No counterpart in the reference: one decode step for callers that must not allocate device

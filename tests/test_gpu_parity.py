@@ -325,6 +325,24 @@ def test_launch_of_many_steps_stops_at_the_end_of_the_cache():
     assert torch.equal(m.x, want_x) and (m.logits() - want_logits).abs().max() < 2e-3
 
 
+def test_host_driven_step_equals_the_device_loop():
+    """vesta_step_host (tokens from pinned host memory, chosen tokens back to it, one call per step) against the
+    kernel feeding itself"""
+    from vesta_gpu_b200.shapes import TINY3
+    m, _ = model(TINY3, 5, 'rich', 4, 12)
+    start = torch.tensor([3, 50, 200, 331], dtype=torch.int32)
+    m.reset(); m.x.copy_(start); m.k.launch(10, per_launch=1)
+    want_x, want_logits = m.x.cpu(), m.logits().cpu()
+    hx, hn = start.clone().pin_memory(), torch.empty(4, dtype=torch.float32).pin_memory()
+    m.reset()
+    for _ in range(10):
+        m.step_host(hx, hn)
+        hx.copy_(hn.to(torch.int32))
+    m.k.check()
+    assert torch.equal(hx, want_x) and torch.equal(m.x.cpu(), want_x)
+    assert (m.logits().cpu() - want_logits).abs().max() < 2e-3
+
+
 def test_out_of_range_inputs_are_refused_not_executed():
     from vesta_gpu_b200.shapes import TINY
     m, _ = model(TINY, 3, 'rich', 2, 8)

@@ -1240,7 +1240,14 @@ __device__ __forceinline__ void step_body(const Args& a) {
         TRACE(1 + first);
 
         if (first == PH_ATT) {
+#if V_TIMING
+            const long long att_t0 = clock64();
+#endif
             attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos, a.TM);
+#if V_TIMING
+            // every CTA's time in the attention phase of the middle layer (cycles), for the balance across the grid
+            if (l == V_L / 2 && c.tid == 0) a.TS[1024 + c.cta] = (u64)(clock64() - att_t0);
+#endif
         } else {
             // LN1 phase clears z2 (the MLP adds into it two barriers later); LN2 phase clears zin for the next layer
             // (not needed with the distributed LayerNorm, which starts those vectors with a plain store)

@@ -40,6 +40,9 @@ struct Driver {
     CUresult (*Launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                        CUstream, void**, void**) = nullptr;
     CUresult (*LaunchEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+    CUresult (*MemcpyHtoDAsync)(CUdeviceptr, const void*, size_t, CUstream) = nullptr;
+    CUresult (*MemcpyDtoHAsync)(void*, CUdeviceptr, size_t, CUstream) = nullptr;
+    CUresult (*StreamSynchronize)(CUstream) = nullptr;
     CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
@@ -64,7 +67,9 @@ int driver() {
               sym(lib, "cuModuleGetFunction", d.ModuleGetFunction) && sym(lib, "cuFuncSetAttribute", d.FuncSetAttribute) &&
               sym(lib, "cuOccupancyMaxActiveBlocksPerMultiprocessor", d.Occupancy) &&
               sym(lib, "cuLaunchCooperativeKernel", d.LaunchCooperative) && sym(lib, "cuLaunchKernel", d.Launch) &&
-              sym(lib, "cuLaunchKernelEx", d.LaunchEx) && sym(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled);
+              sym(lib, "cuLaunchKernelEx", d.LaunchEx) && sym(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled) &&
+              sym(lib, "cuMemcpyHtoDAsync_v2", d.MemcpyHtoDAsync) && sym(lib, "cuMemcpyDtoHAsync_v2", d.MemcpyDtoHAsync) &&
+              sym(lib, "cuStreamSynchronize", d.StreamSynchronize);
     if (!ok) return fail(-1, "libcuda.so.1 lacks a required driver entry point");
     d.lib = lib;
     g_cu = d;
@@ -290,6 +295,28 @@ int vesta_step_run(void* bound, void* stream, int steps) {
         CUresult r = g_cu.LaunchCooperative(b->fn, b->grid, 1, 1, b->block, 1, 1, b->smem, (CUstream)stream, b->ptrs.data());
         if (r != CUDA_SUCCESS) return cu(r, "cuLaunchCooperativeKernel");
     }
+    return 0;
+}
+
+int vesta_step_host(void* bound, void* stream, unsigned long long tokens_dev, const void* tokens_host, size_t tokens_bytes,
+                    unsigned long long result_dev, void* result_host, size_t result_bytes) {
+    if (!bound) return fail(-1, "vesta_step_host: not bound");
+    if (int e = driver()) return e;
+    Bound* b = (Bound*)bound;
+    CUstream st = (CUstream)stream;
+    CUresult r;
+    if (tokens_host && tokens_bytes) {
+        r = g_cu.MemcpyHtoDAsync((CUdeviceptr)tokens_dev, tokens_host, tokens_bytes, st);
+        if (r != CUDA_SUCCESS) return cu(r, "cuMemcpyHtoDAsync");
+    }
+    r = g_cu.LaunchCooperative(b->fn, b->grid, 1, 1, b->block, 1, 1, b->smem, st, b->ptrs.data());
+    if (r != CUDA_SUCCESS) return cu(r, "cuLaunchCooperativeKernel");
+    if (result_host && result_bytes) {
+        r = g_cu.MemcpyDtoHAsync(result_host, (CUdeviceptr)result_dev, result_bytes, st);
+        if (r != CUDA_SUCCESS) return cu(r, "cuMemcpyDtoHAsync");
+    }
+    r = g_cu.StreamSynchronize(st);
+    if (r != CUDA_SUCCESS) return cu(r, "cuStreamSynchronize");
     return 0;
 }
 

@@ -92,6 +92,12 @@ class VestaGPT2:
     def step(self, steps=1):
         self.k.launch(steps)
 
+    def step_host(self, tokens_host, next_host):
+        """one step for a host-side loop: tokens_host (pinned int32 [batch]) becomes x, the chosen tokens (the
+        `next` values, float32 [batch] as in the reference's scratch) land in next_host (pinned); returns when
+        they have"""
+        self.k.step_host(self.x, tokens_host, self.next(), next_host)
+
     def logits(self):
         return self.k.view('logit')
 

@@ -52,6 +52,7 @@ def lib():
         L.vesta_step_run.argtypes = [vp, vp, ci]
         L.vesta_step_run_fused.argtypes = [vp, vp, ci, ci]
         L.vesta_tensor_map_rows.argtypes = [vp, vp, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_ulonglong, ctypes.c_uint, ctypes.c_uint]
+        L.vesta_step_host.argtypes = [vp, vp, ctypes.c_ulonglong, vp, sz, ctypes.c_ulonglong, vp, sz]
         L.vesta_step_release.argtypes = [vp]
         L.vesta_step_release.restype = None
         _lib = L
@@ -217,6 +218,15 @@ class Kernel:
         else:
             ok(lib().vesta_step_run(self._bound, stream, steps))
             self.launches += steps
+
+    def step_host(self, x_dev, tokens_host, result_dev, result_host):
+        """one decode step with host buffers: tokens_host (pinned) -> x_dev, one launch, result_dev -> result_host
+        (pinned), stream synchronised on return: a single call into the library (vesta_step_host)"""
+        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+        ok(lib().vesta_step_host(self._bound, stream, x_dev.data_ptr(), ctypes.c_void_p(tokens_host.data_ptr()),
+                                 tokens_host.numel() * tokens_host.element_size(), result_dev.data_ptr(),
+                                 ctypes.c_void_p(result_host.data_ptr()), result_host.numel() * result_host.element_size()))
+        self.launches += 1
 
     def __call__(self, residue):
         self.bind(residue)
