@@ -136,6 +136,9 @@ def test_against_oracle_other_batches(batch):
     (64, None, dict(tc=True)),                         # 64 sequences and more: logits on tcgen05 / tensor memory
     (70, None, dict(tc=True)),                                # ... two slabs of 64 sequences, the second ragged
     (70, None, dict(tc=False)),                        # ... and the same batch on the mma.sync path
+    (33, 2, dict(ksplit=False)),                       # large batch with the projections as wide fold slices (148-way sums)
+    (9, 1, dict(ksplit=True)),                         # small batch with the projections as deep fold slices, GELU through global memory
+    (20, None, dict(ksplit=True, ln_dist=False)),      # ... with every CTA normalising its own rows
 ])
 def test_batches_above_one_slab(batch, slab_tiles, tune):
     """batches larger than the operand tiles in shared memory run slab by slab (the last slab ragged), in both

@@ -16,8 +16,8 @@ def stream_tiles(rec, dims, cta):
     base, layer, qj0, qnj, pj0, pnj, pk0, pnk, fj0, fnj, lj0, lnj = [int(v) for v in rec[cta][:12]]
     WG = dims['WG']                                  # output tiles per WIDE group of this lowering
 
-    def narrow(kind, l, j0, nj, kt):
-        return [(kind, l, j0 + i % nj, i // nj) for i in range(nj * kt)]
+    def narrow(kind, l, j0, nj, kt, k0=0):
+        return [(kind, l, j0 + i % nj, k0 + i // nj) for i in range(nj * kt)]
 
     def wide(kind, l, j0, nj, k0, nk):
         out = []
@@ -29,8 +29,13 @@ def stream_tiles(rec, dims, cta):
         return out
     tiles = []
     for l in range(L):
-        seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
-            + narrow('fc', l, fj0, fnj, KT_D) + wide('p2', l, 0, JT_D, fj0, fnj)
+        if dims['ksplit']:                           # both projections as (two output tiles x a slice of the fold)
+            qj0_, qnj_, qk0_, qnk_ = [int(v) for v in rec[cta][12:16]]
+            seg = narrow('qkv', l, qj0, qnj, KT_D) + narrow('proj', l, pj0, pnj, pnk, pk0) \
+                + narrow('fc', l, fj0, fnj, KT_D) + narrow('p2', l, qj0_, qnj_, qnk_, qk0_)
+        else:
+            seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
+                + narrow('fc', l, fj0, fnj, KT_D) + wide('p2', l, 0, JT_D, fj0, fnj)
         assert len(seg) == layer
         tiles += seg
     tiles += wide('logit', 0, lj0, lnj, 0, KT_D)
@@ -38,7 +43,8 @@ def stream_tiles(rec, dims, cta):
 
 
 @pytest.mark.parametrize('sh,batch,grid', [(GPT2_SMALL, 1, 148), (GPT2_SMALL, 8, 148), (TINY, 3, 148), (TINY3, 2, 148),
-                                           (GPT2_XL, 1, 148), (GPT2_SMALL, 8, 132), (TINY, 1, 7)])
+                                           (GPT2_XL, 1, 148), (GPT2_SMALL, 8, 132), (TINY, 1, 7),
+                                           (GPT2_SMALL, 64, 148), (TINY3, 40, 148), (GPT2_SMALL, 256, 132)])
 def test_every_weight_tile_exactly_once(sh, batch, grid):
     low = lower_for(sh, batch, 64, grid=grid)
     dims = low.dims

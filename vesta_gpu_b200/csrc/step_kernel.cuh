@@ -38,6 +38,7 @@ typedef unsigned short u16;
 #define NTHREADS (NCONS + 32)
 #define KT_D (V_D / 16)
 #define JT_D (V_D / 16)
+#define KT_F (V_F / 16)
 #define FRAG_BYTES 512
 #define WN_MAX 4                      // widest NARROW placement (output tiles per CTA)
 #define TPW V_TPW                     // output tiles a warp owns in a WIDE group (more where the batch is small:
@@ -130,6 +131,10 @@ __device__ __forceinline__ u64 best_key(float v, u32 n) {
 #define PT_FC_NJ 9
 #define PT_LOG_J0 10     // WIDE over the whole fold
 #define PT_LOG_NJ 11
+#define PT_P2_J0 12      // V_KSPLIT: the MLP projection as output tiles [j0, j0+nj) x fold tiles [k0, k0+nk)
+#define PT_P2_NJ 13
+#define PT_P2_K0 14
+#define PT_P2_NK 15
 
 // A step is a sequence of phases separated by grid barriers: per layer QKV, ATT, PROJ, MLP (= FC then
 // P2 inside the CTA), then LOGITS. Batches above one slab (SB = 8 * V_NB rows: what the operand
@@ -141,7 +146,15 @@ __device__ __forceinline__ u64 best_key(float v, u32 n) {
 #define PH_FC 3
 #define PH_P2 4
 #define PH_LOGITS 5
-#define PH_PER_LAYER 4                // QKV, ATT, PROJ, MLP
+// V_KSPLIT (large batches): the two projections that combine partial sums with fp32 atomics are placed as a
+// few output tiles x a slice of the fold per CTA (a 6-way instead of a 48- / 148-way sum); the MLP projection
+// then is a phase of its own, and the GELU output passes through global memory.
+#define PH_PER_LAYER (4 + V_KSPLIT)   // QKV, ATT, PROJ, MLP (or FC, P2)
+// the contractions of phase `pl` of a layer: first..last run inside the CTA without a barrier between them
+__device__ __forceinline__ void phase_kinds(int pl, int& first, int& last) {
+    first = (pl == 3) ? PH_FC : (pl == 4) ? PH_P2 : pl;
+    last = (first == PH_FC && !V_KSPLIT) ? PH_P2 : first;
+}
 #define SB (8 * V_NB)                 // rows per slab
 #define NSLAB ((V_B + SB - 1) / SB)
 
@@ -154,10 +167,10 @@ struct Seg { int rows, nj, off; bool wide; };
 __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
     Seg s;
     const int n_qkv = P[PT_QKV_NJ] * KT_D, n_proj = P[PT_PROJ_NJ] * P[PT_PROJ_NK], n_fc = P[PT_FC_NJ] * KT_D;
-    s.wide = (kind == PH_PROJ) | (kind == PH_P2) | (kind == PH_LOGITS);
-    s.rows = (kind == PH_PROJ) ? P[PT_PROJ_NK] : (kind == PH_P2) ? P[PT_FC_NJ] : KT_D;
+    s.wide = V_KSPLIT ? (kind == PH_LOGITS) : ((kind == PH_PROJ) | (kind == PH_P2) | (kind == PH_LOGITS));
+    s.rows = (kind == PH_PROJ) ? P[PT_PROJ_NK] : (kind == PH_P2) ? (V_KSPLIT ? P[PT_P2_NK] : P[PT_FC_NJ]) : KT_D;
     s.nj = (kind == PH_QKV) ? P[PT_QKV_NJ] : (kind == PH_PROJ) ? P[PT_PROJ_NJ] : (kind == PH_FC) ? P[PT_FC_NJ]
-         : (kind == PH_P2) ? JT_D : (kind == PH_LOGITS) ? P[PT_LOG_NJ] : 0;
+         : (kind == PH_P2) ? (V_KSPLIT ? P[PT_P2_NJ] : JT_D) : (kind == PH_LOGITS) ? P[PT_LOG_NJ] : 0;
     s.off = (kind == PH_PROJ) ? n_qkv : (kind == PH_FC) ? n_qkv + n_proj : (kind == PH_P2) ? n_qkv + n_proj + n_fc : 0;
     if (s.rows == 0) s.nj = 0;
     return s;
@@ -283,7 +296,9 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
 #pragma unroll 1
     for (int ph = 0; ph < nsteps * (V_L * PH_PER_LAYER + 1); ph++) {          // every step reads the same stream again
         const int l = (ph % (V_L * PH_PER_LAYER + 1)) / PH_PER_LAYER, pl = ph % (V_L * PH_PER_LAYER + 1);
-        const int first = (l == V_L) ? PH_LOGITS : (pl - l * PH_PER_LAYER == 3 ? PH_FC : pl - l * PH_PER_LAYER);
+        int first, last;
+        phase_kinds(pl - l * PH_PER_LAYER, first, last);
+        if (l == V_L) { first = PH_LOGITS; last = PH_LOGITS; }
         if (first == PH_ATT) continue;
 #if V_TC
         if (first == PH_LOGITS) {
@@ -304,7 +319,6 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
             continue;
         }
 #endif
-        const int last = (first == PH_FC) ? PH_P2 : first;
 #pragma unroll 1
         for (int slab = 0; slab < NSLAB; slab++)
 #pragma unroll 1
@@ -613,11 +627,14 @@ __device__ __forceinline__ void ln_rows_to_global(Ctx& c, const float* __restric
         }
     }
 }
-__device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __restrict__ tiles, unsigned char* act) {
+__device__ __forceinline__ void load_tiles(Ctx& c, const unsigned char* __restrict__ tiles, unsigned char* act, int bytes) {
 #pragma unroll 1
-    for (int i = c.tid; i < SLAB_TILE_BYTES / 16; i += NCONS) cp16(act + (size_t)i * 16, tiles + (size_t)i * 16);
+    for (int i = c.tid; i < bytes / 16; i += NCONS) cp16(act + (size_t)i * 16, tiles + (size_t)i * 16);
     cp_wait();
     cons_sync();
+}
+__device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __restrict__ tiles, unsigned char* act) {
+    load_tiles(c, tiles, act, SLAB_TILE_BYTES);
 }
 
 // Attention output for the fold range [k0*16, (k0+nk)*16) of the projection, merged from the
@@ -814,7 +831,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
 #pragma unroll 1
     while (att_valid(cur)) {
-        TRACE(44);
+        if (V_B <= 16) TRACE(44);
         const bool last = cur.s + KV_POS >= cur.hi;
         const int next_it = cur.it + c.ncta;
         if (last && next_it < ATT_ITEMS) {
@@ -838,7 +855,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 }
                 cons_sync();
             }
-            TRACE(45);
+            if (V_B <= 16) TRACE(45);
             const int p0 = c.warp * 16;                                 // this warp's positions of the tile
             if (p0 < cnt && !c.dead) {
                 // scores of 16 positions: rows g and g + 8 of the tile slice, in the lanes with t == 0
@@ -882,7 +899,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 }
             }
         }
-        TRACE(46);
+        if (V_B <= 16) TRACE(46);
         float* out = part + (size_t)cur.it * PART_STRIDE;
         // the warps' partial results of an item meet in shared memory; consecutive items use alternate buffers, so
         // that a warp that is already done with the next item does not overwrite what the merge is still reading
@@ -1201,6 +1218,9 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_TC
     unsigned char* tcg = reinterpret_cast<unsigned char*>(a.S + V_OFF_TC);
 #endif
+#if V_KSPLIT
+    unsigned char* gg = reinterpret_cast<unsigned char*>(a.S + V_OFF_GG);     // GELU outputs as operand tiles: [slab][fold tile][batch tile]
+#endif
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
@@ -1229,8 +1249,9 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #pragma unroll 1
     for (int ph = 0; ph < V_L * PH_PER_LAYER + 1; ph++) {
         const int l = ph / PH_PER_LAYER;
-        const int first = (l == V_L) ? PH_LOGITS : (ph - l * PH_PER_LAYER == 3 ? PH_FC : ph - l * PH_PER_LAYER);
-        const int last = (first == PH_FC) ? PH_P2 : first;
+        int first, last;
+        phase_kinds(ph - l * PH_PER_LAYER, first, last);
+        if (l == V_L) { first = PH_LOGITS; last = PH_LOGITS; }
         float* zin = Z + (size_t)((2 * l) % 3) * ZS;          // layer input (for LOGITS: the final state)
         float* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
         float* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
@@ -1289,6 +1310,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
                 }
                 else if (kind == PH_PROJ && P[PT_PROJ_NJ])
                     merge_to_act(c, part, P[PT_PROJ_K0], P[PT_PROJ_NK], act, row0, nrows);
+#if V_KSPLIT
+                else if (kind == PH_P2 && P[PT_P2_NJ])
+                    // the GELU outputs of the slab for this CTA's slice of the fold, written by the FC phase of all CTAs
+                    load_tiles(c, gg + ((size_t)slab * KT_F + P[PT_P2_K0]) * (V_NB * ATILE), act, P[PT_P2_NK] * (V_NB * ATILE));
+#endif
                 TRACE(10 + kind);
 
                 // ---- the contraction, group by group, each followed by its epilogue
@@ -1301,7 +1327,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
                     const int width = sg.wide ? min(WG, sg.nj - j) : sg.nj;
                     float acc[TPW][V_NB][4];
                     TRACE(50);
-                    gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2) ? gact : act, acc);
+                    gemm_group(c, sg.rows, width, sg.wide, (kind == PH_P2 && !V_KSPLIT) ? gact : act, acc);
                     TRACE(51);
                     if (!sg.wide) {
                         // NARROW: sum the warps that share an output tile; thread (jj, o) then owns one output
@@ -1318,6 +1344,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
                             for (int w = jj; w < NW; w += width) v += red[(size_t)w * V_NB * 128 + r];
                             const int i = r & 3, ln = (r >> 2) & 31, nb = r >> 7;
                             const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (ln & 3) * 2 + (i & 1), b = row0 + rb;
+                            if (kind == PH_PROJ || kind == PH_P2) {
+                                // a slice of the fold: added to the vector the LayerNorm pass started (residual + bias)
+                                if (rb < nrows) red_add(((kind == PH_PROJ) ? z1 : z2) + (size_t)b * V_D + (P[(kind == PH_PROJ) ? PT_PROJ_J0 : PT_P2_J0] + jj) * 16 + j_in, v);
+                                continue;
+                            }
                             v += h2f(prm[3 * V_D + jj * 16 + j_in]);
                             if (kind == PH_QKV) {
                                 // q to scratch, K and V rounded to fp16 into the cache at t
@@ -1332,7 +1363,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
                             } else {
                                 // g = gelu(u) -> operand tiles of the MLP projection: fold index = jj*16 + j_in
                                 const float g = (rb < nrows) ? V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))) : 0.f;
+#if V_KSPLIT
+                                act_store1(gg + (size_t)slab * KT_F * (V_NB * ATILE), rb, (P[PT_FC_J0] + jj) * 16 + j_in, g);
+#else
                                 act_store1(gact, rb, jj * 16 + j_in, g);
+#endif
                             }
                         }
                         cons_sync();
@@ -1387,12 +1422,12 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (first == PH_LOGITS) break;
 
         // ---- grid barrier; the next LayerNorm's parameters are fetched while waiting
-        TICK(2 + 2 * (ph - l * PH_PER_LAYER));
+        TICK(2 + 2 * min(ph - l * PH_PER_LAYER, 3));
         phase_end(c);
         if (first == PH_PROJ)
             fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
                          a.fcb + (size_t)l * V_F + P[PT_FC_J0] * 16, P[PT_FC_NJ]);
-        else if (first == PH_FC) {
+        else if (ph - l * PH_PER_LAYER == PH_PER_LAYER - 1) {
             if (l + 1 < V_L)
                 fetch_params(c, a.ln1w + (size_t)(l + 1) * V_D, a.ln1b + (size_t)(l + 1) * V_D, a.ob + (size_t)(l + 1) * V_D,
                              a.qkvb + (size_t)(l + 1) * 3 * V_D + P[PT_QKV_J0] * 16, P[PT_QKV_NJ]);
@@ -1402,7 +1437,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (first == PH_QKV) attention_prefetch(c, l, s_pos, a.TM);
         TRACE(30 + first);
         phase_wait(c);
-        TICK(3 + 2 * (ph - l * PH_PER_LAYER));
+        TICK(3 + 2 * min(ph - l * PH_PER_LAYER, 3));
     }
     TICK(10);
 
@@ -1519,11 +1554,11 @@ __device__ int pack_segment(const PackArgs& a, unsigned char* dst, const int* __
     const Seg s = seg_of(P, kind);
     const int n = s.rows * s.nj;
     const int j0 = (kind == PH_QKV) ? P[PT_QKV_J0] : (kind == PH_PROJ) ? P[PT_PROJ_J0] : (kind == PH_FC) ? P[PT_FC_J0]
-                 : (kind == PH_LOGITS) ? P[PT_LOG_J0] : 0;
-    const int k0 = (kind == PH_PROJ) ? P[PT_PROJ_K0] : (kind == PH_P2) ? P[PT_FC_J0] : 0;
+                 : (kind == PH_LOGITS) ? P[PT_LOG_J0] : (kind == PH_P2 && V_KSPLIT) ? P[PT_P2_J0] : 0;
+    const int k0 = (kind == PH_PROJ) ? P[PT_PROJ_K0] : (kind == PH_P2) ? (V_KSPLIT ? P[PT_P2_K0] : P[PT_FC_J0]) : 0;
     for (int i = wid; i < n; i += nwarp) {
         int jt, kt;
-        if (!s.wide) { jt = j0 + i % s.nj; kt = i / s.nj; }
+        if (!s.wide) { jt = j0 + i % s.nj; kt = k0 + i / s.nj; }
         else {
             const int grp = i / (WG * s.rows);                 // full groups before this tile hold WG*rows tiles
             const int width = min(WG, s.nj - grp * WG);

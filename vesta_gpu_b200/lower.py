@@ -232,14 +232,16 @@ def _spread(total, loads, cap):
     return counts
 
 
-def place_step(dims, grid):
-    """-> (int32 [grid, PT_STRIDE] placement records, tiles per CTA stream, plan notes)"""
+def place_step(dims, grid, ksplit=False):
+    """-> (int32 [grid, PT_STRIDE] placement records, tiles per CTA stream, plan notes). ksplit: the attention
+    projection and the MLP projection as units of two output tiles x a slice of the fold (as few slices as fill
+    the grid), the MLP projection independent of where the FC tiles are"""
     D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
     KT_D, KT_F, JT_D, JT_J, JT_N = D // 16, F // 16, D // 16, 3 * D // 16, (N + 15) // 16
     G = grid
     # FC / MLP-proj: every f tile costs 2*KT_D tiles of stream; at most WN_MAX per CTA
     fc = _spread(KT_F, [0.0] * G, WN_MAX)
-    load = [2.0 * KT_D * n for n in fc]
+    load = [(1.0 if ksplit else 2.0) * KT_D * n for n in fc]
     # QKV: every output tile costs KT_D tiles of stream
     cnt = [0] * G
     for _ in range(JT_J):
@@ -247,20 +249,32 @@ def place_step(dims, grid):
         cnt[c] += 1
         load[c] += KT_D
     qkv = cnt
-    # attn-proj: groups of 8 output tiles x slices of the fold, one unit per CTA
-    groups = math.ceil(JT_D / WG)
-    splits = max(1, min(KT_D, G // groups))
-    nk = math.ceil(KT_D / splits)
-    units = [(jg, k0) for jg in range(groups) for k0 in range(0, KT_D, nk)]
-    if len(units) > G:
-        raise NotImplementedError('placement: projection units exceed the grid')
-    proj = [None] * G
-    order = sorted(range(G), key=lambda i: (load[i], i))
-    for (jg, k0), c in zip(units, order):
-        j0, nj = jg * WG, min(WG, JT_D - jg * WG)
-        kk = min(nk, KT_D - k0)
-        proj[c] = (j0, nj, k0, kk)
-        load[c] += nj * kk
+
+    def units_of(kt, wj):
+        """output tiles in groups of wj x slices of a fold of kt tiles, one unit per CTA"""
+        groups = math.ceil(JT_D / wj)
+        splits = max(1, min(kt, G // groups))
+        nk = math.ceil(kt / splits)
+        us = [(jg * wj, min(wj, JT_D - jg * wj), k0, min(nk, kt - k0)) for jg in range(groups) for k0 in range(0, kt, nk)]
+        if len(us) > G:
+            raise NotImplementedError('placement: projection units exceed the grid')
+        return us, nk
+
+    def deal(us):
+        out = [None] * G
+        order = sorted(range(G), key=lambda i: (load[i], i))
+        for u, c in zip(us, order):
+            out[c] = u
+            load[c] += u[1] * u[3]
+        return out
+    # attn-proj: groups of WG output tiles x slices of the fold, one unit per CTA (ksplit: groups of two)
+    units, nk = units_of(KT_D, 2 if ksplit else WG)
+    proj = deal(units)
+    p2 = [None] * G
+    p2_nk = 0
+    if ksplit:
+        units2, p2_nk = units_of(KT_F, 2)
+        p2 = deal(units2)
     # logits: output tiles over the whole fold; balance the whole step (layers x per-layer load + logits)
     step_load = [L * v for v in load]
     cnt = [0] * G
@@ -275,8 +289,10 @@ def place_step(dims, grid):
     fj = qj = lj = 0
     for c in range(G):
         pj0, pnj, pk0, pnk = proj[c] or (0, 0, 0, 0)
-        layer = qkv[c] * KT_D + pnj * pnk + fc[c] * KT_D + JT_D * fc[c]
+        qj0, qnj, qk0, qnk = p2[c] or (0, 0, 0, 0)
+        layer = qkv[c] * KT_D + pnj * pnk + fc[c] * KT_D + (qnj * qnk if ksplit else JT_D * fc[c])
         rec[c, :12] = (base, layer, qj, qkv[c], pj0, pnj, pk0, pnk, fj, fc[c], lj, logit[c])
+        rec[c, 12:16] = (qj0, qnj, qk0, qnk)
         qj += qkv[c]; fj += fc[c]; lj += logit[c]
         base += L * layer + logit[c] * KT_D
     assert qj == JT_J and fj == KT_F and lj == JT_N
@@ -284,7 +300,7 @@ def place_step(dims, grid):
         raise NotImplementedError('packed weights exceed the 32-bit tile index')
     per = rec[:, 1].astype(np.int64) * L + rec[:, 11].astype(np.int64) * KT_D
     notes = dict(tiles_total=int(base), tiles_min=int(per.min()), tiles_max=int(per.max()),
-                 tiles_mean=float(per.mean()), proj_units=len(units), proj_nk=nk)
+                 tiles_mean=float(per.mean()), proj_units=len(units), proj_nk=nk, p2_nk=p2_nk)
     return rec, int(base), notes
 
 
@@ -383,7 +399,15 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     tpw = int(tune.get('tpw', 2))
     wg = tpw * NW
     ch = max(CHUNK_TILES, wg)
-    rec, tiles, notes = place_step(dims, grid)
+    # Option (tune['ksplit'], off by default): the projections that combine partial sums with fp32 atomics get few,
+    # deep slices of the fold (a 6-way instead of a 48- / 148-way sum), at the price of one more grid barrier per
+    # layer and the GELU output passing through global memory; possible where a slice of the MLP fold fits the
+    # operand tiles. Measured on B200 it is slower (batch 64: 1,068 against 1,037 us per step; 256 ragged
+    # sequences: 3,400 against 3,146): the atomics are not what the MLP phase waits for.
+    _groups = math.ceil((D // 16) / 2)
+    _nk = math.ceil((F // 16) / max(1, min(F // 16, grid // _groups))) if _groups <= grid else 1 << 30
+    ksplit = bool(tune.get('ksplit', False) and _nk <= KT_D and _groups <= grid)
+    rec, tiles, notes = place_step(dims, grid, ksplit)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
     def up(v, a=64):
@@ -422,7 +446,9 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
               and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
     off_tc = off_best + up(2 * B)
-    scratch_floats = off_tc + (up(((B + 63) // 64) * 64 * D * 2 // 4) if tc else 0)
+    off_gg = off_tc + (up(((B + 63) // 64) * 64 * D * 2 // 4) if tc else 0)
+    # V_KSPLIT: the GELU outputs as operand tiles, per slab [fold tile of F][batch tile]
+    scratch_floats = off_gg + (up(((B + 8 * NB - 1) // (8 * NB)) * (F // 16) * NB * atile // 4) if ksplit else 0)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     fixed = smem_fixed(NB)
@@ -440,7 +466,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
@@ -494,7 +520,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
         + ['logits', 'finish']
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
-                  barriers_per_launch=1 + 4 * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
+                  barriers_per_launch=1 + (4 + int(ksplit)) * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
-                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc), roles=roles)
+                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc, ksplit=ksplit), roles=roles)
     return low
