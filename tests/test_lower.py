@@ -29,9 +29,9 @@ def stream_tiles(rec, dims, cta):
         return out
     tiles = []
     for l in range(L):
-        if dims['ksplit']:                           # both projections as (two output tiles x a slice of the fold)
+        if dims['ksplit']:                           # the MLP projection as (two output tiles x a slice of the fold)
             qj0_, qnj_, qk0_, qnk_ = [int(v) for v in rec[cta][12:16]]
-            seg = narrow('qkv', l, qj0, qnj, KT_D) + narrow('proj', l, pj0, pnj, pnk, pk0) \
+            seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
                 + narrow('fc', l, fj0, fnj, KT_D) + narrow('p2', l, qj0_, qnj_, qnk_, qk0_)
         else:
             seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
@@ -46,7 +46,8 @@ def stream_tiles(rec, dims, cta):
                                            (GPT2_XL, 1, 148), (GPT2_SMALL, 8, 132), (TINY, 1, 7),
                                            (GPT2_SMALL, 64, 148), (TINY3, 40, 148), (GPT2_SMALL, 256, 132)])
 def test_every_weight_tile_exactly_once(sh, batch, grid):
-    low = lower_for(sh, batch, 64, grid=grid)
+    low = lower_for(sh, batch, 64, grid=grid, tune=dict(ksplit=True) if batch >= 40 else None)
+    assert low.dims['ksplit'] == (batch >= 40)
     dims = low.dims
     D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
     want = {'qkv': (3 * D // 16, D // 16), 'proj': (D // 16, D // 16), 'fc': (F // 16, D // 16),

@@ -146,9 +146,9 @@ __device__ __forceinline__ u64 best_key(float v, u32 n) {
 #define PH_FC 3
 #define PH_P2 4
 #define PH_LOGITS 5
-// V_KSPLIT (large batches): the two projections that combine partial sums with fp32 atomics are placed as a
-// few output tiles x a slice of the fold per CTA (a 6-way instead of a 48- / 148-way sum); the MLP projection
-// then is a phase of its own, and the GELU output passes through global memory.
+// V_KSPLIT (an option): the MLP projection, which combines partial sums with fp32 atomics, is placed as two
+// output tiles x a slice of the fold per CTA (a 6-way instead of a 148-way sum); it then is a phase of its own,
+// and the GELU output passes through global memory.
 #define PH_PER_LAYER (4 + V_KSPLIT)   // QKV, ATT, PROJ, MLP (or FC, P2)
 // the contractions of phase `pl` of a layer: first..last run inside the CTA without a barrier between them
 __device__ __forceinline__ void phase_kinds(int pl, int& first, int& last) {
@@ -167,7 +167,7 @@ struct Seg { int rows, nj, off; bool wide; };
 __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
     Seg s;
     const int n_qkv = P[PT_QKV_NJ] * KT_D, n_proj = P[PT_PROJ_NJ] * P[PT_PROJ_NK], n_fc = P[PT_FC_NJ] * KT_D;
-    s.wide = V_KSPLIT ? (kind == PH_LOGITS) : ((kind == PH_PROJ) | (kind == PH_P2) | (kind == PH_LOGITS));
+    s.wide = (kind == PH_PROJ) | (kind == PH_P2 && !V_KSPLIT) | (kind == PH_LOGITS);
     s.rows = (kind == PH_PROJ) ? P[PT_PROJ_NK] : (kind == PH_P2) ? (V_KSPLIT ? P[PT_P2_NK] : P[PT_FC_NJ]) : KT_D;
     s.nj = (kind == PH_QKV) ? P[PT_QKV_NJ] : (kind == PH_PROJ) ? P[PT_PROJ_NJ] : (kind == PH_FC) ? P[PT_FC_NJ]
          : (kind == PH_P2) ? (V_KSPLIT ? P[PT_P2_NJ] : JT_D) : (kind == PH_LOGITS) ? P[PT_LOG_NJ] : 0;

@@ -233,9 +233,9 @@ def _spread(total, loads, cap):
 
 
 def place_step(dims, grid, ksplit=False):
-    """-> (int32 [grid, PT_STRIDE] placement records, tiles per CTA stream, plan notes). ksplit: the attention
-    projection and the MLP projection as units of two output tiles x a slice of the fold (as few slices as fill
-    the grid), the MLP projection independent of where the FC tiles are"""
+    """-> (int32 [grid, PT_STRIDE] placement records, tiles per CTA stream, plan notes). ksplit: the MLP projection
+    as units of two output tiles x a slice of the fold (as few slices as fill the grid), independent of where the
+    FC tiles are"""
     D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
     KT_D, KT_F, JT_D, JT_J, JT_N = D // 16, F // 16, D // 16, 3 * D // 16, (N + 15) // 16
     G = grid
@@ -267,8 +267,8 @@ def place_step(dims, grid, ksplit=False):
             out[c] = u
             load[c] += u[1] * u[3]
         return out
-    # attn-proj: groups of WG output tiles x slices of the fold, one unit per CTA (ksplit: groups of two)
-    units, nk = units_of(KT_D, 2 if ksplit else WG)
+    # attn-proj: groups of WG output tiles x slices of the fold, one unit per CTA
+    units, nk = units_of(KT_D, WG)
     proj = deal(units)
     p2 = [None] * G
     p2_nk = 0
@@ -399,14 +399,15 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     tpw = int(tune.get('tpw', 2))
     wg = tpw * NW
     ch = max(CHUNK_TILES, wg)
-    # Option (tune['ksplit'], off by default): the projections that combine partial sums with fp32 atomics get few,
-    # deep slices of the fold (a 6-way instead of a 48- / 148-way sum), at the price of one more grid barrier per
-    # layer and the GELU output passing through global memory; possible where a slice of the MLP fold fits the
-    # operand tiles. Measured on B200 it is slower (batch 64: 1,068 against 1,037 us per step; 256 ragged
-    # sequences: 3,400 against 3,146): the atomics are not what the MLP phase waits for.
+    # Large batches: the MLP projection, which combines partial sums with fp32 atomics, gets few, deep slices of the
+    # fold (a 6-way instead of a 148-way sum: its atomics cost 1,900 cycles per group of 16 output tiles and slab),
+    # at the price of one more grid barrier per layer and the GELU output passing through global memory; possible
+    # where a slice of the MLP fold fits the operand tiles. Measured on B200: batch 64, 1,037 -> 938 us per step;
+    # 256 ragged sequences, 3,146 -> 2,735. (The same placement for the attention projection was slower: its
+    # operand is merged from the attention partials element by element, eight times more of them per CTA.)
     _groups = math.ceil((D // 16) / 2)
     _nk = math.ceil((F // 16) / max(1, min(F // 16, grid // _groups))) if _groups <= grid else 1 << 30
-    ksplit = bool(tune.get('ksplit', False) and _nk <= KT_D and _groups <= grid)
+    ksplit = bool(tune.get('ksplit', B >= 32) and _nk <= KT_D and _groups <= grid)
     rec, tiles, notes = place_step(dims, grid, ksplit)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
