@@ -1336,13 +1336,26 @@ __device__ __forceinline__ void step_body(const Args& a) {
                             *reinterpret_cast<float4*>(red + ((size_t)(c.warp * V_NB + nb) * 32 + c.lane) * 4) = make_float4(acc[0][nb][0], acc[0][nb][1], acc[0][nb][2], acc[0][nb][3]);
                         cons_sync();
                         TRACE(52);
+                        // One batch tile: a thread per output (256 of them for two output tiles). More: a thread takes the
+                        // four sums of one lane of an output tile and reads the warps' partial tiles 16 bytes at a time.
+#define EPI4 (V_NB >= 2)
 #pragma unroll 1
-                        for (int o = c.tid; o < width * V_NB * 128; o += NCONS) {
-                            const int jj = o / (V_NB * 128), r = o - jj * (V_NB * 128);
-                            float v = 0.f;
+                        for (int o4 = c.tid; o4 < width * V_NB * (EPI4 ? 32 : 128); o4 += NCONS) {
+                          const int per = V_NB * (EPI4 ? 32 : 128);
+                          const int jj = o4 / per, r4 = o4 - jj * per;
+                          float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
-                            for (int w = jj; w < NW; w += width) v += red[(size_t)w * V_NB * 128 + r];
-                            const int i = r & 3, ln = (r >> 2) & 31, nb = r >> 7;
+                          for (int w = jj; w < NW; w += width) {
+                              if (EPI4) {
+                                  const float4 p4 = *reinterpret_cast<const float4*>(red + ((size_t)w * V_NB * 32 + r4) * 4);
+                                  v4.x += p4.x; v4.y += p4.y; v4.z += p4.z; v4.w += p4.w;
+                              } else v4.x += red[(size_t)w * V_NB * 128 + r4];
+                          }
+                          const int ln = EPI4 ? (r4 & 31) : ((r4 >> 2) & 31), nb = EPI4 ? (r4 >> 5) : (r4 >> 7);
+#pragma unroll 1
+                          for (int i4 = 0; i4 < (EPI4 ? 4 : 1); i4++) {
+                            const int i = EPI4 ? i4 : (r4 & 3);
+                            float v = (!EPI4 || i4 == 0) ? v4.x : i4 == 1 ? v4.y : i4 == 2 ? v4.z : v4.w;
                             const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (ln & 3) * 2 + (i & 1), b = row0 + rb;
                             if (kind == PH_PROJ || kind == PH_P2) {
                                 // a slice of the fold: added to the vector the LayerNorm pass started (residual + bias)
@@ -1369,6 +1382,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
                                 act_store1(gact, rb, jj * 16 + j_in, g);
 #endif
                             }
+                          }
                         }
                         cons_sync();
                     } else {
