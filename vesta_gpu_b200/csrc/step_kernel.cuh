@@ -193,11 +193,12 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define MISC_STAT ((MISC_POS + V_B * 4 + 15) & ~15)                // 8 x 2 floats
 #define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
 #define MISC_STOP (MISC_FLAG + 4)                                 // one int: the consumers are leaving
+#define MISC_ATTSEQ (MISC_FLAG + 12)                              // one u32: attention phases the consumers have opened
 #define MISC_TMEM (MISC_FLAG + 8)                                 // one u32: base address of this CTA's tensor memory (V_TC)
 #define MISC_SIDE (MISC_FLAG + 16)                                // per K/V stage: the K row and the V row of the current position
 #define SM_MISC_BYTES (MISC_SIDE + V_KVST * 256)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
-#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + V_KVST + 2) * 8)        // + operand-loaded and products-done barriers of the tensor-core logits
+#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + 2 * V_KVST + 2) * 8)        // + operand-loaded and products-done barriers of the tensor-core logits
 
 struct Ctx {
     unsigned char* smem;
@@ -275,6 +276,96 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
     if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
 }
 
+// ---- K/V tiles of the attention phase (the arithmetic is further down, at attention_phase) ----
+#define ATT_MAXCH (V_NCH > V_TS ? V_NCH : V_TS)
+// work items of the attention phase: V_NCH position chunks for each of the first V_TAIL_BH (sequence, head) pairs,
+// V_TS chunks for each of the rest (the pairs left over after whole rounds of the grid: split so that the last
+// round is a fraction of an item for every CTA instead of a whole item for some)
+#define ATT_ITEMS (V_TAIL_BH * V_NCH + (V_B * V_H - V_TAIL_BH) * V_TS)
+#define KV_POS (NW * 16)                         // positions per tile: sixteen per warp
+#define KV_SMALL 32                              // boxes of 32, 64, 96 and 128 rows
+#define KV_TILE_BYTES (KV_POS * 128)             // K (or V) rows of one tile
+#define KV_STAGE_BYTES (2 * KV_TILE_BYTES)       // K rows then V rows
+#define TMAP_BYTES 128                           // descriptors at TM: K, V with boxes of 32 rows, of 64, of 96, of 128; then the embedding table
+
+struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
+
+// (sequence, head), chunk and chunk count of item `it`
+__device__ __forceinline__ void att_item(int it, int& b, int& h, int& ch, int& nch) {
+    int bh;
+    if (it < V_TAIL_BH * V_NCH) { bh = it / V_NCH; ch = it - bh * V_NCH; nch = V_NCH; }
+    else { const int j = it - V_TAIL_BH * V_NCH; bh = V_TAIL_BH + j / V_TS; ch = j % V_TS; nch = V_TS; }
+    b = bh / V_H; h = bh - b * V_H;
+}
+__device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int ncta) {
+    if (a.it < ATT_ITEMS) {
+        int ch, nch;
+        att_item(a.it, a.b, a.h, ch, nch);
+        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + nch - 1) / nch;
+        a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
+    }
+}
+__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < ATT_ITEMS; }
+__device__ __forceinline__ bool att_has_rows(const AttIter& a) { return a.hi > a.s; }      // an empty chunk is a tile without data
+__device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int ncta) {
+    a.s += KV_POS;
+    if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
+}
+__device__ __forceinline__ u32 kv_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + stage) * 8; }
+// byte offset of the 16-byte piece `piece` of row `row` in a swizzled tile
+__device__ __forceinline__ int kv_off(int row, int piece) { return row * 128 + ((piece ^ (row & 7)) << 4); }
+
+__device__ __forceinline__ void tma_rows(u32 dst, const unsigned char* tmap, int x, int row, int plane, u32 bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 :: "r"(dst), "l"(tmap), "r"(x), "r"(row), "r"(plane), "r"(bar) : "memory");
+}
+
+__device__ __forceinline__ u32 kv_empty_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST + 2 + stage) * 8; }
+
+// The producer thread's part of an attention phase: once the consumer warps have finished the QKV contraction of the
+// layer (att_go), it requests this CTA's K/V tiles in order, each as soon as the stage it goes to has been released
+// by all consumer warps. The first V_KVST requests can precede the grid barrier that ends the QKV phase (their row
+// of the current position may be stale: the consumers patch it); every later one follows a release made after it.
+__device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_pos, const unsigned char* __restrict__ TM, int ncta) {
+    {
+        // a counter, not a barrier: the consumers may be a whole phase ahead of this thread in a CTA without weight tiles
+        const volatile u32* seq = reinterpret_cast<const volatile u32*>(c.smem + SM_MISC + MISC_ATTSEQ);
+        const volatile int* stop = reinterpret_cast<const volatile int*>(c.smem + SM_MISC + MISC_STOP);
+        c.tcl++;
+        const u64 t0 = now_ns();
+        u32 spins = 0;
+        while ((int)(*seq - c.tcl) < 0) {
+            if (*stop) { c.dead = true; return; }
+            if ((++spins & 63u) == 0) {
+                if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; return; }
+                if (now_ns() - t0 > WAIT_NS) { give_up(c.bar, 0x800u, c.cta); c.dead = true; return; }
+            }
+        }
+        __threadfence_block();
+    }
+    AttIter a; a.it = c.cta;
+    att_load_item(a, s_pos, ncta);
+#pragma unroll 1
+    while (att_valid(a) && !c.dead) {
+        if (att_has_rows(a)) {
+            const u32 stage = c.kvi % V_KVST;
+            wait_mbar(c, kv_empty_bar(c, stage), ((c.kvi / V_KVST) & 1u) ^ 1u, 0x800u);
+            if (c.dead) break;
+            // the smallest box that covers what is left of the item: 32, 64, 96 or 128 rows
+            const int q = min((a.hi - a.s + KV_SMALL - 1) / KV_SMALL, KV_POS / KV_SMALL) - 1;
+            const u32 bar = kv_bar(c, stage), dst = smem_u32(c.smem + SM_KV + stage * KV_STAGE_BYTES);
+            // rows that other CTAs wrote with ordinary stores, a stage that was read and patched with ordinary accesses
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect(bar, 2 * (q + 1) * KV_SMALL * 128);
+            tma_rows(dst, TM + (2 * q) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+            tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+            c.kvi++;
+        }
+        att_advance(a, s_pos, ncta);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
@@ -289,9 +380,10 @@ __device__ __noinline__ void producer_drain(Ctx& c) {
     }
 }
 __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP,
-                                      const unsigned char* __restrict__ TM, int cta, int nsteps) {
+                                      const unsigned char* __restrict__ TM, int cta, int ncta, int nsteps) {
     Ctx c;
-    c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta;
+    c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta; c.kvi = 0; c.tcl = 0;
+    const int* s_pos = reinterpret_cast<const int*>(smem + SM_MISC + MISC_POS);
     const unsigned char* base = WP + (size_t)(u32)P[PT_BASE] * FRAG_BYTES;
 #pragma unroll 1
     for (int ph = 0; ph < nsteps * (V_L * PH_PER_LAYER + 1); ph++) {          // every step reads the same stream again
@@ -299,7 +391,11 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
         int first, last;
         phase_kinds(pl - l * PH_PER_LAYER, first, last);
         if (l == V_L) { first = PH_LOGITS; last = PH_LOGITS; }
-        if (first == PH_ATT) continue;
+        if (first == PH_ATT) {
+            producer_attention(c, l, s_pos, TM, ncta);
+            if (c.dead) { producer_drain(c); return; }
+            continue;
+        }
 #if V_TC
         if (first == PH_LOGITS) {
             // 128 rows x 64 k of the embedding table per slot, by tensor copy; once per slab of 64 sequences
@@ -641,11 +737,6 @@ __device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __re
 // per-chunk partial results (m, sum, unnormalised o[V_E]) of the attention phase, into operand
 // tiles 0..nk-1.
 #define PART_STRIDE (V_E + 2)
-#define ATT_MAXCH (V_NCH > V_TS ? V_NCH : V_TS)
-// work items of the attention phase: V_NCH position chunks for each of the first V_TAIL_BH (sequence, head) pairs,
-// V_TS chunks for each of the rest (the pairs left over after whole rounds of the grid: split so that the last
-// round is a fraction of an item for every CTA instead of a whole item for some)
-#define ATT_ITEMS (V_TAIL_BH * V_NCH + (V_B * V_H - V_TAIL_BH) * V_TS)
 __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, int row0, int nrows) {
     const int cols = nk * 16;
 #pragma unroll 1
@@ -693,70 +784,6 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // 16 dims x 16 positions), B = the weights, head and remainder again in columns 0 and 1.
 // Result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
-#define KV_POS (NW * 16)                         // positions per tile: sixteen per warp
-#define KV_SMALL 32                              // boxes of 32, 64, 96 and 128 rows
-#define KV_TILE_BYTES (KV_POS * 128)             // K (or V) rows of one tile
-#define KV_STAGE_BYTES (2 * KV_TILE_BYTES)       // K rows then V rows
-#define TMAP_BYTES 128                           // descriptors at TM: K, V with boxes of 32 rows, of 64, of 96, of 128; then the embedding table
-
-struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
-
-// (sequence, head), chunk and chunk count of item `it`
-__device__ __forceinline__ void att_item(int it, int& b, int& h, int& ch, int& nch) {
-    int bh;
-    if (it < V_TAIL_BH * V_NCH) { bh = it / V_NCH; ch = it - bh * V_NCH; nch = V_NCH; }
-    else { const int j = it - V_TAIL_BH * V_NCH; bh = V_TAIL_BH + j / V_TS; ch = j % V_TS; nch = V_TS; }
-    b = bh / V_H; h = bh - b * V_H;
-}
-__device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int ncta) {
-    if (a.it < ATT_ITEMS) {
-        int ch, nch;
-        att_item(a.it, a.b, a.h, ch, nch);
-        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + nch - 1) / nch;
-        a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
-    }
-}
-__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.it < ATT_ITEMS; }
-__device__ __forceinline__ bool att_has_rows(const AttIter& a) { return a.hi > a.s; }      // an empty chunk is a tile without data
-__device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int ncta) {
-    a.s += KV_POS;
-    if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
-}
-__device__ __forceinline__ u32 kv_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + stage) * 8; }
-// byte offset of the 16-byte piece `piece` of row `row` in a swizzled tile
-__device__ __forceinline__ int kv_off(int row, int piece) { return row * 128 + ((piece ^ (row & 7)) << 4); }
-
-__device__ __forceinline__ void tma_rows(u32 dst, const unsigned char* tmap, int x, int row, int plane, u32 bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-                 :: "r"(dst), "l"(tmap), "r"(x), "r"(row), "r"(plane), "r"(bar) : "memory");
-}
-
-// request the tile [a.s, a.s + KV_POS) of item a into the next stage (one thread; every thread counts it)
-__device__ __forceinline__ void att_issue(Ctx& c, const AttIter& a, int l, const unsigned char* __restrict__ TM) {
-    if (c.tid == 0) {
-        const u32 stage = c.kvi % V_KVST;
-        // the smallest box that covers what is left of the item: 32, 64, 96 or 128 rows
-        const int q = min((a.hi - a.s + KV_SMALL - 1) / KV_SMALL, KV_POS / KV_SMALL) - 1;
-        const u32 bar = kv_bar(c, stage), dst = smem_u32(c.smem + SM_KV + stage * KV_STAGE_BYTES);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");    // the stage was last written and read with ordinary accesses
-        mbar_expect(bar, 2 * (q + 1) * KV_SMALL * 128);
-        tma_rows(dst, TM + (2 * q) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
-        tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
-    }
-    c.kvi++;
-}
-
-// the first tiles of this CTA, before the barrier (their row of the current position is stale: see attention_phase)
-__device__ __forceinline__ void attention_prefetch(Ctx& c, int l, const int* s_pos, const unsigned char* __restrict__ TM) {
-    AttIter a; a.it = c.cta;
-    att_load_item(a, s_pos, c.ncta);
-#pragma unroll 1
-    while (att_valid(a) && c.kvi - c.kvn < V_KVST) {
-        if (att_has_rows(a)) att_issue(c, a, l, TM);
-        att_advance(a, s_pos, c.ncta);
-    }
-}
-
 __device__ __forceinline__ void ldsm4(u32 (&r)[4], const unsigned char* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
 }
@@ -791,17 +818,15 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     AttIter cur, pf;
     cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
     if (!att_valid(cur)) return;
-    // rows written by other CTAs during the QKV phase are read by the copies below through the async proxy
-    if (c.tid == 0) asm volatile("fence.proxy.async.global;" ::: "memory");
-    // The tiles requested before the barrier: where one holds the current position of its sequence, that row is
-    // fetched now into a side buffer (one per stage) and moved into the tile when the tile is used.
+    // The first V_KVST tiles may have been requested before the barrier: where one holds the current position of its
+    // sequence, that row is fetched now into a side buffer (one per stage) and moved into the tile when it is used.
     unsigned char* side = c.smem + SM_MISC + MISC_SIDE;
     u32 patch = 0;
     pf = cur;
     {
         u32 n = c.kvn;
 #pragma unroll 1
-        while (n != c.kvi && att_valid(pf)) {
+        while (n != c.kvn + V_KVST && att_valid(pf)) {
             if (att_has_rows(pf)) {
                 const int tp = s_pos[pf.b];
                 if (tp >= pf.s && tp < min(pf.hi, pf.s + KV_POS)) {
@@ -915,15 +940,14 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 for (int mt = 0; mt < V_E / 16; mt++) { w[2 + mt * 16 + g] = o[mt][0] + o[mt][1]; w[2 + mt * 16 + g + 8] = o[mt][2] + o[mt][3]; }
             }
         }
-        cons_sync();                                   // everybody is done with this stage (and ms is written)
         if (cnt > 0) {
+            // this warp is done with the stage: the producer thread refills it when all eight are
+            __syncwarp();
+            if (c.lane == 0) mbar_arrive(kv_empty_bar(c, c.kvn % V_KVST));
             c.kvn++;
-            // the stage is free: the tile V_KVST ahead goes into it
-#pragma unroll 1
-            while (att_valid(pf) && !att_has_rows(pf)) att_advance(pf, s_pos, c.ncta);
-            if (att_valid(pf) && !c.dead) { att_issue(c, pf, l, TM); att_advance(pf, s_pos, c.ncta); }
         }
         if (last) {
+            cons_sync();                               // the warps' partial results of the item are in shared memory
             if (c.tid < V_E) {
                 float M = -3.0e38f;
 #pragma unroll
@@ -1178,7 +1202,8 @@ __device__ __forceinline__ void step_body(const Args& a) {
         *stop = 0;
         if (c.cta == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(0u) : "memory");   // nobody reads it before the first barrier
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
-        for (int s = 0; s < V_KVST; s++) mbar_init(kv_bar(c, s), 1);
+        for (int s = 0; s < V_KVST; s++) { mbar_init(kv_bar(c, s), 1); mbar_init(kv_empty_bar(c, s), NW); }
+        *reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ) = 0;
         mbar_init(tc_load_bar(c), 1); mbar_init(tc_done_bar(c), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -1200,7 +1225,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #endif
     const int* P = a.PT + c.cta * PT_STRIDE;
     if (c.warp == NW) {
-        if (c.lane == 0) producer(smem, a.bar, P, a.WP, a.TM, c.cta, nsteps);
+        if (c.lane == 0) producer(smem, a.bar, P, a.WP, a.TM, c.cta, c.ncta, nsteps);
         return;
     }
 
@@ -1448,7 +1473,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
             else
                 fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
         }
-        if (first == PH_QKV) attention_prefetch(c, l, s_pos, a.TM);
+        if (first == PH_QKV && c.tid == 0) {                                // the producer thread may request this layer's K/V tiles
+            volatile u32* seq = reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ);
+            __threadfence_block();
+            *seq = *seq + 1;
+        }
         TRACE(30 + first);
         phase_wait(c);
         TICK(3 + 2 * min(ph - l * PH_PER_LAYER, 3));

@@ -386,7 +386,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     kvst = int(tune.get('kv_stages', 3 if B * H > grid else 2))
 
     def smem_fixed(nb):
-        return (kvst * (2 * NW * 16 * 128 + 256 + 8) + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
+        return (kvst * (2 * NW * 16 * 128 + 256 + 16) + 32 + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
                 + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 + 16 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
