@@ -108,6 +108,10 @@ __device__ __forceinline__ uint4 lds_act(const unsigned char* p) {
 #endif
 }
 
+// a / w for small non-negative a (< 4096) and 1 <= w <= 64, with rcp = 1 / w: the integer division by a run-time
+// divisor costs some thirty dependent instructions, this one four ((a + 0.5) / w is never within rounding of an integer)
+__device__ __forceinline__ int qdiv(int a, float rcp) { return __float2int_rz(((float)a + 0.5f) * rcp); }
+
 // orderable key of (value, index): larger value wins, then the lower index
 __device__ __forceinline__ u64 best_key(float v, u32 n) {
     u32 u = __float_as_uint(v);
@@ -456,7 +460,8 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
         for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
             for (int i = 0; i < 4; i++) { acc[t][nb][i] = 0.f; lo[t][nb][i] = 0.f; }
-    const int rpc = V_CH / width, per = rpc * width, total = rows * width;
+    const float rcpw = __frcp_rn((float)width);
+    const int rpc = qdiv(V_CH, rcpw), per = rpc * width, total = rows * width;
     if (wide) {
         bool own[TPW];
 #pragma unroll
@@ -489,10 +494,12 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             c.chunk++;
         }
     } else {
-        const int cnt = (NW - (c.warp % width) + width - 1) / width;             // rows advance by cnt
+        const int wq = qdiv(c.warp, rcpw), wm = c.warp - wq * width;             // warp / width, warp % width
+        const int cnt = qdiv(NW - wm + width - 1, rcpw);                         // rows advance by cnt
         const int stride = cnt * width;
-        int f = (c.warp / width < rows) ? c.warp : 0x3fffffff;                   // next tile of this warp
-        int row = c.warp / width;
+        const float rcps = __frcp_rn((float)stride);
+        int f = (wq < rows) ? c.warp : 0x3fffffff;                               // next tile of this warp
+        int row = wq;
 #pragma unroll 1
         for (int base = 0; base < total; base += per) {
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
@@ -500,7 +507,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             TRACE(53);
             const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES + (size_t)c.lane * 16;
             const int lim = c.dead ? 0 : min(base + per, total);
-            int mine = f < lim ? (lim - f + stride - 1) / stride : 0;            // this warp's tiles in the chunk
+            int mine = f < lim ? qdiv(lim - f + stride - 1, rcps) : 0;           // this warp's tiles in the chunk
 #pragma unroll 1
             for (; mine > 0; mine -= NT, f += NT * stride, row += NT * cnt) {
                 // all loads of up to NT tiles first, then their products: the loads and the first product's latency overlap
@@ -653,7 +660,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
 #else
                 *reinterpret_cast<uint2*>(dst + (size_t)kt * V_NB * ATILE) = make_uint2(out.x, out.y);
 #endif
-                if (init && (kt % c.ncta) == c.cta) {
+                if (init && ((KT_D <= V_MAXGRID) ? (kt == c.cta) : ((kt % c.ncta) == c.cta))) {
                     const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
                     float* o = init + (size_t)rb * V_D + k;
                     red_add(o, v0[i].x + h_lo(i0)); red_add(o + 1, v0[i].y + h_hi(i0));
@@ -739,9 +746,10 @@ __device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __re
 #define PART_STRIDE (V_E + 2)
 __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, int row0, int nrows) {
     const int cols = nk * 16;
+    const float rcpk = __frcp_rn((float)nk);
 #pragma unroll 1
     for (int i = c.tid; i < nrows * cols; i += NCONS) {
-        const int b = i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
+        const int b = (nk <= 64) ? qdiv(i >> 4, rcpk) : i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
         // the chunks of (sequence, head): V_NCH of them, or V_TS for the items of the last, split round
         const int bh = (row0 + b) * V_H + h;
         const bool tail = bh >= V_TAIL_BH;
