@@ -98,6 +98,22 @@ __device__ __forceinline__ void bulk_g2s(u32 dst, const void* src, u32 bytes, u3
 __device__ __forceinline__ void cp16(void* dst, const void* src) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(dst)), "l"(src) : "memory"); }
 __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ uint4 lds128(const unsigned char* p) { return *reinterpret_cast<const uint4*>(p); }
+// the same from a 32-bit shared-memory address (explicit ld.shared: 32-bit address arithmetic, no generic-address path)
+__device__ __forceinline__ uint4 lds128s(u32 a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+    return v;
+}
+__device__ __forceinline__ uint4 lds_acts(u32 a) {
+#if V_ACT_LO
+    return lds128s(a);
+#else
+    uint4 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+    v.z = 0u; v.w = 0u;
+    return v;
+#endif
+}
 // one lane's part of an operand tile: (b0, b1) of the head and, if kept, (b0, b1) of the remainder
 __device__ __forceinline__ uint4 lds_act(const unsigned char* p) {
 #if V_ACT_LO
@@ -305,7 +321,8 @@ __device__ __forceinline__ void att_load_item(AttIter& a, const int* s_pos, int 
     if (a.it < ATT_ITEMS) {
         int ch, nch;
         att_item(a.it, a.b, a.h, ch, nch);
-        const int n = s_pos[a.b] + 1, cs = (max(n, 1) + nch - 1) / nch;
+        const int n = s_pos[a.b] + 1;
+        const int cs = (nch == V_NCH) ? (max(n, 1) + V_NCH - 1) / V_NCH : (max(n, 1) + V_TS - 1) / V_TS;     // divisions by constants
         a.s = ch * cs; a.hi = min(n, (ch + 1) * cs);
     }
 }
@@ -428,7 +445,7 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
 #pragma unroll 1
                 for (int j = 0; j < s.nj; j += (s.wide ? WG : WN_MAX * 4)) {
                     const int width = s.wide ? min(WG, s.nj - j) : s.nj;
-                    const int rpc = V_CH / width;
+                    const int rpc = qdiv(V_CH, __frcp_rn((float)width));
 #pragma unroll 1
                     for (int r = 0; r < s.rows; r += rpc) {
                         const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
@@ -461,6 +478,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
 #pragma unroll
             for (int i = 0; i < 4; i++) { acc[t][nb][i] = 0.f; lo[t][nb][i] = 0.f; }
     const float rcpw = __frcp_rn((float)width);
+    const u32 act32 = smem_u32(act);
     const int rpc = qdiv(V_CH, rcpw), per = rpc * width, total = rows * width;
     if (wide) {
         bool own[TPW];
@@ -472,16 +490,16 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
             wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
             TRACE(53);
-            const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) + (size_t)c.lane * 16;
+            const u32 tiles = smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES) + (u32)c.lane * 16u;
             const int nr = c.dead ? 0 : min(rpc, rows - row);
 #pragma unroll 2
             for (int r = 0; r < nr; r++) {
-                const unsigned char* tp = tiles + (size_t)(r * width + c.warp) * FRAG_BYTES;
+                const u32 tp = tiles + (u32)(r * width + c.warp) * FRAG_BYTES;
                 uint4 a[TPW], b[V_NB];
 #pragma unroll
-                for (int t = 0; t < TPW; t++) a[t] = own[t] ? lds128(tp + t * NW * FRAG_BYTES) : make_uint4(0, 0, 0, 0);
+                for (int t = 0; t < TPW; t++) a[t] = own[t] ? lds128s(tp + t * NW * FRAG_BYTES) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int nb = 0; nb < V_NB; nb++) b[nb] = lds_act(act + ((size_t)((row + r) * V_NB + nb) * 32 + c.lane) * ALB);
+                for (int nb = 0; nb < V_NB; nb++) b[nb] = lds_acts(act32 + (u32)(((row + r) * V_NB + nb) * 32 + c.lane) * ALB);
 #pragma unroll
                 for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
@@ -505,7 +523,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
             wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
             TRACE(53);
-            const unsigned char* tiles = c.smem + SM_RING + slot * (V_CH * FRAG_BYTES) - (size_t)base * FRAG_BYTES + (size_t)c.lane * 16;
+            const u32 tiles = smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES) - (u32)base * FRAG_BYTES + (u32)c.lane * 16u;
             const int lim = c.dead ? 0 : min(base + per, total);
             int mine = f < lim ? qdiv(lim - f + stride - 1, rcps) : 0;           // this warp's tiles in the chunk
 #pragma unroll 1
@@ -515,9 +533,9 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
 #pragma unroll
                 for (int i = 0; i < NT; i++) {
                     if (i < mine) {
-                        a[i] = lds128(tiles + (size_t)(f + i * stride) * FRAG_BYTES);
+                        a[i] = lds128s(tiles + (u32)(f + i * stride) * FRAG_BYTES);
 #pragma unroll
-                        for (int nb = 0; nb < V_NB; nb++) b[i][nb] = lds_act(act + ((size_t)((row + i * cnt) * V_NB + nb) * 32 + c.lane) * ALB);
+                        for (int nb = 0; nb < V_NB; nb++) b[i][nb] = lds_acts(act32 + (u32)(((row + i * cnt) * V_NB + nb) * 32 + c.lane) * ALB);
                     }
                 }
 #pragma unroll
@@ -642,7 +660,7 @@ __device__ __forceinline__ void ln_to_act(Ctx& c, const float* __restrict__ z, f
         }
 #pragma unroll
         for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        const float rs = rsqrtf(q * (1.0f / V_D) + V_EPS);
         TRACE(41);
 #pragma unroll
         for (int i = 0; i < LNI; i++) {
@@ -706,7 +724,7 @@ __device__ __forceinline__ void ln_rows_to_global(Ctx& c, const float* __restric
         }
 #pragma unroll
         for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        const float rs = rsqrtf(q * (1.0f / V_D) + V_EPS);
         unsigned char* tiles = actg + (size_t)(r / SB) * SLAB_TILE_BYTES;
         const int rb = r % SB;
 #pragma unroll
@@ -771,7 +789,7 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
             den += w * dd[ch];
             num += w * oo[ch];
         }
-        act_store1(act, b, kk, den > 0.f ? num / den : 0.f);      // a sequence that has not started attends to nothing
+        act_store1(act, b, kk, den > 0.f ? __fdividef(num, den) : 0.f);      // a sequence that has not started attends to nothing
     }
     cons_sync();
 }
@@ -1054,7 +1072,7 @@ __device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ 
         }
 #pragma unroll
         for (int m = 16; m; m >>= 1) q += __shfl_xor_sync(0xffffffffu, q, m);
-        const float rs = 1.0f / sqrtf(q * (1.0f / V_D) + V_EPS);
+        const float rs = rsqrtf(q * (1.0f / V_D) + V_EPS);
         const int rb = r % TC_N;
         unsigned char* dst = tcg + (size_t)(r / TC_N) * TC_B_BYTES + rb * 128;
 #pragma unroll
