@@ -844,6 +844,10 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     AttIter cur, pf;
     cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
     if (!att_valid(cur)) return;
+    u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
+#pragma unroll
+    for (int kq = 0; kq < V_E / 16; kq++) { bqn[kq][0] = 0; bqn[kq][1] = 0; }
+    att_load_q(bq, qbuf, cur.b, cur.h, g, t);        // requested first: its trip to L2 overlaps the walk below
     // The first V_KVST tiles may have been requested before the barrier: where one holds the current position of its
     // sequence, that row is fetched now into a side buffer (one per stage) and moved into the tile when it is used.
     unsigned char* side = c.smem + SM_MISC + MISC_SIDE;
@@ -870,10 +874,6 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
 
-    u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
-#pragma unroll
-    for (int kq = 0; kq < V_E / 16; kq++) { bqn[kq][0] = 0; bqn[kq][1] = 0; }
-    att_load_q(bq, qbuf, cur.b, cur.h, g, t);
     float m = -3.0e38f, den = 0.f, o[V_E / 16][4];   // o[mt]: dims mt*16 + g (regs 0+1) and mt*16 + g + 8 (regs 2+3), lanes t == 0
     int item = 0;                                    // items finished by this CTA in this phase
 #pragma unroll
@@ -1000,8 +1000,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         }
         att_advance(cur, s_pos, c.ncta);
     }
-    cp_wait();
-    cons_sync();                                       // ms may be reused by the next phase
+    cp_wait();                                         // (the phase ends with a block-wide sync before anything else uses this memory)
 }
 
 // ---------------------------------------------------------------------------------------------
