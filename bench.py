@@ -99,21 +99,27 @@ class ClockSampler:
         return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=int(rows[0][1]), reasons=reasons, samples=len(rows))
 
 
-def cpu_baseline(sh, W, batch, ctx, steps, warm=1):
-    """the NumPy oracle on the host: `steps` decode steps of one sequence at context ~ctx (the cache
-    is filled with random fp16 values: the time does not depend on them)"""
+def cpu_baseline(sh, W, batch, ctx, steps, warm=1, max_seconds=None):
+    """the NumPy oracle on the host: up to `steps` decode steps of one sequence starting at context ~ctx (the cache
+    is filled with random fp16 values: the time does not depend on them), cut short after max_seconds.
+    -> (steps per second, seconds, steps done)"""
     from oracle import gpt2_numpy as O
     rng = np.random.default_rng(0)
-    keys = (rng.standard_normal((sh.L, ctx + steps + warm, sh.H, sh.E), dtype=np.float32) * 0.1).astype(np.float16)
+    room = min(ctx + steps + warm, sh.C)
+    keys = (rng.standard_normal((sh.L, room, sh.H, sh.E), dtype=np.float32) * 0.1).astype(np.float16)
     vals = keys.copy()
     x = 1
     for t in range(warm):
-        _, x = O.step(sh, W, keys, vals, x, ctx + t)
+        _, x = O.step(sh, W, keys, vals, x, min(ctx + t, room - 1))
     t0 = time.perf_counter()
+    done = 0
     for t in range(steps):
-        _, x = O.step(sh, W, keys, vals, x, ctx + warm + t)
+        _, x = O.step(sh, W, keys, vals, x, min(ctx + warm + t, room - 1))
+        done += 1
+        if max_seconds and time.perf_counter() - t0 > max_seconds:
+            break
     dt = time.perf_counter() - t0
-    return steps / dt, dt
+    return done / dt, dt, done
 
 
 def run_reference(args, wl, sh):
@@ -125,8 +131,8 @@ def run_reference(args, wl, sh):
     from vesta_gpu_b200.synth import make_weights
     W = O.upcast(make_weights(sh, 0))
     ctx = wl['prompt'] + wl['gen'] // 2
-    steps = max(1, min(args.steps, 12))
-    tps, dt = cpu_baseline(sh, W, wl['batch'], ctx, steps, warm=max(1, min(args.warmup, 2)))
+    # every step is one decode step of one sequence (a bounded sample of the batch); at most two minutes in all
+    tps, dt, steps = cpu_baseline(sh, W, wl['batch'], ctx, max(1, args.steps), warm=max(1, min(args.warmup, 3)), max_seconds=120)
     cores = os.cpu_count()
     sample = f'{steps} decode steps of one sequence at context {ctx} (of batch {wl["batch"]} x {wl["gen"]} steps), sequences run one after another'
     line = dict(metric=METRIC, value=tps, unit=UNIT, impl='reference', n_gpus=args.gpus, steps=steps, warmup=args.warmup,
@@ -308,8 +314,8 @@ def main():
     if not args.no_cpu_baseline and world == 1:
         from oracle import gpt2_numpy as O
         ctx = P + K // 2
-        nsteps = 12 if sh.D <= 768 else 3
-        tps, dt = cpu_baseline(sh, O.upcast(hf.weights), B, ctx, nsteps)
+        # a bounded sample: about 12 seconds of decode steps of one sequence
+        tps, dt, nsteps = cpu_baseline(sh, O.upcast(hf.weights), B, ctx, 2000, max_seconds=12)
         line['cpu_baseline'] = dict(value=tps, unit=UNIT, cores=os.cpu_count(), kind='port',
                                     sample=f'{nsteps} decode steps of one sequence at context {ctx}, NumPy oracle, {dt:.1f} s')
     print(json.dumps(line))
