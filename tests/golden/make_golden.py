@@ -1,6 +1,7 @@
 """Generate the golden fixtures in this directory from the reference interpreter itself.
 
-Runs where the reference checkout is available (REF, default /root/reference): imports
+Runs where a checkout of the reference is available (its directory in the environment variable
+VESTA_REFERENCE): imports
 vesta.interp.run unmodified and drives it exactly as a user would, one sequence at a time,
 with fp16-rounded weights up-cast to float32 and np.float16 K/V arrays. The fixtures pin the
 CPU oracle (oracle/gpt2_numpy.py) and, through it and directly, the GPU kernel.

@@ -73,8 +73,11 @@ def test_shipped_programs_match_generator():
         assert sum(isinstance(s, sx.StepFold) for s in prog) == 1
 
 
-@pytest.mark.skipif(not os.path.exists('/root/reference/vesta/programs/gpt2.vst'), reason='reference checkout not present')
+REF_PROGRAM = os.path.join(os.environ.get('VESTA_REFERENCE', '/root/reference'), 'vesta', 'programs', 'gpt2.vst')
+
+
+@pytest.mark.skipif(not os.path.exists(REF_PROGRAM), reason='reference checkout not present')
 def test_same_tree_as_reference_program():
     """the program the reference ships and the generated text are the same statements"""
-    ref = open('/root/reference/vesta/programs/gpt2.vst', encoding='utf-8').read()
+    ref = open(REF_PROGRAM, encoding='utf-8').read()
     assert sx.parse(ref) == sx.parse(decode_program(GPT2_SMALL))
