@@ -242,10 +242,15 @@ def place_step(dims, grid, ksplit=False):
     # FC / MLP-proj: every f tile costs 2*KT_D tiles of stream; at most WN_MAX per CTA
     fc = _spread(KT_F, [0.0] * G, WN_MAX)
     load = [(1.0 if ksplit else 2.0) * KT_D * n for n in fc]
-    # QKV: every output tile costs KT_D tiles of stream
+    # QKV: every output tile costs KT_D tiles of stream. The phases are separated by grid barriers, so what a phase
+    # costs is its largest share: no CTA gets more than ceil(tiles / CTAs) of them; within that, the CTAs with the
+    # fewest bytes so far come first.
+    cap = min(WN_MAX, max(1, math.ceil(JT_J / G)))
+    if JT_J > cap * G:
+        raise NotImplementedError('placement: too many QKV output tiles for this grid')
     cnt = [0] * G
     for _ in range(JT_J):
-        c = min((i for i in range(G) if cnt[i] < WN_MAX), key=lambda i: (load[i], i))
+        c = min((i for i in range(G) if cnt[i] < cap), key=lambda i: (load[i], i))
         cnt[c] += 1
         load[c] += KT_D
     qkv = cnt
@@ -275,13 +280,12 @@ def place_step(dims, grid, ksplit=False):
     if ksplit:
         units2, p2_nk = units_of(KT_F, 2)
         p2 = deal(units2)
-    # logits: output tiles over the whole fold; balance the whole step (layers x per-layer load + logits)
+    # logits: output tiles over the whole fold, the same number per CTA (the phase costs its largest share); the
+    # CTAs with the fewest bytes in the layers take the remainder
     step_load = [L * v for v in load]
-    cnt = [0] * G
-    for _ in range(JT_N):
-        c = min(range(G), key=lambda i: (step_load[i], i))
+    cnt = [JT_N // G] * G
+    for c in sorted(range(G), key=lambda i: (step_load[i], i))[:JT_N % G]:
         cnt[c] += 1
-        step_load[c] += KT_D
     logit = cnt
 
     rec = np.zeros((G, PT_STRIDE), np.int32)
@@ -505,18 +509,26 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     src = head + KERNEL_TEXT.read_text(encoding='utf-8') + tail
 
     q = env
+    ln_how = ('each row normalised once on one warp of the grid, operand tiles through global memory (+1 barrier)' if ln_dist
+              else 'every CTA recomputes, one warp per row held in registers, into mma operand tiles')
+    att_items_txt = (f'{tail_bh} whole (sequence, head) items, the other {B * H - tail_bh} in {ts} position chunks' if ts > 1
+                     else f'one item per (sequence, head, 1/{nch} of the positions)')
     plan = [
         (f'{q["$z0"]} (embed)', 'grid-stride, then barrier'),
-        (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', 'every CTA recomputes, one warp per row, into mma operand tiles'),
+        (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', ln_how),
         (f'{q["$qkv"]} + emits', f'NARROW: whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA; bias, q, K/V emit in the epilogue'),
-        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)', f'one CTA per (sequence, head, 1/{nch} of the positions), online softmax in registers, merged by the projection'),
+        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)',
+         f'{att_items_txt}, dealt round-robin over the CTAs; K/V tiles by TMA ({kvst} stages), online softmax in registers, merged by the projection'),
         (f'{q["$oo"]}, {q["$z1"]}', f'WIDE: {notes["proj_units"]} units of up to {WG} output tiles x {notes["proj_nk"]} fold tiles, fp32 atomics'),
-        (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', 'every CTA recomputes'),
-        (f'{q["$u"]}, {q["$g"]}', f'NARROW: {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
-        (f'{q["$z2"]}', 'WIDE over the CTA\'s own f tiles, fp32 atomics'),
-        (f'{q["$m3"]}, {q["$v3"]}, {q["$c"]} (LNf)', 'every CTA recomputes'),
-        (f'{q["$logit"]}', f'WIDE over the whole fold, {min(rec[:, 11])}-{max(rec[:, 11])} vocabulary tiles per CTA'),
-        (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes'),
+        (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', ln_how),
+        (f'{q["$u"]}, {q["$g"]}', f'NARROW: {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result '
+                                  + ('through global memory as operand tiles (+1 barrier)' if ksplit else 'stays in shared memory')),
+        (f'{q["$z2"]}', (f'NARROW: two output tiles x {notes["p2_nk"]} fold tiles per CTA, fp32 atomics' if ksplit
+                         else 'WIDE over the CTA\'s own f tiles, fp32 atomics')),
+        (f'{q["$m3"]}, {q["$v3"]}, {q["$c"]} (LNf)', ln_how),
+        (f'{q["$logit"]}', ('tcgen05.mma tiles of 128 vocabulary rows x 64 sequences, accumulators in tensor memory, ' if tc else 'WIDE over the whole fold, ')
+                           + f'{min(rec[:, 11])}-{max(rec[:, 11])} vocabulary tiles per CTA'),
+        (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes and releases the next step of the launch'),
     ]
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] \
         + ['logits', 'finish']
