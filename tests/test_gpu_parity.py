@@ -347,6 +347,41 @@ def test_host_driven_step_equals_the_device_loop():
     assert (m.logits().cpu() - want_logits).abs().max() < 2e-3
 
 
+def test_prefill_in_one_call_and_state_round_trip():
+    """prefill() (prompts to the device once, the kernel feeds itself) against feeding the prompt token by token from
+    the host; state() / load_state() carry a generation over to a second model"""
+    from vesta_gpu_b200.shapes import TINY3
+    from vesta_gpu_b200.synth import make_ragged_prompts
+    B, gen = 4, 6
+    lens, toks = make_ragged_prompts(TINY3, B, 2, 7, seed=9)
+    pmax = int(lens.max())
+    m, hf = model(TINY3, 13, 'rich', B, pmax + gen + 1, per_sequence_t=True, prompt_len=pmax)
+    m.prefill(toks[:, :pmax], lens)
+    m.k.check()
+    first = m.x.cpu().numpy().copy()
+    assert m.t.cpu().numpy().tolist() == lens.tolist()
+    # the same prompts, one sequence at a time, token by token
+    m1, _ = model(TINY3, 13, 'rich', 1, pmax + gen + 1)
+    for i in range(B):
+        m1.reset()
+        for p in range(int(lens[i])):
+            m1.x.fill_(int(toks[i, p])); m1.step()
+        assert int(m1.x.cpu()[0]) == int(first[i]), i
+    # carry on, save in the middle, finish on a second model
+    m.step(2)
+    st = m.state()
+    m.step(gen - 2)
+    want = m.x.cpu().numpy().copy()
+    m2, _ = model(TINY3, 13, 'rich', B, pmax + gen + 1, per_sequence_t=True, prompt_len=pmax)
+    m2.prompt.copy_(m.prompt); m2.plen.copy_(m.plen)
+    m2.load_state(st)
+    m2.step(gen - 2)
+    m2.k.check()
+    assert np.array_equal(m2.x.cpu().numpy(), want)
+    with pytest.raises(ValueError):
+        m2.load_state(dict(st, x=st['x'][:2]))
+
+
 def test_out_of_range_inputs_are_refused_not_executed():
     from vesta_gpu_b200.shapes import TINY
     m, _ = model(TINY, 3, 'rich', 2, 8)

@@ -98,6 +98,44 @@ class VestaGPT2:
         they have"""
         self.k.step_host(self.x, tokens_host, self.next(), next_host)
 
+    def prefill(self, tokens, lengths=None):
+        """consume whole prompts in one call (needs prompt_len >= the longest prompt and per_sequence_t when the
+        lengths differ): the prompts go to the device once, then the kernel feeds itself one position per step,
+        several steps per launch, until every prompt has been read; sequences shorter than the longest start late
+        (negative positions) so that all of them end together. On return x holds the first generated token of every
+        sequence and t its position. tokens: int array (batch, P), lengths: (batch,) or None for P everywhere."""
+        import numpy as np
+        tokens = np.asarray(tokens)
+        B, P = tokens.shape
+        if not hasattr(self, 'prompt') or B != self.B or P > self.prompt.shape[1]:
+            raise ValueError('prefill needs a model built with prompt_len >= the prompt length and the same batch')
+        lens = np.full(B, P, np.int32) if lengths is None else np.asarray(lengths, np.int32)
+        if lens.min() < 1 or lens.max() > P:
+            raise ValueError('prompt lengths must lie in 1..P')
+        pmax = int(lens.max())
+        if self.t.numel() == 1 and lens.min() != pmax:
+            raise ValueError('prompts of different lengths need per_sequence_t=True')
+        buf = np.zeros(tuple(self.prompt.shape), np.int32)
+        buf[:, :P] = tokens
+        self.reset()
+        self.prompt.copy_(torch.from_numpy(buf)); self.plen.copy_(torch.from_numpy(lens))
+        start = (lens - pmax).astype(np.int32)
+        self.t.copy_(torch.from_numpy(start[:self.t.numel()]))
+        self.x.copy_(torch.from_numpy(np.where(start == 0, tokens[:, 0], 0).astype(np.int32)))
+        self.k.launch(pmax)
+
+    def state(self):
+        """the decode state (cache, tokens, positions) as CPU tensors, for load_state() on a model of the same
+        shape, batch and tmax: generation then continues where it stood"""
+        return {'keys': self.keys.cpu(), 'vals': self.vals.cpu(), 'x': self.x.cpu(), 't': self.t.cpu()}
+
+    def load_state(self, st):
+        for name in ('keys', 'vals', 'x', 't'):
+            dst, src = getattr(self, name), st[name]
+            if tuple(dst.shape) != tuple(src.shape) or dst.dtype != src.dtype:
+                raise ValueError(f'state[{name!r}] is {tuple(src.shape)} {src.dtype}, the model holds {tuple(dst.shape)} {dst.dtype}')
+            dst.copy_(src)
+
     def logits(self):
         return self.k.view('logit')
 
