@@ -215,3 +215,16 @@ def test_attention_items_cover_every_sequence_head_and_position():
             assert seen.min() == 1 and seen.max() == 1
         if sh is GPT2_SMALL and B == 64 and tmax == 1025:
             assert ts == 4 and tail_bh == 740 and items <= 6 * 148        # five whole rounds and one of quarter items
+
+
+def test_small_division_by_reciprocal_is_exact():
+    """qdiv in csrc/step_kernel.cuh: a / w as trunc((a + 0.5) * (1 / w)) in fp32 with a reciprocal that is off by up to
+    two ulps, for every a < 4096 and w <= 64 (the kernel's operands: tiles per chunk, warps, fold tiles per CTA)"""
+    a = np.arange(0, 4096, dtype=np.int32)
+    for w in range(1, 65):
+        r = np.float32(1.0) / np.float32(w)
+        lo = np.nextafter(np.nextafter(r, np.float32(0)), np.float32(0))
+        hi = np.nextafter(np.nextafter(r, np.float32(2)), np.float32(2))
+        for rr in (lo, r, hi):
+            q = ((a.astype(np.float32) + np.float32(0.5)) * rr).astype(np.int32)
+            assert np.array_equal(q, a // w), w

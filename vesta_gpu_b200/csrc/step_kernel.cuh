@@ -127,6 +127,8 @@ __device__ __forceinline__ uint4 lds_act(const unsigned char* p) {
 // a / w for small non-negative a (< 4096) and 1 <= w <= 64, with rcp = 1 / w: the integer division by a run-time
 // divisor costs some thirty dependent instructions, this one four ((a + 0.5) / w is never within rounding of an integer)
 __device__ __forceinline__ int qdiv(int a, float rcp) { return __float2int_rz(((float)a + 0.5f) * rcp); }
+// 1 / w to within an ulp (one instruction): enough for qdiv, whose quotients stay 1/128 away from an integer
+__device__ __forceinline__ float rcp_fast(int w) { float r; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"((float)w)); return r; }
 
 // orderable key of (value, index): larger value wins, then the lower index
 __device__ __forceinline__ u64 best_key(float v, u32 n) {
@@ -356,6 +358,7 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
         const u64 t0 = now_ns();
         u32 spins = 0;
         while ((int)(*seq - c.tcl) < 0) {
+            __nanosleep(200);                      // this thread shares a scheduler with two consumer warps
             if (*stop) { c.dead = true; return; }
             if ((++spins & 63u) == 0) {
                 if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; return; }
@@ -445,7 +448,7 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
 #pragma unroll 1
                 for (int j = 0; j < s.nj; j += (s.wide ? WG : WN_MAX * 4)) {
                     const int width = s.wide ? min(WG, s.nj - j) : s.nj;
-                    const int rpc = qdiv(V_CH, __frcp_rn((float)width));
+                    const int rpc = qdiv(V_CH, rcp_fast(width));
 #pragma unroll 1
                     for (int r = 0; r < s.rows; r += rpc) {
                         const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
@@ -477,7 +480,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
         for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
             for (int i = 0; i < 4; i++) { acc[t][nb][i] = 0.f; lo[t][nb][i] = 0.f; }
-    const float rcpw = __frcp_rn((float)width);
+    const float rcpw = rcp_fast(width);
     const u32 act32 = smem_u32(act);
     const int rpc = qdiv(V_CH, rcpw), per = rpc * width, total = rows * width;
     if (wide) {
@@ -515,7 +518,7 @@ __device__ __forceinline__ void gemm_group(Ctx& c, int rows, int width, bool wid
         const int wq = qdiv(c.warp, rcpw), wm = c.warp - wq * width;             // warp / width, warp % width
         const int cnt = qdiv(NW - wm + width - 1, rcpw);                         // rows advance by cnt
         const int stride = cnt * width;
-        const float rcps = __frcp_rn((float)stride);
+        const float rcps = rcp_fast(stride);
         int f = (wq < rows) ? c.warp : 0x3fffffff;                               // next tile of this warp
         int row = wq;
 #pragma unroll 1
@@ -764,7 +767,7 @@ __device__ __forceinline__ void load_act_tiles(Ctx& c, const unsigned char* __re
 #define PART_STRIDE (V_E + 2)
 __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, int row0, int nrows) {
     const int cols = nk * 16;
-    const float rcpk = __frcp_rn((float)nk);
+    const float rcpk = rcp_fast(nk);
 #pragma unroll 1
     for (int i = c.tid; i < nrows * cols; i += NCONS) {
         const int b = (nk <= 64) ? qdiv(i >> 4, rcpk) : i / cols, kk = i - b * cols, d = k0 * 16 + kk, h = d / V_E, e = d % V_E;
