@@ -9,6 +9,7 @@ CPU oracle (oracle/gpt2_numpy.py) and, through it and directly, the GPU kernel.
     python tests/golden/make_golden.py tiny tiny3 small_rich      # seconds to a minute
     python tests/golden/make_golden.py cfg2                       # 8 processes x 384 steps (sequence 0 is the batch-1 config)
     python tests/golden/make_golden.py xl                         # 8 steps of the XL-shaped program
+    python tests/golden/make_golden.py cfg3_sample                # 4 of 64 sequences, 2 steps at context 600 on a seeded cache
 
 Each fixture: per sequence the greedy token chosen at every step, the top-1 margin, and for a
 set of kept steps a strided sample of the logits plus the top-5 (index, value) pairs; small
@@ -27,7 +28,7 @@ REF = os.environ.get('VESTA_REFERENCE', '/root/reference')
 sys.path.insert(0, ROOT)
 
 from vesta_gpu_b200.shapes import SHAPES                      # noqa: E402
-from vesta_gpu_b200.synth import make_weights, make_prompts   # noqa: E402
+from vesta_gpu_b200.synth import make_weights, make_prompts, make_cache   # noqa: E402
 from vesta_gpu_b200.program_text import decode_program        # noqa: E402
 
 STRIDE = 127
@@ -100,7 +101,52 @@ def spread(steps, P):
     return {v for v in s if 0 <= v < steps}
 
 
+def ref_steps_on_cache(job):
+    """teacher-forced steps of one sequence on a seeded, filled cache (synth.make_cache): what the batch-64 config
+    looks like deep into its context, without the hours the interpreter would need to get there"""
+    shape, seed, init, cache_seed, ctx, x0, steps = job
+    run = ref_run()
+    sh = SHAPES[shape]
+    text = decode_program(sh)
+    W = {k: v.astype(np.float32) for k, v in make_weights(sh, seed, init).items()}
+    k0, v0 = make_cache(sh, cache_seed, ctx)
+    keys = np.zeros((sh.L, ctx + steps, sh.H, sh.E), np.float16); vals = np.zeros_like(keys)
+    keys[:, :ctx] = k0; vals[:, :ctx] = v0
+    x, out = int(x0), []
+    for i in range(steps):
+        env = run(text, dict(W, x=x, t=ctx + i, keys=keys, vals=vals))
+        logit = np.asarray(env['logit'][0], np.float32)
+        nxt = int(env['next'][0])
+        p = np.partition(logit, -2)
+        top = np.argsort(-logit, kind='stable')[:5]
+        out.append((x, nxt, float(p[-1] - p[-2]), logit[::STRIDE].copy(), top.astype(np.int32), logit[top]))
+        x = nxt
+    return out
+
+
+def build_cache_sample(name, shape, seed, init, batch, ctx, steps, sample):
+    sh = SHAPES[shape]
+    x0 = [(b * 97 + 11) % sh.N for b in range(batch)]
+    t0 = time.time()
+    with Pool(len(sample)) as pool:
+        res = pool.map(ref_steps_on_cache, [(shape, seed, init, 1000 + b, ctx, x0[b], steps) for b in sample])
+    print(name, 'took %.1f s' % (time.time() - t0))
+    out = dict(shape=shape, seed=seed, init=init, batch=batch, ctx=ctx, steps=steps, sample=np.array(sample, np.int32),
+               x0=np.array(x0, np.int32), cache_seed_base=np.int32(1000), stride=np.int32(STRIDE))
+    for i, r in enumerate(res):
+        out[f'fed_{i}'] = np.array([s[0] for s in r], np.int32)
+        out[f'tokens_{i}'] = np.array([s[1] for s in r], np.int32)
+        out[f'margins_{i}'] = np.array([s[2] for s in r], np.float32)
+        out[f'logits_{i}'] = np.stack([s[3] for s in r])
+        out[f'top_idx_{i}'] = np.stack([s[4] for s in r])
+        out[f'top_val_{i}'] = np.stack([s[5] for s in r])
+    path = os.path.join(HERE, name + '.npz')
+    np.savez_compressed(path, **out)
+    print(name, 'written', os.path.getsize(path), 'bytes')
+
+
 TARGETS = {
+    'cfg3_sample': lambda: build_cache_sample('gpt2_cfg3_sample', 'gpt2', 5, 'rich', 64, 600, 2, [0, 21, 42, 63]),
     'tiny': lambda: build('tiny_b3', 'tiny', 3, 'rich', 3, 5, 12, set(range(17)), True, 1),
     'tiny3': lambda: build('tiny3_b2', 'tiny3', 4, 'rich', 2, 7, 20, set(range(27)), True, 1),
     'small_rich': lambda: build('gpt2_rich_b1', 'gpt2', 5, 'rich', 1, 6, 6, set(range(12)), False, 1),

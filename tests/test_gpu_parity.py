@@ -74,6 +74,41 @@ def test_gpt2_xl_shape():
     run_fixture('gpt2_xl_b1')
 
 
+def test_batch64_deep_context_sample_against_the_reference():
+    """the batch-64 configuration deep into its context (600 positions in every cache, seeded): slabs, distributed
+    LayerNorm, fold-slice MLP projection, several attention items of five tiles per CTA, tcgen05 logits; four of the
+    64 sequences against the reference interpreter's logits and tokens over two teacher-forced steps"""
+    from vesta_gpu_b200.shapes import SHAPES
+    from vesta_gpu_b200.synth import make_cache
+    g = load('gpt2_cfg3_sample')
+    sh, ctx, steps, stride, B = SHAPES[str(g['shape'])], int(g['ctx']), int(g['steps']), int(g['stride']), int(g['batch'])
+    m, _ = model(sh, int(g['seed']), str(g['init']), B, ctx + steps)
+    assert m.low.dims['tc'] and m.low.dims['ksplit']
+    m.reset()
+    for b in range(B):
+        k0, v0 = make_cache(sh, int(g['cache_seed_base']) + b, ctx)
+        m.keys[b, :, :ctx].copy_(torch.from_numpy(k0)); m.vals[b, :, :ctx].copy_(torch.from_numpy(v0))
+    m.t.fill_(ctx); m.x.copy_(torch.from_numpy(g['x0']))
+    worst = 0.0
+    for s_ in range(steps):
+        if s_:
+            x = m.x.cpu().numpy().copy()
+            for i, b in enumerate(g['sample']):
+                x[b] = g[f'fed_{i}'][s_]                          # teacher forcing for the compared sequences
+            m.x.copy_(torch.from_numpy(x))
+        m.step()
+        lg, nx = m.logits().cpu().numpy(), m.next().cpu().numpy()
+        for i, b in enumerate(g['sample']):
+            ref = g[f'logits_{i}'][s_]
+            assert close(lg[b][::stride], ref), (s_, b)
+            worst = max(worst, float(np.abs(lg[b][::stride] - ref).max()))
+            assert np.abs(lg[b][g[f'top_idx_{i}'][s_]] - g[f'top_val_{i}'][s_]).max() < 5e-3
+            if g[f'margins_{i}'][s_] > MARGIN:
+                assert int(nx[b]) == int(g[f'tokens_{i}'][s_]), (s_, b)
+    m.k.check()
+    assert worst < 5e-3, worst          # fp16-head operands at this batch: a few 1e-3, far inside the 2e-2 rule
+
+
 def test_free_running_feedback_matches_reference_tokens():
     """feedback on, no host write between generated steps: the stream equals the reference's up to the
     first step whose margin is below the bar"""

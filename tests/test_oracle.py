@@ -81,3 +81,23 @@ def test_kv_cache_rounds_to_fp16():
     b, _ = O.step(TINY, W, k32, v32, 5, 0)
     assert k16.dtype == np.float16 and np.array_equal(k16[0, 0], k32[0, 0].astype(np.float16))   # layer 0 sees the same input
     assert np.abs(a - b).max() < 1e-2 and not np.array_equal(a, b)
+
+
+def test_gpt2_small_deep_context_sample_of_the_batch64_config():
+    """four of 64 sequences, two teacher-forced steps at context 600 on a seeded cache (the reference interpreter
+    needs a second per position, so the fixture starts from a filled cache instead of a 600-token prompt)"""
+    from vesta_gpu_b200.shapes import SHAPES
+    from vesta_gpu_b200.synth import make_cache
+    g = load('gpt2_cfg3_sample')
+    sh, ctx, steps, stride = SHAPES[str(g['shape'])], int(g['ctx']), int(g['steps']), int(g['stride'])
+    W = weights(sh, int(g['seed']), str(g['init']))
+    for i, b in enumerate(g['sample']):
+        k0, v0 = make_cache(sh, int(g['cache_seed_base']) + int(b), ctx)
+        keys = np.zeros((sh.L, ctx + steps, sh.H, sh.E), np.float16); vals = np.zeros_like(keys)
+        keys[:, :ctx] = k0; vals[:, :ctx] = v0
+        for s_ in range(steps):
+            logit, nxt = O.step(sh, W, keys, vals, int(g[f'fed_{i}'][s_]), ctx + s_)
+            assert np.abs(logit[::stride] - g[f'logits_{i}'][s_]).max() < TIGHT
+            assert np.abs(logit[g[f'top_idx_{i}'][s_]] - g[f'top_val_{i}'][s_]).max() < TIGHT
+            if g[f'margins_{i}'][s_] > MARGIN:
+                assert nxt == int(g[f'tokens_{i}'][s_])

@@ -53,6 +53,16 @@ def make_ragged_prompts(sh: Shape, batch, lo, hi, seed=1):
     return lens, toks
 
 
+def make_cache(sh: Shape, seed, positions, scale=0.3):
+    """a filled KV cache of one sequence: (keys, vals) fp16 [L, positions, H, E], N(0, scale), from a seed.
+    Stands for the cache a long prompt would have left, where running the prompt is too slow (the reference
+    interpreter needs about a second per position)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    k = (rng.standard_normal((sh.L, positions, sh.H, sh.E), dtype=np.float32) * scale).astype(np.float16)
+    v = (rng.standard_normal((sh.L, positions, sh.H, sh.E), dtype=np.float32) * scale).astype(np.float16)
+    return k, v
+
+
 class SynthGPT2:
     """Stands where the Hugging Face model stands in VestaGPT2(hf, ...): offers state_dict()
     under the Hugging Face names (vesta/gpt2.py:18-25), built from make_weights."""
