@@ -10,6 +10,7 @@ CPU oracle (oracle/gpt2_numpy.py) and, through it and directly, the GPU kernel.
     python tests/golden/make_golden.py cfg2                       # 8 processes x 384 steps (sequence 0 is the batch-1 config)
     python tests/golden/make_golden.py xl                         # 8 steps of the XL-shaped program
     python tests/golden/make_golden.py cfg3_sample                # 4 of 64 sequences, 2 steps at context 600 on a seeded cache
+    python tests/golden/make_golden.py cfg5_sample                # 4 of 32 sequences with contexts 64..512 (ragged batch)
 
 Each fixture: per sequence the greedy token chosen at every step, the top-1 margin, and for a
 set of kept steps a strided sample of the logits plus the top-5 (index, value) pairs; small
@@ -125,13 +126,15 @@ def ref_steps_on_cache(job):
 
 
 def build_cache_sample(name, shape, seed, init, batch, ctx, steps, sample):
+    """ctx: one context for every sequence, or a function of the sequence index (ragged batch)"""
     sh = SHAPES[shape]
+    ctxs = [int(ctx(b)) if callable(ctx) else int(ctx) for b in range(batch)]
     x0 = [(b * 97 + 11) % sh.N for b in range(batch)]
     t0 = time.time()
     with Pool(len(sample)) as pool:
-        res = pool.map(ref_steps_on_cache, [(shape, seed, init, 1000 + b, ctx, x0[b], steps) for b in sample])
+        res = pool.map(ref_steps_on_cache, [(shape, seed, init, 1000 + b, ctxs[b], x0[b], steps) for b in sample])
     print(name, 'took %.1f s' % (time.time() - t0))
-    out = dict(shape=shape, seed=seed, init=init, batch=batch, ctx=ctx, steps=steps, sample=np.array(sample, np.int32),
+    out = dict(shape=shape, seed=seed, init=init, batch=batch, ctx=max(ctxs), ctxs=np.array(ctxs, np.int32), steps=steps, sample=np.array(sample, np.int32),
                x0=np.array(x0, np.int32), cache_seed_base=np.int32(1000), stride=np.int32(STRIDE))
     for i, r in enumerate(res):
         out[f'fed_{i}'] = np.array([s[0] for s in r], np.int32)
@@ -147,6 +150,7 @@ def build_cache_sample(name, shape, seed, init, batch, ctx, steps, sample):
 
 TARGETS = {
     'cfg3_sample': lambda: build_cache_sample('gpt2_cfg3_sample', 'gpt2', 5, 'rich', 64, 600, 2, [0, 21, 42, 63]),
+    'cfg5_sample': lambda: build_cache_sample('gpt2_cfg5_sample', 'gpt2', 5, 'rich', 32, lambda b: 64 + (b * 53) % 449, 2, [0, 9, 20, 31]),
     'tiny': lambda: build('tiny_b3', 'tiny', 3, 'rich', 3, 5, 12, set(range(17)), True, 1),
     'tiny3': lambda: build('tiny3_b2', 'tiny3', 4, 'rich', 2, 7, 20, set(range(27)), True, 1),
     'small_rich': lambda: build('gpt2_rich_b1', 'gpt2', 5, 'rich', 1, 6, 6, set(range(12)), False, 1),

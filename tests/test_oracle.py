@@ -83,15 +83,18 @@ def test_kv_cache_rounds_to_fp16():
     assert np.abs(a - b).max() < 1e-2 and not np.array_equal(a, b)
 
 
-def test_gpt2_small_deep_context_sample_of_the_batch64_config():
-    """four of 64 sequences, two teacher-forced steps at context 600 on a seeded cache (the reference interpreter
-    needs a second per position, so the fixture starts from a filled cache instead of a 600-token prompt)"""
+@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample'])
+def test_gpt2_small_deep_context_samples(name):
+    """sampled sequences of the batch-64 config (context 600) and of a ragged batch of 32 (contexts 64..512): two
+    teacher-forced steps on seeded caches (the reference interpreter needs a second per position, so the fixtures
+    start from a filled cache instead of a long prompt)"""
     from vesta_gpu_b200.shapes import SHAPES
     from vesta_gpu_b200.synth import make_cache
-    g = load('gpt2_cfg3_sample')
-    sh, ctx, steps, stride = SHAPES[str(g['shape'])], int(g['ctx']), int(g['steps']), int(g['stride'])
+    g = load(name)
+    sh, steps, stride = SHAPES[str(g['shape'])], int(g['steps']), int(g['stride'])
     W = weights(sh, int(g['seed']), str(g['init']))
     for i, b in enumerate(g['sample']):
+        ctx = int(g['ctxs'][b])
         k0, v0 = make_cache(sh, int(g['cache_seed_base']) + int(b), ctx)
         keys = np.zeros((sh.L, ctx + steps, sh.H, sh.E), np.float16); vals = np.zeros_like(keys)
         keys[:, :ctx] = k0; vals[:, :ctx] = v0
