@@ -11,6 +11,7 @@ CPU oracle (oracle/gpt2_numpy.py) and, through it and directly, the GPU kernel.
     python tests/golden/make_golden.py xl                         # 8 steps of the XL-shaped program
     python tests/golden/make_golden.py cfg3_sample                # 4 of 64 sequences, 2 steps at context 600 on a seeded cache
     python tests/golden/make_golden.py cfg5_sample                # 4 of 32 sequences with contexts 64..512 (ragged batch)
+    python tests/golden/make_golden.py xl16_sample                # 2 of 16 sequences of the XL shape at context 300
 
 Each fixture: per sequence the greedy token chosen at every step, the top-1 margin, and for a
 set of kept steps a strided sample of the logits plus the top-5 (index, value) pairs; small
@@ -150,6 +151,7 @@ def build_cache_sample(name, shape, seed, init, batch, ctx, steps, sample):
 
 TARGETS = {
     'cfg3_sample': lambda: build_cache_sample('gpt2_cfg3_sample', 'gpt2', 5, 'rich', 64, 600, 2, [0, 21, 42, 63]),
+    'xl16_sample': lambda: build_cache_sample('gpt2_xl16_sample', 'gpt2_xl', 0, 'baseline', 16, 300, 2, [0, 15]),
     'cfg5_sample': lambda: build_cache_sample('gpt2_cfg5_sample', 'gpt2', 5, 'rich', 32, lambda b: 64 + (b * 53) % 449, 2, [0, 9, 20, 31]),
     'tiny': lambda: build('tiny_b3', 'tiny', 3, 'rich', 3, 5, 12, set(range(17)), True, 1),
     'tiny3': lambda: build('tiny3_b2', 'tiny3', 4, 'rich', 2, 7, 20, set(range(27)), True, 1),

@@ -74,12 +74,12 @@ def test_gpt2_xl_shape():
     run_fixture('gpt2_xl_b1')
 
 
-@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample'])
+@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample', 'gpt2_xl16_sample'])
 def test_deep_context_samples_against_the_reference(name):
     """the large-batch paths at full model size against the reference interpreter: (cfg3) 64 sequences with 600
     positions in every cache: slabs, distributed LayerNorm, fold-slice MLP projection, several attention items of
     five tiles per CTA, tcgen05 logits; (cfg5) a ragged batch of 32 with 64..512 positions per sequence and
-    per-sequence positions. Caches are seeded (synth.make_cache); the sampled sequences are compared over two
+    per-sequence positions; (xl16) the XL shape at batch 16, context 300. Caches are seeded (synth.make_cache); the sampled sequences are compared over two
     teacher-forced steps."""
     from vesta_gpu_b200.shapes import SHAPES
     from vesta_gpu_b200.synth import make_cache

@@ -38,6 +38,27 @@ def check_fixture(name, seqs=None, steps=None):
                 assert np.abs(r['logits'][t][g[f'top_idx_{i}'][k]] - g[f'top_val_{i}'][k]).max() < TIGHT
 
 
+def check_samples(name):
+    """sampled sequences of a large batch, two teacher-forced steps on seeded caches (the reference interpreter needs
+    a second per position, so these fixtures start from a filled cache instead of a long prompt)"""
+    from vesta_gpu_b200.shapes import SHAPES
+    from vesta_gpu_b200.synth import make_cache
+    g = load(name)
+    sh, steps, stride = SHAPES[str(g['shape'])], int(g['steps']), int(g['stride'])
+    W = weights(sh, int(g['seed']), str(g['init']))
+    for i, b in enumerate(g['sample']):
+        ctx = int(g['ctxs'][b])
+        k0, v0 = make_cache(sh, int(g['cache_seed_base']) + int(b), ctx)
+        keys = np.zeros((sh.L, ctx + steps, sh.H, sh.E), np.float16); vals = np.zeros_like(keys)
+        keys[:, :ctx] = k0; vals[:, :ctx] = v0
+        for s_ in range(steps):
+            logit, nxt = O.step(sh, W, keys, vals, int(g[f'fed_{i}'][s_]), ctx + s_)
+            assert np.abs(logit[::stride] - g[f'logits_{i}'][s_]).max() < TIGHT
+            assert np.abs(logit[g[f'top_idx_{i}'][s_]] - g[f'top_val_{i}'][s_]).max() < TIGHT
+            if g[f'margins_{i}'][s_] > MARGIN:
+                assert nxt == int(g[f'tokens_{i}'][s_])
+
+
 def test_tiny_all_steps():
     check_fixture('tiny_b3')
 
@@ -64,6 +85,11 @@ def test_gpt2_xl_shape():
     check_fixture('gpt2_xl_b1')
 
 
+def test_gpt2_xl_batch16_sample():
+    """two of 16 sequences of the XL shape at context 300 (runs next to the other XL test: the weights are shared)"""
+    check_samples('gpt2_xl16_sample')
+
+
 def test_tie_goes_to_lowest_index():
     """gpt2.vst:81-82: next = min index whose logit equals the maximum"""
     logit = np.array([0.5, 2.0, 2.0, 1.0], np.float32)
@@ -85,22 +111,5 @@ def test_kv_cache_rounds_to_fp16():
 
 @pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample'])
 def test_gpt2_small_deep_context_samples(name):
-    """sampled sequences of the batch-64 config (context 600) and of a ragged batch of 32 (contexts 64..512): two
-    teacher-forced steps on seeded caches (the reference interpreter needs a second per position, so the fixtures
-    start from a filled cache instead of a long prompt)"""
-    from vesta_gpu_b200.shapes import SHAPES
-    from vesta_gpu_b200.synth import make_cache
-    g = load(name)
-    sh, steps, stride = SHAPES[str(g['shape'])], int(g['steps']), int(g['stride'])
-    W = weights(sh, int(g['seed']), str(g['init']))
-    for i, b in enumerate(g['sample']):
-        ctx = int(g['ctxs'][b])
-        k0, v0 = make_cache(sh, int(g['cache_seed_base']) + int(b), ctx)
-        keys = np.zeros((sh.L, ctx + steps, sh.H, sh.E), np.float16); vals = np.zeros_like(keys)
-        keys[:, :ctx] = k0; vals[:, :ctx] = v0
-        for s_ in range(steps):
-            logit, nxt = O.step(sh, W, keys, vals, int(g[f'fed_{i}'][s_]), ctx + s_)
-            assert np.abs(logit[::stride] - g[f'logits_{i}'][s_]).max() < TIGHT
-            assert np.abs(logit[g[f'top_idx_{i}'][s_]] - g[f'top_val_{i}'][s_]).max() < TIGHT
-            if g[f'margins_{i}'][s_] > MARGIN:
-                assert nxt == int(g[f'tokens_{i}'][s_])
+    """the batch-64 config at context 600 and a ragged batch of 32 with contexts 64..512"""
+    check_samples(name)
