@@ -99,6 +99,17 @@ class ClockSampler:
         return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=int(rows[0][1]), reasons=reasons, samples=len(rows))
 
 
+def host_threads():
+    """let NumPy's BLAS use every host core (torchrun exports OMP_NUM_THREADS=1); -> the threads it then runs on"""
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+        threadpool_limits(limits=os.cpu_count())
+        n = [int(i.get('num_threads', 1)) for i in threadpool_info()]
+        return max(n) if n else 1
+    except Exception:
+        return 1
+
+
 def cpu_baseline(sh, W, batch, ctx, steps, warm=1, max_seconds=None):
     """the NumPy oracle on the host: up to `steps` decode steps of one sequence starting at context ~ctx (the cache
     is filled with random fp16 values: the time does not depend on them), cut short after max_seconds.
@@ -130,10 +141,10 @@ def run_reference(args, wl, sh):
     from oracle import gpt2_numpy as O
     from vesta_gpu_b200.synth import make_weights
     W = O.upcast(make_weights(sh, 0))
+    cores = host_threads()
     ctx = wl['prompt'] + wl['gen'] // 2
     # every step is one decode step of one sequence (a bounded sample of the batch); at most two minutes in all
     tps, dt, steps = cpu_baseline(sh, W, wl['batch'], ctx, max(1, args.steps), warm=max(1, min(args.warmup, 3)), max_seconds=120)
-    cores = os.cpu_count()
     sample = f'{steps} decode steps of one sequence at context {ctx} (of batch {wl["batch"]} x {wl["gen"]} steps), sequences run one after another'
     line = dict(metric=METRIC, value=tps, unit=UNIT, impl='reference', n_gpus=args.gpus, steps=steps, warmup=args.warmup,
                 ms_per_step=1e3 * dt / steps / 1.0, higher_is_better=True, scaling='weak', vs_baseline=None,
@@ -313,10 +324,11 @@ def main():
                               frac_of_8tbs=achieved / 8000.0))
     if not args.no_cpu_baseline and world == 1:
         from oracle import gpt2_numpy as O
+        cores = host_threads()
         ctx = P + K // 2
         # a bounded sample: about 12 seconds of decode steps of one sequence
         tps, dt, nsteps = cpu_baseline(sh, O.upcast(hf.weights), B, ctx, 2000, max_seconds=12)
-        line['cpu_baseline'] = dict(value=tps, unit=UNIT, cores=os.cpu_count(), kind='port',
+        line['cpu_baseline'] = dict(value=tps, unit=UNIT, cores=cores, kind='port',
                                     sample=f'{nsteps} decode steps of one sequence at context {ctx}, NumPy oracle, {dt:.1f} s')
     print(json.dumps(line))
     if world > 1:
