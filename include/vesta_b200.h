@@ -102,7 +102,11 @@ void vesta_step_release(void* bound);
  * an error (vesta_static_last_error) and nothing is launched. The array is shared by every call and
  * keeps the last call's contents: each call clears the range it uses first, and calls that overlap
  * on the GPU race on it. The first call on a device resolves the array's address and should be
- * made before any stream capture. */
+ * made before any stream capture. The kernel's status word lives in the array as well, so it is
+ * copied to status_out (4 bytes, device or pinned host memory, may be NULL) on `stream` with the
+ * results: 0 = the step ran; 0x900 = refused (a position outside the cache or a token outside the
+ * vocabulary; logits and next are then zero and x, t and the cache untouched); anything else = a
+ * bounded wait gave up (phase in bits 8-15, CTA in bits 16-31). At most 56 residues. */
 size_t vesta_static_scratch_bytes(void);
 const char* vesta_static_last_error(void);
 int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
@@ -112,7 +116,7 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
                       size_t scratch_floats, size_t counters,
                       size_t logit_offset, size_t logit_count, float* logits_out,
                       size_t next_offset, size_t next_count, float* next_out,
-                      void* stream);
+                      unsigned* status_out, void* stream);
 
 #ifdef __cplusplus
 }

@@ -12,6 +12,9 @@ CPU oracle (oracle/gpt2_numpy.py) and, through it and directly, the GPU kernel.
     python tests/golden/make_golden.py cfg3_sample                # 4 of 64 sequences, 2 steps at context 600 on a seeded cache
     python tests/golden/make_golden.py cfg5_sample                # 4 of 32 sequences with contexts 64..512 (ragged batch)
     python tests/golden/make_golden.py xl16_sample                # 2 of 16 sequences of the XL shape at context 300
+    python tests/golden/make_golden.py cfg5_b64_sample cfg5_b256_sample   # 4 sequences of ragged batches of 64 and of 256
+    python tests/golden/make_golden.py cfg3_tail_sample           # batch 64 at context 1021..1023: the last position of a 1024-row cache
+    python tests/golden/make_golden.py xl1_sample                 # the XL shape at batch 1, context 300
 
 Each fixture: per sequence the greedy token chosen at every step, the top-1 margin, and for a
 set of kept steps a strided sample of the logits plus the top-5 (index, value) pairs; small
@@ -26,7 +29,9 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get('VESTA_REFERENCE', '/root/reference')
+REF = os.environ.get('VESTA_REFERENCE')
+if not REF:
+    raise SystemExit('set VESTA_REFERENCE to a checkout of the reference (the directory that holds vesta/interp.py)')
 sys.path.insert(0, ROOT)
 
 from vesta_gpu_b200.shapes import SHAPES                      # noqa: E402
@@ -153,6 +158,10 @@ TARGETS = {
     'cfg3_sample': lambda: build_cache_sample('gpt2_cfg3_sample', 'gpt2', 5, 'rich', 64, 600, 2, [0, 21, 42, 63]),
     'xl16_sample': lambda: build_cache_sample('gpt2_xl16_sample', 'gpt2_xl', 0, 'baseline', 16, 300, 2, [0, 15]),
     'cfg5_sample': lambda: build_cache_sample('gpt2_cfg5_sample', 'gpt2', 5, 'rich', 32, lambda b: 64 + (b * 53) % 449, 2, [0, 9, 20, 31]),
+    'cfg5_b64_sample': lambda: build_cache_sample('gpt2_cfg5_b64_sample', 'gpt2', 5, 'rich', 64, lambda b: 64 + (b * 53) % 449, 2, [0, 21, 42, 63]),
+    'cfg5_b256_sample': lambda: build_cache_sample('gpt2_cfg5_b256_sample', 'gpt2', 5, 'rich', 256, lambda b: 64 + (b * 53) % 449, 2, [0, 85, 170, 255]),
+    'cfg3_tail_sample': lambda: build_cache_sample('gpt2_cfg3_tail_sample', 'gpt2', 5, 'rich', 64, 1021, 3, [0, 21, 42, 63]),
+    'xl1_sample': lambda: build_cache_sample('gpt2_xl1_sample', 'gpt2_xl', 0, 'baseline', 1, 300, 2, [0]),
     'tiny': lambda: build('tiny_b3', 'tiny', 3, 'rich', 3, 5, 12, set(range(17)), True, 1),
     'tiny3': lambda: build('tiny3_b2', 'tiny3', 4, 'rich', 2, 7, 20, set(range(27)), True, 1),
     'small_rich': lambda: build('gpt2_rich_b1', 'gpt2', 5, 'rich', 1, 6, 6, set(range(12)), False, 1),

@@ -79,3 +79,25 @@ def test_product_does_not_import_the_oracle():
             if f.endswith(('.py', '.cuh', '.cpp', '.cu')):
                 text = open(os.path.join(dirpath, f), encoding='utf-8').read()
                 assert 'import oracle' not in text and 'from oracle' not in text, f
+
+
+def test_static_step_refuses_oversized_requests_before_touching_the_gpu(built_library):
+    """vesta_step_static checks its sizes on the host first: more residues than its argument array holds, a scratch
+    size whose byte count would wrap around, and output ranges outside the scratch are all refused with a message
+    (no CUDA call has been made at that point, so this runs without a GPU)"""
+    lib = ctypes.CDLL(str(built_library))
+    lib.vesta_static_last_error.restype = ctypes.c_char_p
+    sz, vp, ull = ctypes.c_size_t, ctypes.c_void_p, ctypes.c_ulonglong
+    ptrs = (ull * 64)(*([0x1000] * 64))
+    fn = vp(0x10)                                   # never launched: every case below is refused before that
+
+    def call(n_res=20, scratch=1024, counters=64, lo=0, ln=16, no=16, nn=4):
+        return lib.vesta_step_static(fn, 148, 288, 0, n_res, ptrs, ull(0), ull(0), ull(0), sz(scratch), sz(counters),
+                                     sz(lo), sz(ln), vp(None), sz(no), sz(nn), vp(None), vp(None), vp(None))
+    assert call(n_res=57) != 0 and b'residues' in lib.vesta_static_last_error()
+    assert call(n_res=-1) != 0
+    assert call(scratch=(1 << 62) + 8) != 0 and b'static scratch holds' in lib.vesta_static_last_error()
+    assert call(scratch=(4 << 20) // 4) != 0 and b'static scratch holds' in lib.vesta_static_last_error()
+    assert call(counters=1 << 20) != 0 and b'counter' in lib.vesta_static_last_error()
+    assert call(lo=(1 << 64) - 8, ln=16) != 0 and b'output range' in lib.vesta_static_last_error()
+    assert call(no=1000, nn=100) != 0 and b'output range' in lib.vesta_static_last_error()

@@ -187,7 +187,8 @@ def test_tensor_core_logits_are_chosen_where_the_contraction_is_dense():
     assert define(lower_for(GPT2_SMALL, 64, 1025), 'V_TC') == 1
     assert define(lower_for(GPT2_SMALL, 256, 640), 'V_TC') == 1
     assert define(lower_for(GPT2_SMALL, 63, 64), 'V_TC') == 0
-    assert define(lower_for(GPT2_SMALL, 8, 384), 'V_TC') == 0
+    assert lower_for(GPT2_SMALL, 8, 384).dims['kernel'] == 'small' and not lower_for(GPT2_SMALL, 8, 384).dims['tc']
+    assert define(lower_for(GPT2_SMALL, 8, 384, tune=dict(large_kernel=True)), 'V_TC') == 0
     assert define(lower_for(GPT2_XL, 64, 64), 'V_TC') == 0              # 64 x 1600 halves exceed the stages
     assert define(lower_for(GPT2_SMALL, 64, 64, tune=dict(tc=False)), 'V_TC') == 0
     low = lower_for(GPT2_SMALL, 64, 1025)
@@ -197,7 +198,7 @@ def test_tensor_core_logits_are_chosen_where_the_contraction_is_dense():
 def test_attention_items_cover_every_sequence_head_and_position():
     """the item arithmetic of the attention phase (att_item / att_load_item in csrc/step_kernel.cuh) restated: whole
     rounds of one item per (sequence, head), then the leftover pairs split into position chunks"""
-    for sh, B, tmax, tune in ((GPT2_SMALL, 64, 1025, None), (GPT2_SMALL, 1, 384, None), (TINY3, 60, 6, dict(tail_split=4)),
+    for sh, B, tmax, tune in ((GPT2_SMALL, 64, 1025, None), (GPT2_SMALL, 1, 384, dict(large_kernel=True)), (TINY3, 60, 6, dict(tail_split=4)),
                               (GPT2_SMALL, 64, 400, None)):
         low = lower_for(sh, B, tmax, tune=tune)
         nch, tail_bh, ts, H = define(low, 'V_NCH'), define(low, 'V_TAIL_BH'), define(low, 'V_TS'), low.dims['H']
@@ -215,6 +216,54 @@ def test_attention_items_cover_every_sequence_head_and_position():
             assert seen.min() == 1 and seen.max() == 1
         if sh is GPT2_SMALL and B == 64 and tmax == 1025:
             assert ts == 4 and tail_bh == 740 and items <= 6 * 148        # five whole rounds and one of quarter items
+
+
+def small_tile_list(low, cta, pos):
+    """build_tile_list of csrc/step_small.cuh restated: the K/V tiles of one CTA for the positions `pos` of the sequences"""
+    nch, H, kvst, maxtl, grid = define(low, 'V_NCH'), low.dims['H'], define(low, 'V_KVST'), define(low, 'V_MAXTL'), low.grid
+    out, live = [], 0
+    for it in range(cta, len(pos) * H * nch, grid):
+        bh, ch = divmod(it, nch)
+        b, h = divmod(bh, H)
+        npos = pos[b] + 1
+        cs = (max(npos, 1) + nch - 1) // nch
+        s, hi = ch * cs, min(npos, (ch + 1) * cs)
+        if hi <= s:
+            out.append(dict(b=b, h=h, s=0, cnt=0, last=True, patch=False, item=it))
+            continue
+        while s < hi:
+            cnt = min(128, hi - s)
+            out.append(dict(b=b, h=h, s=s, cnt=cnt, last=s + 128 >= hi, patch=live < kvst and s <= pos[b] < s + cnt, item=it))
+            live += 1
+            s += 128
+    assert len(out) <= maxtl, (len(out), maxtl)
+    return out
+
+
+def test_small_kernel_tile_lists_cover_every_sequence_head_and_position():
+    """at most eight sequences: every (sequence, head, position) is in exactly one tile of one CTA, every item ends with a
+    `last` tile, the list fits the space the lowering reserved, and the tile that holds the current position is marked
+    for patching whenever it can be requested before the barrier (among the first V_KVST tiles of its CTA)"""
+    for sh, B, tmax, pos in ((GPT2_SMALL, 8, 385, [384] * 8), (GPT2_SMALL, 8, 385, [0, 5, 127, 128, 129, 300, 383, -3]),
+                             (GPT2_SMALL, 1, 1024, [1023]), (GPT2_XL, 1, 385, [200]), (TINY3, 5, 9, [8, 0, 3, -1, 4]),
+                             (GPT2_XL, 8, 1024, [1023] * 8)):
+        low = lower_for(sh, B, tmax, per_sequence_t=True)
+        assert low.dims['kernel'] == 'small'
+        seen = [np.zeros((sh.H, max(p + 1, 0)), np.int32) for p in pos]
+        items = set()
+        for cta in range(low.grid):
+            tl = small_tile_list(low, cta, pos)
+            for k, e in enumerate(tl):
+                seen[e['b']][e['h'], e['s']: e['s'] + e['cnt']] += 1
+                if e['last']:
+                    assert e['item'] not in items
+                    items.add(e['item'])
+                early = sum(1 for f in tl[:k] if f['cnt']) < define(low, 'V_KVST')
+                holds = e['cnt'] and e['s'] <= pos[e['b']] < e['s'] + e['cnt']
+                assert e['patch'] == bool(early and holds)
+        assert all(v.size == 0 or (v.min() == 1 and v.max() == 1) for v in seen)
+        assert items == set(range(B * sh.H * define(low, 'V_NCH')))
+        assert low.shared_bytes <= 227 * 1024
 
 
 def test_small_division_by_reciprocal_is_exact():

@@ -21,20 +21,20 @@ from helpers import TIGHT
 pytestmark = pytest.mark.gpu
 
 
-def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=None, tmaps=None):
+def static_step(lib, k, residues, stream, logits_out, next_out, scratch_floats=None, tmaps=None, status_out=None, n_residues=None):
     low = k.lowered
     ptrs = [residues[name].data_ptr() for name, _, _ in low.params]
     arr = (ctypes.c_ulonglong * len(ptrs))(*ptrs)
     lo, _, lshape = low.scratch['logit']
     no, _, nshape = low.scratch['next']
-    return lib.vesta_step_static(k.fn, k.grid, k.block, k.smem, len(ptrs), arr,
+    return lib.vesta_step_static(k.fn, k.grid, k.block, k.smem, len(ptrs) if n_residues is None else n_residues, arr,
                                  ctypes.c_ulonglong(k.WP.data_ptr()), ctypes.c_ulonglong(k.PT.data_ptr()),
                                  ctypes.c_ulonglong(tmaps.data_ptr()),
                                  ctypes.c_size_t(low.scratch_floats if scratch_floats is None else scratch_floats),
                                  ctypes.c_size_t(low.counters),
                                  ctypes.c_size_t(lo), ctypes.c_size_t(int(np.prod(lshape))), ctypes.c_void_p(logits_out.data_ptr()),
                                  ctypes.c_size_t(no), ctypes.c_size_t(int(np.prod(nshape))), ctypes.c_void_p(next_out.data_ptr()),
-                                 ctypes.c_void_p(stream))
+                                 ctypes.c_void_p(status_out.data_ptr() if status_out is not None else None), ctypes.c_void_p(stream))
 
 
 def test_static_scratch_step_matches_the_allocating_path():
@@ -65,11 +65,13 @@ def test_static_scratch_step_matches_the_allocating_path():
     nxt = torch.empty(B, dtype=torch.float32, device='cuda')
     stream = torch.cuda.current_stream().cuda_stream
 
+    status = torch.full((1,), 77, dtype=torch.int32, device='cuda')
     for step in range(2):                       # two calls in a row: the second one finds the first one's leftovers
         m.step()
-        rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps)
+        rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps, status_out=status)
         assert rc == 0, lib.vesta_static_last_error()
         torch.cuda.synchronize()
+        assert int(status.item()) == 0, step
         assert torch.allclose(logits, m.logits(), atol=TIGHT, rtol=0), step
         assert torch.equal(nxt, m.next()), step
         assert torch.equal(mine['x'], m.x) and torch.equal(mine['t'], m.t), step
@@ -82,3 +84,24 @@ def test_static_scratch_step_matches_the_allocating_path():
     assert rc != 0 and b'static scratch holds' in lib.vesta_static_last_error()
     torch.cuda.synchronize()
     assert torch.equal(before, logits)
+    # sizes that would wrap around a 64-bit byte count are refused as well, and so is an argument list that
+    # would not fit the entry point's own array
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, scratch_floats=(1 << 62) + 8, tmaps=tmaps)
+    assert rc != 0 and b'static scratch holds' in lib.vesta_static_last_error()
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps, n_residues=57)
+    assert rc != 0 and b'residues' in lib.vesta_static_last_error()
+
+    # a step the kernel itself refuses (the position is the end of the cache) comes back as a status, not as
+    # "token 0": the call succeeds, the status word says why nothing was computed, x and t stay as they were
+    mine['t'].fill_(tmax)
+    x_before = mine['x'].clone()
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps, status_out=status)
+    assert rc == 0, lib.vesta_static_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) & 0xff00 == 0x900
+    assert torch.equal(mine['x'], x_before) and int(mine['t'][0]) == tmax
+    # and the next good step through the same array is unaffected by that refusal
+    mine['t'].fill_(2)
+    rc = static_step(lib, m.k, mine, stream, logits, nxt, tmaps=tmaps, status_out=status)
+    torch.cuda.synchronize()
+    assert rc == 0 and int(status.item()) == 0

@@ -17,7 +17,11 @@
 //   * calls that overlap on the GPU (two streams, two threads) race on the array: one call at a
 //     time per device, or order them on one stream;
 //   * the first call on a device looks the array's address up (cudaGetSymbolAddress, with that
-//     device current) and caches it; make that first call before any stream capture begins.
+//     device current) and caches it; make that first call before any stream capture begins;
+//   * the kernel's status word (0 = the step ran; otherwise why it was refused or where a bounded wait
+//     gave up, as Kernel.status() of the ordinary path reports it) lives in the array too, so the call
+//     copies it out to `status_out` with the results: a refused step leaves logits and next at zero,
+//     which would otherwise read as "token 0".
 #include <cuda_runtime.h>
 #include <mutex>
 #include <string>
@@ -28,6 +32,7 @@
 #define COUNTER_WORDS 2048                      // barrier / status words at the front of the array
 #define TIMING_WORDS 2048                       // 64-bit timing sums behind them
 #define HEADER_BYTES (COUNTER_WORDS * 4 + TIMING_WORDS * 8)
+#define VESTA_STATIC_MAX_RESIDUES 56            // kernel parameters that are residues (the step program has 20 to 22)
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device address.
 static __device__ __align__(256) unsigned char vesta_static_scratch[VESTA_STATIC_SCRATCH_BYTES];
@@ -82,17 +87,20 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
                       size_t scratch_floats, size_t counters,
                       size_t logit_offset, size_t logit_count, float* logits_out,
                       size_t next_offset, size_t next_count, float* next_out,
-                      void* stream) {
-    if (!function || n_residues < 0 || n_residues > 60 || (n_residues && !residue_pointers))
-        return fail("vesta_step_static: bad argument");
+                      unsigned* status_out, void* stream) {
+    // the argument array below holds the residues and the seven pointers and counts that follow them
+    if (!function || n_residues < 0 || n_residues > VESTA_STATIC_MAX_RESIDUES || (n_residues && !residue_pointers))
+        return fail("vesta_step_static: bad argument (at most " + std::to_string(VESTA_STATIC_MAX_RESIDUES) + " residues)");
     if (counters > COUNTER_WORDS)
         return fail("vesta_step_static: the program needs " + std::to_string(counters) + " counter words, the static scratch holds " +
                     std::to_string(COUNTER_WORDS));
+    // compared before multiplying: a huge count must not wrap around into range
+    if (scratch_floats > (VESTA_STATIC_SCRATCH_BYTES - HEADER_BYTES) / sizeof(float))
+        return fail("vesta_step_static: this step needs " + std::to_string(scratch_floats) + " floats of scratch, the static scratch holds " +
+                    std::to_string((size_t)(VESTA_STATIC_SCRATCH_BYTES - HEADER_BYTES) / sizeof(float)) + " (batch x vocabulary is too large for the no-allocation path)");
     const size_t need = HEADER_BYTES + scratch_floats * sizeof(float);
-    if (need > VESTA_STATIC_SCRATCH_BYTES)
-        return fail("vesta_step_static: this step needs " + std::to_string(need) + " bytes of scratch, the static scratch holds " +
-                    std::to_string((size_t)VESTA_STATIC_SCRATCH_BYTES) + " (batch x vocabulary is too large for the no-allocation path)");
-    if (logit_offset + logit_count > scratch_floats || next_offset + next_count > scratch_floats)
+    if (logit_offset > scratch_floats || logit_count > scratch_floats - logit_offset ||
+        next_offset > scratch_floats || next_count > scratch_floats - next_offset)
         return fail("vesta_step_static: output range outside the scratch");
     unsigned char* base = nullptr;
     if (scratch_base(&base)) return -1;
@@ -105,8 +113,8 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     if (e != cudaSuccess) return fail(std::string("clear_static_scratch: ") + cudaGetErrorString(e));
 
     // the step kernel's parameters: residues, then S, bar, TS, packed weights, plan table, K/V descriptors, steps per launch
-    unsigned long long vals[64];
-    void* args[64];
+    unsigned long long vals[VESTA_STATIC_MAX_RESIDUES + 7];
+    void* args[VESTA_STATIC_MAX_RESIDUES + 7];
     int n = 0;
     for (; n < n_residues; n++) vals[n] = residue_pointers[n];
     vals[n++] = (unsigned long long)(base + HEADER_BYTES);              // S
@@ -128,6 +136,10 @@ int vesta_step_static(void* function, unsigned grid, unsigned block, unsigned dy
     if (next_out && next_count) {
         e = cudaMemcpyAsync(next_out, S + next_offset, next_count * sizeof(float), cudaMemcpyDefault, st);
         if (e != cudaSuccess) return fail(std::string("copy of next: ") + cudaGetErrorString(e));
+    }
+    if (status_out) {
+        e = cudaMemcpyAsync(status_out, base, sizeof(unsigned), cudaMemcpyDefault, st);       // bar[0]: the kernel's status word
+        if (e != cudaSuccess) return fail(std::string("copy of the status word: ") + cudaGetErrorString(e));
     }
     return 0;
 }

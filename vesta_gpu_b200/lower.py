@@ -29,7 +29,10 @@ import numpy as np
 
 from . import syntax as sx
 
-KERNEL_TEXT = Path(__file__).resolve().parent / 'csrc' / 'step_kernel.cuh'
+CSRC = Path(__file__).resolve().parent / 'csrc'
+COMMON_TEXT = CSRC / 'step_common.cuh'
+KERNEL_TEXT = CSRC / 'step_kernel.cuh'          # batches above eight sequences
+SMALL_TEXT = CSRC / 'step_small.cuh'            # at most eight sequences: one batch tile
 
 CTYPE = {'f32': 'float', 'f16': 'unsigned short', 'i32': 'int'}
 NW = 8                 # consumer warps per CTA (one more warp streams the weights)
@@ -309,6 +312,138 @@ def place_step(dims, grid, ksplit=False):
 
 
 # ------------------------------------------------------------------ assembly
+
+def _entry_points(res, roles, fb, prompt_len, with_tensor_core_arg=True):
+    """-> (params, pack_params, text of the two extern "C" kernels that wrap step_body / pack_body)"""
+    emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
+    params, sig = [], []
+    for name, (shape, dt) in res.items():
+        em = name in emitted
+        params.append((name, dt, em))
+        sig.append(f'{"" if em else "const "}{CTYPE[dt]}* __restrict__ R_{name}')
+    if prompt_len and fb:
+        params += [('prompt', 'i32', False), ('plen', 'i32', False)]
+        sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
+    R = {k: 'R_' + v for k, v in roles.items()}
+    step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
+                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT',
+                                'const unsigned char* __restrict__ TM', 'int nsteps'])
+    fill = [f'a.x = {R["x"]}; a.t = {R["t"]};']
+    for k in ('wte', 'wpe', 'ln1w', 'ln1b', 'qkvb', 'ob', 'ln2w', 'ln2b', 'fcb', 'pb', 'lnfw', 'lnfb'):
+        fill.append(f'a.{k} = {R[k]};')
+    fill.append(f'a.keys = {R["keys"]}; a.vals = {R["vals"]};')
+    if fb:
+        fill.append(f'a.x_out = {R["x"]}; a.t_out = {R["t"]};')
+    else:
+        fill.append('a.x_out = 0; a.t_out = 0;')
+    fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
+    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.TM = TM; a.nsteps = nsteps;')
+    pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
+    pack_params = [roles[k] for k in pack_roles]
+    pack_sig = ', '.join([f'const unsigned short* __restrict__ R_{roles[k]}' for k in pack_roles]
+                         + ['unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
+    pack_fill = ' '.join(f'p.{k} = R_{roles[k]};' for k in pack_roles) + ' p.WP = WP; p.PT = PT;'
+    tail = (f'\nextern "C" __global__ void __launch_bounds__(NTHREADS, 1) vesta_step({step_sig}) {{\n'
+            f'    Args a; {" ".join(fill)}\n    step_body(a);\n}}\n'
+            f'\nextern "C" __global__ void vesta_pack({pack_sig}) {{\n'
+            f'    PackArgs p; {pack_fill}\n    pack_body(p);\n}}\n')
+    return params, pack_params, tail
+
+
+def _f32(v):
+    return repr(float(np.float32(v))) + 'f'
+
+
+def _up(v, a=64):
+    return (v + a - 1) // a * a
+
+
+def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, prompt_len, timing, grid, tune):
+    """at most eight sequences: the kernel text csrc/step_small.cuh (one batch tile, fold split over the warps of a CTA
+    for QKV and FC, whole output tiles per warp for the projections, attention tiles listed once per step)"""
+    D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
+    KT_D = D // 16
+    rec, tiles, notes = place_step(dims, grid, False)
+    umax = max(int(rec[:, 7].max()), int(rec[:, 9].max()), 1)            # deepest fold slice of a projection unit
+    if umax > CHUNK_TILES:
+        raise NotImplementedError('placement: a projection unit exceeds a ring slot')
+    kvst = int(tune.get('kv_stages', 3 if B * H > grid else 2))
+
+    # position chunks per (sequence, head): rounds of the grid x (positions per chunk + the fixed cost of an item,
+    # about one and a half tiles of 128 positions), at a typical context of tmax / 2
+    def att_cost(k):
+        return math.ceil(B * H * k / grid) * (max(tmax // 2, 1) / k + 192)
+    nch = int(tune.get('nch', min(range(1, 17), key=lambda k: (att_cost(k), k))))
+    att_items = B * H * nch
+    maxtl = math.ceil(att_items / grid) * math.ceil(math.ceil(tmax / nch) / 128)
+
+    off_logit, off_next = 0, _up(B * N)
+    off_z = _up(off_next + B)
+    off_q = off_z + 3 * _up(B * D)
+    off_part = off_q + _up(B * D)
+    off_best = off_part + _up(att_items * (E + 2))
+    scratch_floats = off_best + _up(2 * B)
+    scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
+
+    # shared memory: [weight ring | K/V stages | operand tiles | GELU operand tiles | partial sums | parameters | misc | barriers]
+    ch = CHUNK_TILES
+    budget = SMEM_LIMIT - (8192 if timing else 0)
+    prm_bytes = (3 * D + WN_MAX * 16) * 2
+    misc_bytes = 2 * NW * (E + 2) * 4 + 8 * NW * 8 + 32 + 512 + 16 + maxtl * 16
+    fixed = kvst * 32768 + KT_D * 512 + WN_MAX * 512 + NW * WN_MAX * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
+    nslot = min((budget - fixed - 2 * kvst * 8 - 64) // (ch * 512 + 16), 16)
+    if nslot < 2:
+        raise NotImplementedError('model too wide for the shared-memory budget')
+    sm_ring = 0
+    sm_kv = sm_ring + nslot * ch * 512
+    sm_act = sm_kv + kvst * 32768
+    sm_gact = sm_act + KT_D * 512
+    sm_red = sm_gact + WN_MAX * 512
+    sm_prm = sm_red + NW * WN_MAX * 512
+    sm_misc = sm_prm + _up(prm_bytes, 16)
+    sm_bars = sm_misc + _up(misc_bytes, 16)
+    shared = sm_bars + (2 * nslot + 2 * kvst) * 8
+
+    scale = dims['scale']
+    defs = dict(V_NW=NW, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
+                V_EPS=_f32(dims['eps']), V_SCALE=_f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5),
+                V_GELU_A=_f32(dims['gelu'][0]), V_GELU_B=_f32(dims['gelu'][1]), V_GELU_C=_f32(dims['gelu'][2]),
+                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
+                V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
+                V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0,
+                V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q, V_OFF_PART=off_part, V_OFF_BEST=off_best,
+                V_SM_RING=sm_ring, V_SM_KV=sm_kv, V_SM_ACT=sm_act, V_SM_GACT=sm_gact, V_SM_RED=sm_red, V_SM_PRM=sm_prm,
+                V_SM_MISC=sm_misc, V_SM_BARS=sm_bars,
+                V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
+    head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
+    params, pack_params, tail = _entry_points(res, roles, fb, prompt_len)
+    src = head + COMMON_TEXT.read_text(encoding='utf-8') + SMALL_TEXT.read_text(encoding='utf-8') + tail
+
+    q = env
+    ln_how = (f'every CTA recomputes: {NW // (1 if B <= 1 else 2 if B <= 2 else 4 if B <= 4 else 8)} warp(s) per row, the row in registers, '
+              'into mma operand tiles (fp16 head + fp16 remainder)')
+    plan = [
+        (f'{q["$z0"]} (embed)', 'grid-stride, then barrier'),
+        (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', ln_how),
+        (f'{q["$qkv"]} + emits', f'whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA, the fold split over the 8 warps; bias, q, K/V emit in the epilogue'),
+        (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)',
+         f'one item per (sequence, head, 1/{nch} of the positions), dealt round-robin over the CTAs, cut into tiles of 128 positions once per step; '
+         f'K/V tiles by TMA ({kvst} stages), online softmax in registers, merged by the projection'),
+        (f'{q["$oo"]}, {q["$z1"]}', f'fold slices: {notes["proj_units"]} units of up to {WG} output tiles x {notes["proj_nk"]} fold tiles, whole output tiles per warp, fp32 atomics'),
+        (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', ln_how),
+        (f'{q["$u"]}, {q["$g"]}', f'whole fold, {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
+        (f'{q["$z2"]}', 'fold slice = the CTA\'s own f tiles, whole output tiles per warp, fp32 atomics'),
+        (f'{q["$m3"]}, {q["$v3"]}, {q["$c"]} (LNf)', ln_how),
+        (f'{q["$logit"]}', f'whole fold, {min(rec[:, 11])}-{max(rec[:, 11])} vocabulary tiles per CTA in groups of 16, two per warp'),
+        (f'{q["$best"]}, {q["$next"]}, feedback', 'packed (value, ~index) max per CTA, atomicMax, last CTA publishes and releases the next step of the launch'),
+    ]
+    sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] + ['logits', 'finish']
+    return Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
+                   barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
+                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
+                   dims=dict(dims, B=B, NB=1, tmax=tmax, notes=notes, WG=WG, chunk_tiles=ch, tc=False, ksplit=False, kernel='small',
+                             nch=nch, kv_stages=kvst, ring_slots=nslot), roles=roles)
+
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
           grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None):
     """See the module docstring. `res`: name -> (shape, dtype) as the kernel sees them (batched
@@ -366,6 +501,10 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     for o in outputs:
         if o not in (env['$logit'], env['$next']):
             raise NotImplementedError(f'output {o}: only {env["$logit"]} and {env["$next"]} are kept for the host')
+
+    tune = dict(tune or {})
+    if B <= 8 and not tune.get('large_kernel') and act_lo is None and not slab_tiles:
+        return _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, prompt_len, timing, grid, tune)
 
     # rows per slab (8 per batch tile): the operand tiles of a slab live in shared memory next to the
     # weight ring, the K/V tiles and the LayerNorm staging; the largest slab that still leaves three
@@ -471,42 +610,11 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_ATT_UNROLL=int(tune.get('att_unroll', 4)))
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
-    emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
-    params, sig = [], []
-    for name, (shape, dt) in res.items():
-        em = name in emitted
-        params.append((name, dt, em))
-        sig.append(f'{"" if em else "const "}{CTYPE[dt]}* __restrict__ R_{name}')
-    if prompt_len and fb:
-        params += [('prompt', 'i32', False), ('plen', 'i32', False)]
-        sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
-    R = {k: 'R_' + v for k, v in roles.items()}
-    step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
-                                'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT',
-                                'const unsigned char* __restrict__ TM', 'int nsteps'])
-    fill = [f'a.x = {R["x"]}; a.t = {R["t"]};']
-    for k in ('wte', 'wpe', 'ln1w', 'ln1b', 'qkvb', 'ob', 'ln2w', 'ln2b', 'fcb', 'pb', 'lnfw', 'lnfb'):
-        fill.append(f'a.{k} = {R[k]};')
-    fill.append(f'a.keys = {R["keys"]}; a.vals = {R["vals"]};')
-    if fb:
-        fill.append(f'a.x_out = {R["x"]}; a.t_out = {R["t"]};')
-    else:
-        fill.append('a.x_out = 0; a.t_out = 0;')
-    fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
-    fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.TM = TM; a.nsteps = nsteps;')
-    pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
-    pack_params = [roles[k] for k in pack_roles]
-    pack_sig = ', '.join([f'const unsigned short* __restrict__ R_{roles[k]}' for k in pack_roles]
-                         + ['unsigned char* __restrict__ WP', 'const int* __restrict__ PT'])
-    pack_fill = ' '.join(f'p.{k} = R_{roles[k]};' for k in pack_roles) + ' p.WP = WP; p.PT = PT;'
-    tail = (f'\nextern "C" __global__ void __launch_bounds__(NTHREADS, 1) vesta_step({step_sig}) {{\n'
-            f'    Args a; {" ".join(fill)}\n    step_body(a);\n}}\n'
-            f'\nextern "C" __global__ void vesta_pack({pack_sig}) {{\n'
-            f'    PackArgs p; {pack_fill}\n    pack_body(p);\n}}\n')
-    src = head + KERNEL_TEXT.read_text(encoding='utf-8') + tail
+    params, pack_params, tail = _entry_points(res, roles, fb, prompt_len)
+    src = head + COMMON_TEXT.read_text(encoding='utf-8') + KERNEL_TEXT.read_text(encoding='utf-8') + tail
 
     q = env
     ln_how = ('each row normalised once on one warp of the grid, operand tiles through global memory (+1 barrier)' if ln_dist
