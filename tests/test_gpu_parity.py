@@ -435,11 +435,42 @@ def test_out_of_range_inputs_are_refused_not_executed():
     assert torch.equal(before, m.logits())        # nothing ran
     with pytest.raises(RuntimeError):
         m.k.check()
-    m.k.bar.zero_(); m.t.fill_(1); m.x.fill_(TINY.N)      # token id == vocabulary size
+    m.k.clear_status(); m.t.fill_(1); m.x.fill_(TINY.N)      # token id == vocabulary size
     m.step()
     assert 'out of range' in str(m.k.status())
-    m.k.bar.zero_(); m.x.fill_(3); m.step()
+    m.k.clear_status(); m.x.fill_(3); m.step()
     assert m.k.status() == 0
+
+
+@pytest.mark.parametrize('batch', [2, 20])
+def test_a_wait_that_runs_out_ends_the_launch_with_a_status(batch):
+    """Every wait in the kernels is bounded. Here the grid barrier's counter is preset so that the first barrier can
+    never be satisfied and the limit is lowered to 2 ms: the launch must return, say where it gave up, leave its
+    counters clear, refuse further launches until the host clears the status, and then work again. (Both kernel
+    texts: at most eight sequences, and more.)"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY3
+    m, hf = model(TINY3, 11, 'rich', batch, 6, tune=dict(wait_ns=2_000_000))
+    m.reset(); m.x.fill_(3)
+    m.k.bar[32] = -(2 ** 31)                       # the counter all CTAs poll: never reaches generation x CTAs
+    m.step()
+    torch.cuda.synchronize()                        # returns: nothing hangs
+    assert 'grid barrier' in str(m.k.status())
+    bar = m.k.bar.cpu().numpy()
+    assert bar[2] == 1 and bar[1] == 0 and bar[3] == 0 and bar[32] == 0     # abort raised; arrivals, step flag and barrier counter left clear
+    with pytest.raises(RuntimeError):
+        m.k.check()
+    # sticky: the next launch does nothing at all
+    m.reset(); m.x.fill_(3)
+    m.step(); torch.cuda.synchronize()
+    assert int(m.t.cpu()[0]) == 0 and int(m.x.cpu()[0]) == 3
+    # cleared: a normal step, equal to the oracle's
+    m.k.clear_status()
+    m.step(); m.k.check()
+    W = O.upcast(hf.weights)
+    k0, v0 = O.new_cache(TINY3, 6)
+    ref, rn = O.step(TINY3, W, k0, v0, 3, 0)
+    assert np.abs(m.logits().cpu().numpy()[0] - ref).max() < TIGHT and int(m.t.cpu()[0]) == 1
 
 
 def test_kernel_api_mirrors_reference():

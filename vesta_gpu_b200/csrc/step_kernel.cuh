@@ -1090,8 +1090,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
             bad |= (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
             s_pos[b] = tb;
         }
+        // a launch that follows one that gave up does nothing: the abort flag stays until the host clears it
+        if (c.tid == 0 && ld_relaxed(a.bar + BAR_ABORT)) bad |= 2;
         if (__syncthreads_or(bad)) {
-            if (c.cta == 0 && c.tid == 0) atomicCAS(a.bar + BAR_STATUS, 0u, 0x900u);
+            if (c.cta == 0 && c.tid == 0) atomicCAS(a.bar + BAR_STATUS, 0u, 0x900u);      // (an earlier failure keeps its own code)
             return;
         }
     }

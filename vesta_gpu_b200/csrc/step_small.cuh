@@ -25,7 +25,7 @@
 // Every wait is bounded: on expiry the kernel records where in bar[0], raises the abort flag that all other waits
 // poll, and runs to its end.
 
-#define WN_MAX 4                        // most output tiles a CTA holds in a whole-fold contraction
+#define WN_MAX V_WN                     // most output tiles a CTA holds in a whole-fold contraction (at most 4)
 #define CH V_CH                         // tiles per ring slot
 #define SLOT_BYTES (CH * FRAG_BYTES)
 #define ATILE 512                       // operand tile: 16 fold indices x 8 sequences, per lane (head.x, head.y, rem.x, rem.y)
@@ -296,31 +296,44 @@ __device__ __forceinline__ void wait_full(u32& st, u32* bar, int cta, u32 slot, 
     if (!mbar_wait_slow(bar, full_bar(slot), parity, 0x300u, cta, reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_STOP))) st |= ST_DEAD;
 }
 
-// Whole fold, `nj` output tiles (stream order: fold tile major), operand tiles at V_SM_ACT. Warp w takes the fold
-// tiles w, w + 8, ... and multiplies each into all nj output tiles; the sums of the eight warps are left in shared
-// memory (V_SM_RED: [warp][output tile][lane] x 4 floats) for the epilogue, which runs after a block-wide sync.
-__device__ __noinline__ u32 gemm_whole_fold(u32 st, u32* bar, int cta, int nj, int rpc) {
+// Whole fold, NJ output tiles (stream order: fold tile major), operand tiles at V_SM_ACT. Warp w takes the fold
+// tiles w, w + 8, ... and multiplies each into all NJ output tiles, alternating between two sets of accumulators
+// (short dependency chains); the sums of the eight warps are left in shared memory (V_SM_RED: [warp][output tile]
+// [lane] x 4 floats) for the epilogue, which runs after a block-wide sync. One instance per NJ: the loops are
+// straight-line code for the CTA's own count.
+template <int NJ>
+__device__ __noinline__ u32 gemm_whole_fold_n(u32 st, u32* bar, int cta, int rpc) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    float acc[WN_MAX][4], lo[WN_MAX][4];
+    float acc[2][NJ][4], lo[2][NJ][4];
 #pragma unroll
-    for (int j = 0; j < WN_MAX; j++)
+    for (int s = 0; s < 2; s++)
 #pragma unroll
-        for (int i = 0; i < 4; i++) { acc[j][i] = 0.f; lo[j][i] = 0.f; }
+        for (int j = 0; j < NJ; j++)
+#pragma unroll
+            for (int i = 0; i < 4; i++) { acc[s][j][i] = 0.f; lo[s][j][i] = 0.f; }
     const unsigned char* actl = smem + V_SM_ACT + lane * 16;
 #pragma unroll 1
     for (int r0 = 0; r0 < KT_D; r0 += rpc) {
         const u32 chunk = st & ~ST_DEAD, slot = chunk % V_NSLOT, use = chunk / V_NSLOT;
         wait_full(st, bar, cta, slot, use & 1u);
-        TRACE(53);
         const unsigned char* tiles = smem + V_SM_RING + slot * SLOT_BYTES + lane * 16;
         const int nr = (st & ST_DEAD) ? 0 : min(rpc, KT_D - r0);
-#pragma unroll 2
-        for (int r = warp; r < nr; r += NW) {
-            const uint4 b = lds16(actl + (r0 + r) * ATILE);
-            const unsigned char* tp = tiles + (r * nj) * FRAG_BYTES;
+        int r = warp;
+#pragma unroll 1
+        for (; r + NW < nr; r += 2 * NW) {
+            const uint4 b0 = lds16(actl + (r0 + r) * ATILE), b1 = lds16(actl + (r0 + r + NW) * ATILE);
+            const unsigned char* tp = tiles + (r * NJ) * FRAG_BYTES;
 #pragma unroll
-            for (int j = 0; j < WN_MAX; j++)
-                if (j < nj) mma_hl(acc[j], lo[j], lds16(tp + j * FRAG_BYTES), b);
+            for (int j = 0; j < NJ; j++) {
+                mma_hl(acc[0][j], lo[0][j], lds16(tp + j * FRAG_BYTES), b0);
+                mma_hl(acc[1][j], lo[1][j], lds16(tp + (NW * NJ + j) * FRAG_BYTES), b1);
+            }
+        }
+        if (r < nr) {
+            const uint4 b0 = lds16(actl + (r0 + r) * ATILE);
+            const unsigned char* tp = tiles + (r * NJ) * FRAG_BYTES;
+#pragma unroll
+            for (int j = 0; j < NJ; j++) mma_hl(acc[0][j], lo[0][j], lds16(tp + j * FRAG_BYTES), b0);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(slot));
@@ -328,11 +341,26 @@ __device__ __noinline__ u32 gemm_whole_fold(u32 st, u32* bar, int cta, int nj, i
     }
     float* red = reinterpret_cast<float*>(smem + V_SM_RED);
 #pragma unroll
-    for (int j = 0; j < WN_MAX; j++)
-        if (j < nj)
-            *reinterpret_cast<float4*>(red + ((warp * WN_MAX + j) * 32 + lane) * 4) =
-                make_float4(acc[j][0] + lo[j][0], acc[j][1] + lo[j][1], acc[j][2] + lo[j][2], acc[j][3] + lo[j][3]);
+    for (int j = 0; j < NJ; j++)
+        *reinterpret_cast<float4*>(red + ((warp * WN_MAX + j) * 32 + lane) * 4) =
+            make_float4((acc[0][j][0] + lo[0][j][0]) + (acc[1][j][0] + lo[1][j][0]), (acc[0][j][1] + lo[0][j][1]) + (acc[1][j][1] + lo[1][j][1]),
+                        (acc[0][j][2] + lo[0][j][2]) + (acc[1][j][2] + lo[1][j][2]), (acc[0][j][3] + lo[0][j][3]) + (acc[1][j][3] + lo[1][j][3]));
     return st;
+}
+__device__ __forceinline__ u32 gemm_whole_fold(u32 st, u32* bar, int cta, int nj, int rpc) {
+    switch (nj) {
+        case 1: return gemm_whole_fold_n<1>(st, bar, cta, rpc);
+#if WN_MAX >= 2
+        case 2: return gemm_whole_fold_n<2>(st, bar, cta, rpc);
+#endif
+#if WN_MAX >= 3
+        case 3: return gemm_whole_fold_n<3>(st, bar, cta, rpc);
+#endif
+#if WN_MAX >= 4
+        case 4: return gemm_whole_fold_n<4>(st, bar, cta, rpc);
+#endif
+        default: return st;                     // the placement gives a CTA at most WN_MAX output tiles
+    }
 }
 // complete sum of output `o` (tile o / 128, element (o % 128) of the accumulator layout: lane * 4 + register)
 __device__ __forceinline__ float whole_fold_sum(const float* red, int o) {
@@ -343,14 +371,16 @@ __device__ __forceinline__ float whole_fold_sum(const float* red, int o) {
     return v;
 }
 
-// A slice of `us` fold tiles for `nunits` output tiles (stream order: output tile major). Warp w takes the output
-// tiles w, w + 8, ... of every ring slot; the sums are added to zt[b][unit * 16 + ...] with fp32 atomics (the
-// other slices of the fold are other CTAs'). The operand tiles of the slice are read once, into registers.
-__device__ __noinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, float* __restrict__ zt) {
+// A slice of US fold tiles for `nunits` output tiles (stream order: output tile major). Warp w takes the output
+// tiles w, w + 8, ... of every ring slot, two at a time (independent chains of products); the sums are added to
+// zt[b][unit * 16 + ...] with fp32 atomics (the other slices of the fold are other CTAs'). The operand tiles of
+// the slice are read once, into registers. One instance per US.
+template <int US>
+__device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nunits, int upc, const unsigned char* act, float* __restrict__ zt) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    uint4 bop[UMAX];
+    uint4 bop[US];
 #pragma unroll
-    for (int r = 0; r < UMAX; r++) bop[r] = (r < us) ? lds16(act + r * ATILE + lane * 16) : make_uint4(0, 0, 0, 0);
+    for (int r = 0; r < US; r++) bop[r] = lds16(act + r * ATILE + lane * 16);
     const int g = lane >> 2, t = lane & 3;
     float* zl = zt + (size_t)(2 * t) * V_D + g;
 #pragma unroll 1
@@ -362,18 +392,16 @@ __device__ __noinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunit
         const int nu = (st & ST_DEAD) ? 0 : min(upc, nunits - u0);
 #pragma unroll 1
         for (int u = warp; u < nu; u += 2 * NW) {
-            // two output tiles at a time: their chains of products are independent
             const bool two = u + NW < nu;
             float a0[4] = {0.f, 0.f, 0.f, 0.f}, l0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f}, l1[4] = {0.f, 0.f, 0.f, 0.f};
-            const unsigned char* tp0 = tiles + (u * us) * FRAG_BYTES;
-            const unsigned char* tp1 = tiles + ((two ? u + NW : u) * us) * FRAG_BYTES;
+            const unsigned char* tp0 = tiles + (u * US) * FRAG_BYTES;
+            const unsigned char* tp1 = tiles + ((two ? u + NW : u) * US) * FRAG_BYTES;
 #pragma unroll
-            for (int r = 0; r < UMAX; r++)
-                if (r < us) {
-                    const uint4 w0 = lds16(tp0 + r * FRAG_BYTES), w1 = lds16(tp1 + r * FRAG_BYTES);
-                    mma_hl(a0, l0, w0, bop[r]);
-                    mma_hl(a1, l1, w1, bop[r]);
-                }
+            for (int r = 0; r < US; r++) {
+                const uint4 w0 = lds16(tp0 + r * FRAG_BYTES), w1 = lds16(tp1 + r * FRAG_BYTES);
+                mma_hl(a0, l0, w0, bop[r]);
+                mma_hl(a1, l1, w1, bop[r]);
+            }
             float* o0 = zl + (u0 + u) * 16;
             if (2 * t < V_B) { red_add(o0, a0[0] + l0[0]); red_add(o0 + 8, a0[2] + l0[2]); }
             if (2 * t + 1 < V_B) { red_add(o0 + V_D, a0[1] + l0[1]); red_add(o0 + V_D + 8, a0[3] + l0[3]); }
@@ -389,6 +417,33 @@ __device__ __noinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunit
     }
     return st;
 }
+__device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, float* zt) {
+    switch (us) {
+        case 1: return gemm_fold_slice_n<1>(st, bar, cta, nunits, upc, act, zt);
+#if UMAX >= 2
+        case 2: return gemm_fold_slice_n<2>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 3
+        case 3: return gemm_fold_slice_n<3>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 4
+        case 4: return gemm_fold_slice_n<4>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 5
+        case 5: return gemm_fold_slice_n<5>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 6
+        case 6: return gemm_fold_slice_n<6>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 7
+        case 7: return gemm_fold_slice_n<7>(st, bar, cta, nunits, upc, act, zt);
+#endif
+#if UMAX >= 8
+        case 8: return gemm_fold_slice_n<8>(st, bar, cta, nunits, upc, act, zt);
+#endif
+        default: return st;                     // the lowering refuses placements with deeper slices
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 // activations -> operand tiles in shared memory
@@ -402,18 +457,40 @@ __device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, flo
     base[(2 + reg) * 2 + half] = f2h(v - h2f(hi));
 }
 
-// Parameters of the next LayerNorm phase into shared memory: gain, shift, the bias added when the following
-// combined vector is started (each V_D halves), and the bias of this CTA's whole-fold output tiles.
+// Parameters of the next LayerNorm phase into shared memory: gain and shift as fp32 (2 x V_D floats: the conversion
+// happens here, in the shadow of the grid barrier, not in the LayerNorm pass), then as halves the bias added when the
+// following combined vector is started (V_D) and the bias of this CTA's whole-fold output tiles. Warp 0 converts
+// nothing: its first thread polls the barrier.
+#define PRM_GAIN 0
+#define PRM_SHIFT (V_D * 4)
+#define PRM_INIT (V_D * 8)
+#define PRM_TILE (V_D * 10)
 __device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* gb, const u16* ib, const u16* tb, int tiles) {
-    u16* prm = reinterpret_cast<u16*>(smem + V_SM_PRM);
-    const int per = V_D / 8;                       // 16-byte pieces per vector
+    unsigned char* prm = smem + V_SM_PRM;
+    const int per = V_D / 8;                       // 16-byte pieces per vector of halves
+    if (ib) {
 #pragma unroll 1
-    for (int i = c.tid; i < 3 * per; i += NCONS) {
-        const int v = i / per, q = i - v * per;
-        const u16* src = v == 0 ? gw : (v == 1 ? gb : ib);
-        if (src) cp16(prm + v * V_D + q * 8, src + q * 8);
+        for (int i = c.tid; i < per; i += NCONS) cp16(prm + PRM_INIT + i * 16, ib + i * 8);
     }
-    if (tb && c.tid < tiles * 2) cp16(prm + 3 * V_D + c.tid * 8, tb + c.tid * 8);
+    if (tb && c.tid < tiles * 2) cp16(prm + PRM_TILE + c.tid * 16, tb + c.tid * 8);
+#pragma unroll 1
+    for (int i = c.tid - 32; i < 2 * per; i += NCONS - 32) {
+        if (i < 0) continue;
+        const int v = i >= per, q = v ? i - per : i;
+        const uint4 h = __ldg(reinterpret_cast<const uint4*>((v ? gb : gw) + q * 8));
+        float4* dst = reinterpret_cast<float4*>(prm + (v ? PRM_SHIFT : PRM_GAIN) + q * 32);
+        dst[0] = make_float4(h_lo(h.x), h_hi(h.x), h_lo(h.y), h_hi(h.y));
+        dst[1] = make_float4(h_lo(h.z), h_hi(h.z), h_lo(h.w), h_hi(h.w));
+    }
+}
+
+// fp32 -> fp16 head + fp16 remainder of two values. The head is the value with its low 13 mantissa bits cleared (so
+// its conversion to fp16 is exact in the normal range and needs no conversion back), the remainder what is left,
+// rounded to fp16: together 21 to 22 bits of the value.
+__device__ __forceinline__ void split_h2(float x, float y, u32& hi, u32& lo) {
+    const float xh = __uint_as_float(__float_as_uint(x) & 0xFFFFE000u), yh = __uint_as_float(__float_as_uint(y) & 0xFFFFE000u);
+    hi = pack_h2(xh, yh);
+    lo = pack_h2(x - xh, y - yh);
 }
 
 // LayerNorm of the rows of z (global, fp32, row stride V_D) into the operand tiles; gain and shift come from the
@@ -430,7 +507,7 @@ __device__ __forceinline__ void fetch_params(Ctx& c, const u16* gw, const u16* g
 __device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restrict__ z, float* __restrict__ init) {
     unsigned char* act = smem + V_SM_ACT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const u16* prm = reinterpret_cast<const u16*>(smem + V_SM_PRM);
+    const unsigned char* prm = smem + V_SM_PRM;
     float* stat = reinterpret_cast<float*>(smem + V_SM_MISC + MISC_STAT);
     const int u = lane >> 2, t = lane & 3;
     const int rb = warp / LN_WPR, wi = warp % LN_WPR;
@@ -484,16 +561,16 @@ __device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restric
     for (int i = 0; i < LNI; i++) {
         const int kt = u + 8 * (wi + LN_WPR * i), k = kt * 16 + 2 * t;
         if (live && kt < KT_D) {
-            const u32 w0 = *reinterpret_cast<const u32*>(prm + k), w1 = *reinterpret_cast<const u32*>(prm + k + 8);
-            const u32 s0 = *reinterpret_cast<const u32*>(prm + V_D + k), s1 = *reinterpret_cast<const u32*>(prm + V_D + k + 8);
-            const float o0 = (v0[i].x - mean) * rs * h_lo(w0) + h_lo(s0), o1 = (v0[i].y - mean) * rs * h_hi(w0) + h_hi(s0);
-            const float o2 = (v1[i].x - mean) * rs * h_lo(w1) + h_lo(s1), o3 = (v1[i].y - mean) * rs * h_hi(w1) + h_hi(s1);
+            const float2 w0 = *reinterpret_cast<const float2*>(prm + PRM_GAIN + k * 4), w1 = *reinterpret_cast<const float2*>(prm + PRM_GAIN + (k + 8) * 4);
+            const float2 s0 = *reinterpret_cast<const float2*>(prm + PRM_SHIFT + k * 4), s1 = *reinterpret_cast<const float2*>(prm + PRM_SHIFT + (k + 8) * 4);
+            const float o0 = (v0[i].x - mean) * rs * w0.x + s0.x, o1 = (v0[i].y - mean) * rs * w0.y + s0.y;
+            const float o2 = (v1[i].x - mean) * rs * w1.x + s1.x, o3 = (v1[i].y - mean) * rs * w1.y + s1.y;
             uint4 out;
-            out.x = pack_h2(o0, o1); out.y = pack_h2(o2, o3);
-            out.z = pack_h2(o0 - h_lo(out.x), o1 - h_hi(out.x)); out.w = pack_h2(o2 - h_lo(out.y), o3 - h_hi(out.y));
+            split_h2(o0, o1, out.x, out.z);
+            split_h2(o2, o3, out.y, out.w);
             *reinterpret_cast<uint4*>(dst + kt * ATILE) = out;
             if (init && ((KT_D <= V_MAXGRID) ? (kt == cta) : ((kt % ncta) == cta))) {
-                const u32 i0 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k), i1 = *reinterpret_cast<const u32*>(prm + 2 * V_D + k + 8);
+                const u32 i0 = *reinterpret_cast<const u32*>(prm + PRM_INIT + k * 2), i1 = *reinterpret_cast<const u32*>(prm + PRM_INIT + (k + 8) * 2);
                 float* o = init + (size_t)rb * V_D + k;
                 red_add(o, v0[i].x + h_lo(i0)); red_add(o + 1, v0[i].y + h_hi(i0));
                 red_add(o + 8, v1[i].x + h_lo(i1)); red_add(o + 9, v1[i].y + h_hi(i1));
@@ -541,24 +618,30 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // x 16 positions), B = the weights, head and remainder again in columns 0 and 1. Result per item: (running max,
 // sum, unnormalised o[V_E]) in global memory; the projection merges the chunks of a (sequence, head).
 // ---------------------------------------------------------------------------------------------
-// B operand of the scores: the query of (b, h), head in column 0 (lanes with g == 0), remainder in column 1 (g == 1)
-__device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* __restrict__ qbuf, int b, int h, int g, int t) {
-    const float* qp = qbuf + (size_t)b * V_D + h * V_E;
-    const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
-#pragma unroll
-    for (int kq = 0; kq < V_E / 16; kq++) {
-        bq[kq][0] = 0; bq[kq][1] = 0;
-        if (g < 2) {
-            const float2 a0 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
-            const float2 a1 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
-            const u32 h0 = pack_h2(a0.x * sc, a0.y * sc), h1 = pack_h2(a1.x * sc, a1.y * sc);
-            bq[kq][0] = g == 0 ? h0 : pack_h2(a0.x * sc - h_lo(h0), a0.y * sc - h_hi(h0));
-            bq[kq][1] = g == 0 ? h1 : pack_h2(a1.x * sc - h_lo(h1), a1.y * sc - h_hi(h1));
-        }
+// B operand of the scores: the query of (b, h), its fp16 head in column 0 (lanes with g == 0) and its fp16 remainder in
+// column 1 (g == 1). The QKV epilogue stores the query in exactly this form (scaled where the divisor is a power of
+// two): per (sequence, head) 128 halves ordered [column][t][k step][register][half], so a lane reads its eight
+// registers with two 16-byte loads and no conversion.
+__device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const u32* __restrict__ qop, int b, int h, int g, int t) {
+    uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+    if (g < 2) {
+        const uint4* p = reinterpret_cast<const uint4*>(qop + (size_t)(b * V_H + h) * 64 + g * 32 + t * 8);
+        x = __ldcg(p); y = __ldcg(p + 1);
     }
+    bq[0][0] = x.x; bq[0][1] = x.y; bq[1][0] = x.z; bq[1][1] = x.w;
+    bq[2][0] = y.x; bq[2][1] = y.y; bq[3][0] = y.z; bq[3][1] = y.w;
+}
+// one element of the query into that form: column 0 gets the fp16 head, column 1 the fp16 remainder
+__device__ __forceinline__ void q_store(u16* __restrict__ qop16, int b, int jx, float v) {
+    const float vs = V_SCALE_IS_POW2 ? v * (1.0f / V_SCALE) : v;
+    const int h = jx / V_E, e = jx - h * V_E, kq = e >> 4, kk = e & 15;
+    u16* q = qop16 + (size_t)(b * V_H + h) * 128 + ((kk & 7) >> 1) * 16 + kq * 4 + (kk >> 3) * 2 + (kk & 1);
+    const u16 hi = f2h(vs);
+    q[0] = hi;
+    q[64] = f2h(vs - h2f(hi));
 }
 
-__device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
+__device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const u32* __restrict__ qbuf,
                                                 float* __restrict__ part, int l, const int* s_pos) {
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
@@ -843,10 +926,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
     unsigned char* act = smem + V_SM_ACT;
     unsigned char* gact = smem + V_SM_GACT;
     float* red = reinterpret_cast<float*>(smem + V_SM_RED);
-    const u16* prm = reinterpret_cast<const u16*>(smem + V_SM_PRM);
+    const u16* tile_bias = reinterpret_cast<const u16*>(smem + V_SM_PRM + PRM_TILE);
     u64* wbest = reinterpret_cast<u64*>(smem + V_SM_MISC + MISC_BEST);
     float* Z = a.S + V_OFF_Z;
-    float* qbuf = a.S + V_OFF_Q;
+    u32* qbuf = reinterpret_cast<u32*>(a.S + V_OFF_Q);
     float* part = a.S + V_OFF_PART;
     float* logit = a.S + V_OFF_LOGIT;
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
@@ -902,11 +985,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
             for (int o = c.tid; o < p.qkv_nj * 128; o += NCONS) {
                 const int r = o & 127, ln = r >> 2, i = r & 3;
                 const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), b = (ln & 3) * 2 + (i & 1);
-                const float v = whole_fold_sum(red, o) + h2f(prm[3 * V_D + (o >> 7) * 16 + j_in]);
+                const float v = whole_fold_sum(red, o) + h2f(tile_bias[(o >> 7) * 16 + j_in]);
                 if (b < V_B) {
                     // q to scratch, K and V rounded to fp16 into the cache at t
                     const int jx = (p.qkv_j0 + (o >> 7)) * 16 + j_in;
-                    if (jx < V_D) qbuf[(size_t)b * V_D + jx] = v;
+                    if (jx < V_D) q_store(reinterpret_cast<u16*>(qbuf), b, jx, v);
                     else if (s_pos[b] >= 0) {
                         const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
                         if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
@@ -962,7 +1045,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
             for (int o = c.tid; o < p.fc_nj * 128; o += NCONS) {
                 const int r = o & 127, ln = r >> 2, i = r & 3;
                 const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), b = (ln & 3) * 2 + (i & 1);
-                const float v = whole_fold_sum(red, o) + h2f(prm[3 * V_D + (o >> 7) * 16 + j_in]);
+                const float v = whole_fold_sum(red, o) + h2f(tile_bias[(o >> 7) * 16 + j_in]);
                 // g = gelu(u) -> operand tiles of the MLP projection: fold index = tile * 16 + j_in
                 if (b < V_B) act_store1(gact, b, (o >> 7) * 16 + j_in, V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))));
             }

@@ -245,6 +245,13 @@ class Kernel:
         if s:
             raise RuntimeError(f'vesta_step gave up: {s}')
 
+    def clear_status(self):
+        """forget a refused step or an abandoned wait: status word, abort flag and the barrier counters back to zero.
+        Both are sticky: until this is called every further launch returns at once without touching x, t or the cache
+        (a refused step never wrote anything; a launch in which a wait ran out may have written part of a step, so
+        reset or reload the decode state before going on)."""
+        self.bar.zero_()
+
     def __del__(self):
         try:
             if getattr(self, '_bound', None):

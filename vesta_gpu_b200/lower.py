@@ -363,16 +363,19 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     for QKV and FC, whole output tiles per warp for the projections, attention tiles listed once per step)"""
     D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
     KT_D = D // 16
+    nw = int(tune.get('warps', NW))                 # consumer warps per CTA
     rec, tiles, notes = place_step(dims, grid, False)
+    wn = max(int(rec[:, 3].max()), int(rec[:, 9].max()), 1)              # most output tiles of a whole-fold contraction per CTA
     umax = max(int(rec[:, 7].max()), int(rec[:, 9].max()), 1)            # deepest fold slice of a projection unit
-    if umax > CHUNK_TILES:
-        raise NotImplementedError('placement: a projection unit exceeds a ring slot')
-    kvst = int(tune.get('kv_stages', 3 if B * H > grid else 2))
+    if umax > 8:
+        raise NotImplementedError('placement: a projection unit is deeper than eight fold tiles')
+    kvst = int(tune.get('kv_stages', 2))
 
-    # position chunks per (sequence, head): rounds of the grid x (positions per chunk + the fixed cost of an item,
-    # about one and a half tiles of 128 positions), at a typical context of tmax / 2
+    # position chunks per (sequence, head), from the measured costs of the attention phase (cycles): an item costs a fixed
+    # 1,500 plus 1,300 per tile of 128 positions, a CTA runs its items one after the other, and the projection that
+    # follows merges the chunks of a pair at about 80 per chunk; sized for a full cache
     def att_cost(k):
-        return math.ceil(B * H * k / grid) * (max(tmax // 2, 1) / k + 192)
+        return math.ceil(B * H * k / grid) * (1500 + 1300 * math.ceil(math.ceil(tmax / k) / 128)) + 80 * k
     nch = int(tune.get('nch', min(range(1, 17), key=lambda k: (att_cost(k), k))))
     att_items = B * H * nch
     maxtl = math.ceil(att_items / grid) * math.ceil(math.ceil(tmax / nch) / 128)
@@ -388,9 +391,9 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     # shared memory: [weight ring | K/V stages | operand tiles | GELU operand tiles | partial sums | parameters | misc | barriers]
     ch = CHUNK_TILES
     budget = SMEM_LIMIT - (8192 if timing else 0)
-    prm_bytes = (3 * D + WN_MAX * 16) * 2
-    misc_bytes = 2 * NW * (E + 2) * 4 + 8 * NW * 8 + 32 + 512 + 16 + maxtl * 16
-    fixed = kvst * 32768 + KT_D * 512 + WN_MAX * 512 + NW * WN_MAX * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
+    prm_bytes = 10 * D + wn * 32               # gain and shift as fp32, two bias vectors as fp16
+    misc_bytes = 2 * nw * (E + 2) * 4 + 8 * nw * 8 + 32 + 512 + 16 + maxtl * 16
+    fixed = kvst * 32768 + KT_D * 512 + wn * 512 + nw * wn * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
     nslot = min((budget - fixed - 2 * kvst * 8 - 64) // (ch * 512 + 16), 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget')
@@ -398,17 +401,17 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     sm_kv = sm_ring + nslot * ch * 512
     sm_act = sm_kv + kvst * 32768
     sm_gact = sm_act + KT_D * 512
-    sm_red = sm_gact + WN_MAX * 512
-    sm_prm = sm_red + NW * WN_MAX * 512
+    sm_red = sm_gact + wn * 512
+    sm_prm = sm_red + nw * wn * 512
     sm_misc = sm_prm + _up(prm_bytes, 16)
     sm_bars = sm_misc + _up(misc_bytes, 16)
     shared = sm_bars + (2 * nslot + 2 * kvst) * 8
 
     scale = dims['scale']
-    defs = dict(V_NW=NW, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
+    defs = dict(V_NW=nw, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
                 V_EPS=_f32(dims['eps']), V_SCALE=_f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5),
                 V_GELU_A=_f32(dims['gelu'][0]), V_GELU_B=_f32(dims['gelu'][1]), V_GELU_C=_f32(dims['gelu'][2]),
-                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
+                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_WN=wn, V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0,
                 V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q, V_OFF_PART=off_part, V_OFF_BEST=off_best,
@@ -420,12 +423,12 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     src = head + COMMON_TEXT.read_text(encoding='utf-8') + SMALL_TEXT.read_text(encoding='utf-8') + tail
 
     q = env
-    ln_how = (f'every CTA recomputes: {NW // (1 if B <= 1 else 2 if B <= 2 else 4 if B <= 4 else 8)} warp(s) per row, the row in registers, '
+    ln_how = (f'every CTA recomputes: {nw // (1 if B <= 1 else 2 if B <= 2 else 4 if B <= 4 else 8)} warp(s) per row, the row in registers, '
               'into mma operand tiles (fp16 head + fp16 remainder)')
     plan = [
         (f'{q["$z0"]} (embed)', 'grid-stride, then barrier'),
         (f'{q["$m1"]}, {q["$v1"]}, {q["$a"]} (LN1)', ln_how),
-        (f'{q["$qkv"]} + emits', f'whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA, the fold split over the 8 warps; bias, q, K/V emit in the epilogue'),
+        (f'{q["$qkv"]} + emits', f'whole fold, {min(rec[:, 3])}-{max(rec[:, 3])} output tiles per CTA, the fold split over the {nw} warps; bias, q, K/V emit in the epilogue'),
         (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)',
          f'one item per (sequence, head, 1/{nch} of the positions), dealt round-robin over the CTAs, cut into tiles of 128 positions once per step; '
          f'K/V tiles by TMA ({kvst} stages), online softmax in registers, merged by the projection'),
@@ -440,8 +443,8 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] + ['logits', 'finish']
     return Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                    barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
-                   block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
-                   dims=dict(dims, B=B, NB=1, tmax=tmax, notes=notes, WG=WG, chunk_tiles=ch, tc=False, ksplit=False, kernel='small',
+                   block=(nw + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
+                   dims=dict(dims, B=B, NB=1, tmax=tmax, notes=notes, WG=WG, chunk_tiles=ch, tc=False, ksplit=False, kernel='small', warps=nw,
                              nch=nch, kv_stages=kvst, ring_slots=nslot), roles=roles)
 
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
