@@ -455,7 +455,8 @@ def test_a_wait_that_runs_out_ends_the_launch_with_a_status(batch):
     m.k.bar[32] = -(2 ** 31)                       # the counter all CTAs poll: never reaches generation x CTAs
     m.step()
     torch.cuda.synchronize()                        # returns: nothing hangs
-    assert 'grid barrier' in str(m.k.status())
+    # the consumers' barrier wait and the producer thread's wait for them run out at about the same time: either may report
+    assert any(w in str(m.k.status()) for w in ('grid barrier', 'producer')), m.k.status()
     bar = m.k.bar.cpu().numpy()
     assert bar[2] == 1 and bar[1] == 0 and bar[3] == 0 and bar[32] == 0     # abort raised; arrivals, step flag and barrier counter left clear
     with pytest.raises(RuntimeError):

@@ -28,7 +28,8 @@
 #define WN_MAX V_WN                     // most output tiles a CTA holds in a whole-fold contraction (at most 4)
 #define CH V_CH                         // tiles per ring slot
 #define SLOT_BYTES (CH * FRAG_BYTES)
-#define ATILE 512                       // operand tile: 16 fold indices x 8 sequences, per lane (head.x, head.y, rem.x, rem.y)
+#define ATILE 576                       // operand tiles (16 fold indices x 8 sequences; per lane head.x, head.y, rem.x, rem.y = 512 B) are
+                                        // 576 B apart: the LayerNorm's 16-byte stores to eight tiles at once then spread over all banks
 #define UMAX V_UMAX                     // deepest fold slice of a projection unit (tiles)
 
 #define PT_STRIDE 16
@@ -91,7 +92,10 @@ struct Plan {
     int rpc_qkv, rpc_fc, upc_proj, upc_p2;       // fold rows / units per ring slot
 };
 // fold rows of a whole-fold contraction per ring slot: whole waves of eight rows (one per warp) where they fit
-__device__ __forceinline__ int rows_per_slot(int nj) { const int k = CH / max(nj, 1); return k >= 8 ? (k & ~7) : k; }
+__device__ __forceinline__ int rows_per_slot(int nj) {
+    const int k = CH / max(nj, 1), w = k & ~7;
+    return (w * max(nj, 1) * 8 >= CH * 7) ? w : k;      // unless that leaves more than an eighth of the slot empty
+}
 __device__ __forceinline__ Plan load_plan(const int* __restrict__ P) {
     Plan p;
     p.qkv_j0 = P[PT_QKV_J0]; p.qkv_nj = P[PT_QKV_NJ]; p.proj_j0 = P[PT_PROJ_J0]; p.proj_nj = P[PT_PROJ_NJ];
@@ -452,7 +456,7 @@ __device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nu
 __device__ __forceinline__ void act_store1(unsigned char* act, int b, int k, float v) {
     const u16 hi = f2h(v);
     const int kt = k >> 4, kk = k & 15, reg = kk >> 3, t = (kk & 7) >> 1, half = kk & 1;
-    u16* base = reinterpret_cast<u16*>(act + (kt * 32 + b * 4 + t) * 16);
+    u16* base = reinterpret_cast<u16*>(act + kt * ATILE + (b * 4 + t) * 16);
     base[reg * 2 + half] = hi;
     base[(2 + reg) * 2 + half] = f2h(v - h2f(hi));
 }

@@ -369,7 +369,6 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     umax = max(int(rec[:, 7].max()), int(rec[:, 9].max()), 1)            # deepest fold slice of a projection unit
     if umax > 8:
         raise NotImplementedError('placement: a projection unit is deeper than eight fold tiles')
-    kvst = int(tune.get('kv_stages', 2))
 
     # position chunks per (sequence, head), from the measured costs of the attention phase (cycles): an item costs a fixed
     # 1,500 plus 1,300 per tile of 128 positions, a CTA runs its items one after the other, and the projection that
@@ -379,6 +378,8 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     nch = int(tune.get('nch', min(range(1, 17), key=lambda k: (att_cost(k), k))))
     att_items = B * H * nch
     maxtl = math.ceil(att_items / grid) * math.ceil(math.ceil(tmax / nch) / 128)
+    # K/V stages of 32 KB: two tiles in flight where a CTA has several per layer, one (and a deeper weight ring) otherwise
+    kvst = int(tune.get('kv_stages', 2 if maxtl > 1 else 1))
 
     off_logit, off_next = 0, _up(B * N)
     off_z = _up(off_next + B)
@@ -393,15 +394,15 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     budget = SMEM_LIMIT - (8192 if timing else 0)
     prm_bytes = 10 * D + wn * 32               # gain and shift as fp32, two bias vectors as fp16
     misc_bytes = 2 * nw * (E + 2) * 4 + 8 * nw * 8 + 32 + 512 + 16 + maxtl * 16
-    fixed = kvst * 32768 + KT_D * 512 + wn * 512 + nw * wn * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
+    fixed = kvst * 32768 + KT_D * 576 + _up(wn * 576, 128) + nw * wn * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
     nslot = min((budget - fixed - 2 * kvst * 8 - 64) // (ch * 512 + 16), 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget')
     sm_ring = 0
     sm_kv = sm_ring + nslot * ch * 512
     sm_act = sm_kv + kvst * 32768
-    sm_gact = sm_act + KT_D * 512
-    sm_red = sm_gact + wn * 512
+    sm_gact = sm_act + KT_D * 576
+    sm_red = sm_gact + _up(wn * 576, 128)
     sm_prm = sm_red + nw * wn * 512
     sm_misc = sm_prm + _up(prm_bytes, 16)
     sm_bars = sm_misc + _up(misc_bytes, 16)
