@@ -55,12 +55,6 @@ int vesta_launch_cooperative(void* function, unsigned grid, unsigned block, unsi
 int vesta_launch(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,
                  void* stream, void** args);
 
-/* Launch with thread-block clusters of `cluster` CTAs (cuLaunchKernelEx; sizes above 8 opt in to the
- * non-portable limit), cooperatively if `cooperative` is non-zero. No counterpart in the reference, whose
- * kernel does not use clusters. */
-int vesta_launch_cluster(void* function, unsigned grid, unsigned block, unsigned dynamic_smem, unsigned cluster,
-                         int cooperative, void* stream, void** args);
-
 /* vesta/launch.py:57-70 bind + launch: the argument list is fixed once (every kernel parameter
  * is a device pointer), after which a step costs one call. vesta_step_run launches `steps`
  * decode steps back to back on `stream` without returning to the caller in between. */

@@ -1,6 +1,6 @@
 """Shared helpers of the tests: golden fixtures and the comparison rules.
 
-Tolerances (BASELINE north_star): per-step logits within max-abs 2e-2 / relative 1e-2 of the
+Tolerances (the parity rule of this backend): per-step logits within max-abs 2e-2 / relative 1e-2 of the
 reference interpreter; greedy tokens identical wherever the reference top-1 margin exceeds 1e-2.
 The measured differences are around 4e-4, so the tests also hold a tighter bound that would catch
 a dropped bias or a wrong rounding point.

@@ -74,12 +74,15 @@ def test_gpt2_xl_shape():
     run_fixture('gpt2_xl_b1')
 
 
-@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample', 'gpt2_xl16_sample'])
+@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample', 'gpt2_xl16_sample', 'gpt2_cfg5_b64_sample', 'gpt2_cfg5_b256_sample',
+                                  'gpt2_cfg3_tail_sample', 'gpt2_xl1_sample'])
 def test_deep_context_samples_against_the_reference(name):
     """the large-batch paths at full model size against the reference interpreter: (cfg3) 64 sequences with 600
     positions in every cache: slabs, distributed LayerNorm, fold-slice MLP projection, several attention items of
-    five tiles per CTA, tcgen05 logits; (cfg5) a ragged batch of 32 with 64..512 positions per sequence and
-    per-sequence positions; (xl16) the XL shape at batch 16, context 300. Caches are seeded (synth.make_cache); the sampled sequences are compared over two
+    five tiles per CTA, tcgen05 logits; (cfg5) ragged batches of 32, 64 and 256 (what the batch-sharded benchmark runs per
+    GPU on 8, 4 and 1 GPUs) with 64..512 positions per sequence and per-sequence positions; (cfg3 tail) 64 sequences at
+    positions 1021..1023 of a 1024-row cache: the last K/V tile and the last position the cache holds; (xl16, xl1) the XL
+    shape at batch 16 and batch 1, context 300. Caches are seeded (synth.make_cache); the sampled sequences are compared over two
     teacher-forced steps."""
     from vesta_gpu_b200.shapes import SHAPES
     from vesta_gpu_b200.synth import make_cache
@@ -483,6 +486,12 @@ def test_kernel_api_mirrors_reference():
     for attr in ('mod', 'fn', 'smem', 'sms', 'grid', 'block', 'lowered', 'S', 'bar', 'TS', 'args', 'keep'):
         assert hasattr(k, attr), attr
     assert k.grid == k.sms == torch.cuda.get_device_properties(0).multi_processor_count
+    k2 = Kernel(m.low, block=256, device=0)               # the reference's default block size is accepted and means the lowered one
+    assert k2.block == m.low.block
+    with pytest.warns(RuntimeWarning):
+        Kernel(m.low, blocks_per_sm=4)
+    with pytest.raises(RuntimeError):
+        Kernel(m.low, block=128)
     assert k.view('logit').shape == (2, TINY.N) and k.view('next').shape == (2,)
     assert k.view('next').dtype == torch.float32
     R = dict(k.keep)

@@ -90,6 +90,11 @@ def test_gpt2_xl_batch16_sample():
     check_samples('gpt2_xl16_sample')
 
 
+def test_gpt2_xl_batch1_sample():
+    """the XL shape at batch 1, context 300"""
+    check_samples('gpt2_xl1_sample')
+
+
 def test_tie_goes_to_lowest_index():
     """gpt2.vst:81-82: next = min index whose logit equals the maximum"""
     logit = np.array([0.5, 2.0, 2.0, 1.0], np.float32)
@@ -109,7 +114,8 @@ def test_kv_cache_rounds_to_fp16():
     assert np.abs(a - b).max() < 1e-2 and not np.array_equal(a, b)
 
 
-@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample'])
+@pytest.mark.parametrize('name', ['gpt2_cfg3_sample', 'gpt2_cfg5_sample', 'gpt2_cfg5_b64_sample', 'gpt2_cfg5_b256_sample', 'gpt2_cfg3_tail_sample'])
 def test_gpt2_small_deep_context_samples(name):
-    """the batch-64 config at context 600 and a ragged batch of 32 with contexts 64..512"""
+    """the batch-64 config at context 600 and at the last positions of a 1024-row cache (1021..1023), ragged batches of
+    32, 64 and 256 with contexts 64..512"""
     check_samples(name)

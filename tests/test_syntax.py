@@ -73,7 +73,10 @@ def test_shipped_programs_match_generator():
         assert sum(isinstance(s, sx.StepFold) for s in prog) == 1
 
 
-REF_PROGRAM = os.path.join(os.environ.get('VESTA_REFERENCE', '/root/reference'), 'vesta', 'programs', 'gpt2.vst')
+# a checkout of the reference (VESTA_REFERENCE) or the copy oracle/make_ref.py installs
+REF_PROGRAM = next((p for p in (os.path.join(os.environ.get('VESTA_REFERENCE', ''), 'vesta', 'programs', 'gpt2.vst'),
+                                os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), 'oracle', '_ref', 'vesta', 'programs', 'gpt2.vst'))
+                    if os.path.exists(p)), '')
 
 
 @pytest.mark.skipif(not os.path.exists(REF_PROGRAM), reason='reference checkout not present')
@@ -81,3 +84,18 @@ def test_same_tree_as_reference_program():
     """the program the reference ships and the generated text are the same statements"""
     ref = open(REF_PROGRAM, encoding='utf-8').read()
     assert sx.parse(ref) == sx.parse(decode_program(GPT2_SMALL))
+
+
+def test_drop_in_package_offers_interp():
+    """vesta.interp of the drop-in package: `parse` is this backend's front end; `run` is the reference's CPU
+    interpreter when a copy of the reference is installed, and says so when it is not"""
+    import numpy as np
+    import vesta.interp as vi
+    assert vi.parse is sx.parse
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if os.path.exists(os.path.join(here, 'oracle', '_ref', 'vesta', 'interp.py')):
+        env = vi.run('residue a\naxis i = 3\nb[i] = a[i] + a[i]\n', {'a': np.arange(3, dtype=np.float32)})
+        assert np.array_equal(np.asarray(env['b'][0]), [0, 2, 4])
+    else:
+        with pytest.raises(ImportError):
+            vi.run('', {})

@@ -39,7 +39,6 @@ struct Driver {
                                   unsigned, CUstream, void**) = nullptr;
     CUresult (*Launch)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned,
                        CUstream, void**, void**) = nullptr;
-    CUresult (*LaunchEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
     CUresult (*MemcpyHtoDAsync)(CUdeviceptr, const void*, size_t, CUstream) = nullptr;
     CUresult (*MemcpyDtoHAsync)(void*, CUdeviceptr, size_t, CUstream) = nullptr;
     CUresult (*StreamSynchronize)(CUstream) = nullptr;
@@ -67,7 +66,7 @@ int driver() {
               sym(lib, "cuModuleGetFunction", d.ModuleGetFunction) && sym(lib, "cuFuncSetAttribute", d.FuncSetAttribute) &&
               sym(lib, "cuOccupancyMaxActiveBlocksPerMultiprocessor", d.Occupancy) &&
               sym(lib, "cuLaunchCooperativeKernel", d.LaunchCooperative) && sym(lib, "cuLaunchKernel", d.Launch) &&
-              sym(lib, "cuLaunchKernelEx", d.LaunchEx) && sym(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled) &&
+              sym(lib, "cuTensorMapEncodeTiled", d.TensorMapEncodeTiled) &&
               sym(lib, "cuMemcpyHtoDAsync_v2", d.MemcpyHtoDAsync) && sym(lib, "cuMemcpyDtoHAsync_v2", d.MemcpyDtoHAsync) &&
               sym(lib, "cuStreamSynchronize", d.StreamSynchronize);
     if (!ok) return fail(-1, "libcuda.so.1 lacks a required driver entry point");
@@ -249,29 +248,6 @@ int vesta_launch(void* function, unsigned grid, unsigned block, unsigned dynamic
     if (int e = driver()) return e;
     return cu(g_cu.Launch((CUfunction)function, grid, 1, 1, block, 1, 1, dynamic_smem, (CUstream)stream, args, nullptr),
               "cuLaunchKernel");
-}
-
-int vesta_launch_cluster(void* function, unsigned grid, unsigned block, unsigned dynamic_smem, unsigned cluster,
-                         int cooperative, void* stream, void** args) {
-    if (int e = driver()) return e;
-    if (cluster > 8) {
-        if (int e = cu(g_cu.FuncSetAttribute((CUfunction)function, CU_FUNC_ATTRIBUTE_NON_PORTABLE_CLUSTER_SIZE_ALLOWED, 1),
-                       "cuFuncSetAttribute(NON_PORTABLE_CLUSTER_SIZE_ALLOWED)")) return e;
-    }
-    CUlaunchAttribute attr[2];
-    unsigned n = 0;
-    if (cluster > 1) {
-        attr[n].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-        attr[n].value.clusterDim.x = cluster; attr[n].value.clusterDim.y = 1; attr[n].value.clusterDim.z = 1;
-        n++;
-    }
-    if (cooperative) { attr[n].id = CU_LAUNCH_ATTRIBUTE_COOPERATIVE; attr[n].value.cooperative = 1; n++; }
-    CUlaunchConfig cfg;
-    memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
-    cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
-    cfg.sharedMemBytes = dynamic_smem; cfg.hStream = (CUstream)stream; cfg.attrs = attr; cfg.numAttrs = n;
-    return cu(g_cu.LaunchEx(&cfg, (CUfunction)function, args, nullptr), "cuLaunchKernelEx");
 }
 
 int vesta_step_bind(void* function, unsigned grid, unsigned block, unsigned dynamic_smem,

@@ -132,9 +132,15 @@ class Kernel:
             ok(L.vesta_module_get_function(mod, b'vesta_pack', ctypes.byref(pk)))
             self.mod, self.fn, self.pack_fn = mod, fn, pk
             self.smem = lowered.shared_bytes
-            self.block = block or lowered.block
-            if self.block != lowered.block:
-                raise RuntimeError(f'the step kernel runs with {lowered.block} threads per block')
+            # The reference's signature defaults to block=256 (vesta/launch.py:30) and callers pass it along: 256 and
+            # None both mean "the block size the program was lowered for" (8 consumer warps + the producer warp).
+            if block not in (None, 256, lowered.block):
+                raise RuntimeError(f'the step kernel runs with {lowered.block} threads per block, not {block}')
+            self.block = lowered.block
+            if blocks_per_sm not in (None, 1):
+                import warnings
+                warnings.warn(f'blocks_per_sm={blocks_per_sm} is ignored: the step kernel is placed for one persistent block per SM',
+                              RuntimeWarning, stacklevel=2)
             ok(L.vesta_func_set_max_dynamic_smem(fn, self.smem))
             per_sm = ctypes.c_int()
             ok(L.vesta_occupancy(fn, self.block, self.smem, ctypes.byref(per_sm)))
