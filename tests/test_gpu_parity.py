@@ -208,6 +208,43 @@ def test_batches_above_one_slab(batch, slab_tiles, tune):
     m.k.check()
 
 
+@pytest.mark.parametrize('batch,tune', [
+    (64, None),                                         # one slab of 64 sequences
+    (70, None),                                         # two slabs, the second with six live rows
+    (130, dict(tcl_ks_proj=2, tcl_ks_p2=2)),            # three slabs; both projections split over the fold
+    (64, dict(tcl_ks_p2=4)),                            # the MLP projection one k-block per unit
+    (64, dict(tc_layers=False)),                        # the same batch with the layer contractions on mma.sync
+])
+def test_tensor_core_layer_contractions(batch, tune):
+    """64 sequences and more at widths that are multiples of 128: QKV, attention projection, FC and MLP projection as
+    tcgen05 units (accumulators in tensor memory, weights from the packed operand image, operands written by the
+    previous phase as fp16 swizzled rows), against the oracle over several steps (K/V emit and attention included)"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY
+    from vesta_gpu_b200.synth import make_prompts
+    steps = 6
+    m, hf = model(TINY, 11, 'rich', batch, steps, tune=dict(tune or {}, ln_dist=True))     # (rows normalised once on the grid, as at full size)
+    assert bool(m.low.dims['tcl']) == (not tune or tune.get('tc_layers', True))
+    W = O.upcast(hf.weights)
+    feed = make_prompts(TINY, batch, steps, seed=batch)
+    caches = [O.new_cache(TINY, steps) for _ in range(batch)]
+    m.reset()
+    worst = 0.0
+    for t in range(steps):
+        m.x.copy_(torch.from_numpy(feed[:, t].copy()).cuda()); m.step()
+        lg = m.logits().cpu().numpy(); nx = m.next().cpu().numpy()
+        for i in range(batch):
+            ref, rn = O.step(TINY, W, caches[i][0], caches[i][1], int(feed[i, t]), t)
+            worst = max(worst, float(np.abs(lg[i] - ref).max()))
+            if O.margin(ref) > MARGIN:
+                assert int(nx[i]) == rn, (t, i)
+    assert worst < TIGHT, worst
+    k = m.keys.cpu().numpy().astype(np.float32)
+    for i in range(batch):
+        assert np.abs(k[i, :, :steps] - caches[i][0].astype(np.float32)).max() <= 2e-3
+    m.k.check()
+
+
 def test_ragged_prompts_fed_on_the_device():
     """per-sequence prompt lengths, consumed by the kernel's own feedback (no host write between steps),
     late starts so that every prompt ends at the same step; the greedy streams equal the oracle's"""

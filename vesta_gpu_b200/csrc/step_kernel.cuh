@@ -277,6 +277,33 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
 // producer: walks this CTA's stream, segment by segment
 // ---------------------------------------------------------------------------------------------
 #define TC_SLABS_P ((V_B + 63) / 64)
+#if V_TCL
+// Layer contractions on the tensor cores (V_TCL: 64 sequences and more). A unit = one accumulator tile: 128 output
+// columns (m-tile) x one slab of 64 sequences x a run of k-blocks (64 fold indices each); units are dealt round-robin
+// over the CTAs. QKV and FC take the whole fold per unit (their epilogues need complete sums: bias, q / K / V emit,
+// GELU); the two projections split the fold V_TCL_KS_PROJ / V_TCL_KS_P2 ways and add into the vector the LayerNorm pass
+// started. The weights come from a packed copy in the shared-memory image of the operand (K-major rows of 128 bytes,
+// 128-byte swizzle), per layer [QKV | attn-proj | FC | MLP-proj], each ordered (m-tile, k-block).
+#define TCL_TILE_BYTES 16384
+#define TCL_KB_D (V_D / 64)
+#define TCL_KB_F (V_F / 64)
+#define TCL_T_PROJ ((3 * V_D / 128) * TCL_KB_D)
+#define TCL_T_FC (TCL_T_PROJ + (V_D / 128) * TCL_KB_D)
+#define TCL_T_P2 (TCL_T_FC + (V_F / 128) * TCL_KB_D)
+#define TCL_T_LAYER (TCL_T_P2 + (V_D / 128) * TCL_KB_F)
+__device__ __forceinline__ int tcl_mt(int kind) { return kind == PH_QKV ? 3 * V_D / 128 : kind == PH_FC ? V_F / 128 : V_D / 128; }
+__device__ __forceinline__ int tcl_ks(int kind) { return kind == PH_PROJ ? V_TCL_KS_PROJ : kind == PH_P2 ? V_TCL_KS_P2 : 1; }
+__device__ __forceinline__ int tcl_ktot(int kind) { return kind == PH_P2 ? TCL_KB_F : TCL_KB_D; }
+__device__ __forceinline__ int tcl_nkb(int kind) { return kind == PH_PROJ ? TCL_KB_D / V_TCL_KS_PROJ : kind == PH_P2 ? TCL_KB_F / V_TCL_KS_P2 : TCL_KB_D; }
+__device__ __forceinline__ int tcl_units(int kind) { return TC_SLABS_P * tcl_mt(kind) * tcl_ks(kind); }
+__device__ __forceinline__ int tcl_first_tile(int kind) { return kind == PH_QKV ? 0 : kind == PH_PROJ ? TCL_T_PROJ : kind == PH_FC ? TCL_T_FC : TCL_T_P2; }
+__device__ __forceinline__ void tcl_unit(int kind, int u, int& slab, int& mt, int& ks) {
+    const int per = tcl_mt(kind) * tcl_ks(kind);
+    slab = u / per;
+    const int r = u - slab * per;
+    mt = r / tcl_ks(kind); ks = r - mt * tcl_ks(kind);
+}
+#endif
 #define TMAP_WTE 8                               // index of the embedding table's descriptor at TM (after the eight of K and V)
 // leaving early: first let the copies still in flight land (bounded), so that none writes into shared memory
 // after the CTA has gone
@@ -318,6 +345,29 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
                              :: "r"(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES)), "l"(TM + TMAP_WTE * 128), "r"(kb * 64), "r"(P[PT_LOG_J0] * 16 + mt * 128), "r"(0),
                                 "r"(full_bar(c, slot)) : "memory");
                 c.chunk++;
+            }
+            continue;
+        }
+#endif
+#if V_TCL
+        {
+            // the weight tiles (128 output columns x 64 k, 16 KB, the shared-memory image of the tensor-core operand) of
+            // this CTA's units, one per ring slot; the same tile serves every slab of 64 sequences (from L2 after the first)
+            const int nkb = tcl_nkb(first);
+#pragma unroll 1
+            for (int u = cta; u < tcl_units(first); u += ncta) {
+                int slab, mt, ks;
+                tcl_unit(first, u, slab, mt, ks);
+                const unsigned char* src = WP + ((size_t)l * TCL_T_LAYER + tcl_first_tile(first) + (size_t)mt * tcl_ktot(first) + ks * nkb) * TCL_TILE_BYTES;
+#pragma unroll 1
+                for (int kb = 0; kb < nkb; kb++) {
+                    const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+                    wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
+                    if (c.dead) { producer_drain(c); return; }
+                    mbar_expect(full_bar(c, slot), TCL_TILE_BYTES);
+                    bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src + (size_t)kb * TCL_TILE_BYTES, TCL_TILE_BYTES, full_bar(c, slot));
+                    c.chunk++;
+                }
             }
             continue;
         }
@@ -714,7 +764,7 @@ __device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* 
 }
 
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
-                                                float* __restrict__ part, int l, const int* s_pos, const unsigned char* __restrict__ TM) {
+                                                float* __restrict__ part, int l, const int* s_pos, const unsigned char* __restrict__ TM, unsigned char* __restrict__ og) {
     const int g = c.lane >> 2, t = c.lane & 3;
     AttIter cur, pf;
     cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
@@ -826,7 +876,9 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
             }
         }
         if (V_B <= 16) TRACE(46);
+#if !V_TCL
         float* out = part + (size_t)cur.it * PART_STRIDE;
+#endif
         // the warps' partial results of an item meet in shared memory; consecutive items use alternate buffers, so
         // that a warp that is already done with the next item does not overwrite what the merge is still reading
         float* ms = reinterpret_cast<float*>(c.smem + SM_MISC + MISC_ATT) + (item & 1) * (NW * (V_E + 2));
@@ -860,8 +912,16 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                     dd += ms[w * (V_E + 2) + 1] * sc;
                     num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
                 }
+#if V_TCL
+                // one item per (sequence, head): the normalised output goes straight into the operand of the projection
+                // (fp16, K-major swizzled rows: k-block = head, as the head width is 64)
+                const int rb = cur.b % 64;
+                *reinterpret_cast<u16*>(og + ((size_t)(cur.b / 64) * TCL_KB_D + cur.h) * (64 * 128) + rb * 128 + (((c.tid >> 3) ^ (rb & 7)) << 4) + (c.tid & 7) * 2) =
+                    f2h(dd > 0.f ? __fdividef(num, dd) : 0.f);
+#else
                 out[2 + c.tid] = num;
                 if (c.tid == 0) { out[0] = M; out[1] = dd; }
+#endif
             }
             // start the next item
             item++;
@@ -921,7 +981,8 @@ __device__ __forceinline__ void tc_commit(u32 bar) {
 
 // the normalised rows of the final state as operand B in global memory: row r of slab r / 64, block k / 64,
 // 16-byte piece (k % 64) / 8 stored at piece ^ (row % 8) of its 128-byte row
-__device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ z, unsigned char* __restrict__ tcg) {
+// With `init` the same pass starts the vector the following projection is combined into: init[r] = z[r] + bias.
+__device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ z, float* __restrict__ init, unsigned char* __restrict__ tcg) {
     const u16* prm = reinterpret_cast<const u16*>(c.smem + SM_PRM);
 #pragma unroll 1
     for (int r = c.cta * NW + c.warp; r < TC_SLABS * TC_N; r += c.ncta * NW) {
@@ -962,6 +1023,11 @@ __device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ 
                 }
                 const int kb = d / TC_KB, piece = (d % TC_KB) >> 3;
                 *reinterpret_cast<uint2*>(dst + (size_t)kb * (TC_N * 128) + ((piece ^ (rb & 7)) << 4) + ((d & 4) ? 8 : 0)) = o;
+                if (init && r < V_B) {
+                    const uint2 ib = *reinterpret_cast<const uint2*>(prm + 2 * V_D + d);
+                    *reinterpret_cast<float4*>(init + (size_t)r * V_D + d) =
+                        make_float4(v[i].x + h_lo(ib.x), v[i].y + h_hi(ib.x), v[i].z + h_lo(ib.y), v[i].w + h_hi(ib.y));
+                }
             }
         }
     }
@@ -1041,6 +1107,106 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
         if (mybest && b < V_B) atomicMax(gbest + b, mybest);
     }
 }
+
+#if V_TCL
+// One layer contraction on the tensor cores: this CTA's units of `kind`, one after the other. Per unit: the operand of
+// its slab (64 sequences x the unit's k-blocks, fp16, K-major swizzled rows written to global memory by the previous
+// phase) is bulk-copied into the K/V stages, which are idle outside the attention phase; the weight tiles arrive in
+// the ring; one thread issues four tcgen05.mma (128 x 64 x 16) per k-block and commits them to the slot's empty
+// barrier, after the last k-block to the "done" barrier; then the eight warps read the accumulator (thread = output
+// column, registers = 32 sequences) and run the epilogue of the kind.
+struct TclOut {
+    const u16 *bias;                 // QKV / FC: bias of the layer (halves), 0 otherwise
+    float* sum;                      // the projections: the vector their partial sums are added into
+    float* q;                        // QKV: queries, fp32 [sequence][V_D]
+    u16 *keys, *vals;                // QKV: the caches
+    unsigned char* gg;               // FC: GELU output as the operand of the MLP projection
+    const int* s_pos;
+};
+__device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const unsigned char* __restrict__ opb, const TclOut& o) {
+    const u32 tmem = *reinterpret_cast<const volatile u32*>(c.smem + SM_MISC + MISC_TMEM);
+    const int nkb = tcl_nkb(kind), ktot = tcl_ktot(kind);
+    const int quarter = c.warp & 3, col0 = (c.warp >> 2) * 32;       // this warp reads lanes 32*quarter.., columns col0..col0+31
+#pragma unroll 1
+    for (int u = c.cta; u < tcl_units(kind); u += c.ncta) {
+        int slab, mt, ks;
+        tcl_unit(kind, u, slab, mt, ks);
+        if (c.tid == 0) {
+            asm volatile("fence.proxy.async.global;" ::: "memory");          // the operand was written by other CTAs with ordinary stores
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect(tc_load_bar(c), (u32)nkb * (TC_N * 128));
+#pragma unroll 1
+            for (int kb = 0; kb < nkb; kb++)
+                bulk_g2s(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128), opb + ((size_t)slab * ktot + ks * nkb + kb) * (TC_N * 128), TC_N * 128, tc_load_bar(c));
+        }
+        wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u); c.tcl++;
+#pragma unroll 1
+        for (int kb = 0; kb < nkb; kb++) {
+            const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+            wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            if (c.warp == 0) {
+                if (c.lane == 0 && !c.dead) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const u64 ad = tc_desc(smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES));
+                    const u64 bd = tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128));
+#pragma unroll
+                    for (int k = 0; k < TC_KB / 16; k++) tc_mma(tmem, ad + 2 * k, bd + 2 * k, (kb | k) ? 1u : 0u);
+                    tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
+                    if (kb == nkb - 1) tc_commit(tc_done_bar(c));
+                } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+                __syncwarp();
+            } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+            c.chunk++;
+        }
+        wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u); c.tcd++;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        u32 r[32];
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                       "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+                       "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                     : "r"(tmem + ((u32)(quarter * 32) << 16) + (u32)col0) : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int j = mt * 128 + quarter * 32 + c.lane;                      // this thread's output column
+        if (!c.dead) {
+            if (kind == PH_QKV) {
+                const float bias = h2f(o.bias[(size_t)l * 3 * V_D + j]);
+                const int part = j / V_D, jj = j - part * V_D;               // 0: query, 1: key, 2: value
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int b = slab * TC_N + col0 + i;
+                    const float v = __uint_as_float(r[i]) + bias;
+                    if (b < V_B) {
+                        if (part == 0) o.q[(size_t)b * V_D + jj] = v;
+                        else if (o.s_pos[b] >= 0) (part == 1 ? o.keys : o.vals)[((size_t)(b * V_L + l) * V_TMAX + o.s_pos[b]) * V_D + jj] = f2h(v);
+                    }
+                }
+            } else if (kind == PH_FC) {
+                const float bias = h2f(o.bias[(size_t)l * V_F + j]);
+                unsigned char* dst = o.gg + ((size_t)slab * TCL_KB_F + (j >> 6)) * (TC_N * 128) + (j & 7) * 2;
+                const int piece = (j & 63) >> 3;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int rb = col0 + i;
+                    const float v = __uint_as_float(r[i]) + bias;
+                    const float g = V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v)));
+                    *reinterpret_cast<u16*>(dst + rb * 128 + ((piece ^ (rb & 7)) << 4)) = f2h(g);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const int b = slab * TC_N + col0 + i;
+                    if (b < V_B) red_add(o.sum + (size_t)b * V_D + j, __uint_as_float(r[i]));
+                }
+            }
+        }
+        // every warp is done reading before the next unit's first product overwrites the accumulator (and before the
+        // next unit's operand replaces this one in the K/V stages: its products have completed)
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        cons_sync();
+    }
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // the step
@@ -1148,6 +1314,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_KSPLIT
     unsigned char* gg = reinterpret_cast<unsigned char*>(a.S + V_OFF_GG);     // GELU outputs as operand tiles: [slab][fold tile][batch tile]
 #endif
+#if V_TCL
+    unsigned char* og = reinterpret_cast<unsigned char*>(a.S + V_OFF_OG);     // attention output as the operand of the projection
+#else
+    unsigned char* og = 0;
+#endif
     u64* gbest = reinterpret_cast<u64*>(a.S + V_OFF_BEST);
     const int gtid = c.cta * NCONS + c.tid, gthreads = c.ncta * NCONS;
     const size_t ZS = (size_t)V_B * V_D;
@@ -1191,7 +1362,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_TIMING
             const long long att_t0 = clock64();
 #endif
-            attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos, a.TM);
+            attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos, a.TM, og);
 #if V_TIMING
             // every CTA's time in the attention phase of the middle layer (cycles), for the balance across the grid
             if (l == V_L / 2 && c.tid == 0) a.TS[1024 + c.cta] = (u64)(clock64() - att_t0);
@@ -1209,8 +1380,12 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_LN_DIST
         if (first == PH_QKV || first == PH_FC || first == PH_LOGITS) {
 #if V_TC
-            if (first == PH_LOGITS) ln_rows_to_tc(c, zin, tcg);
+            if (first == PH_LOGITS) ln_rows_to_tc(c, zin, (float*)0, tcg);
             else
+#endif
+#if V_TCL
+            ln_rows_to_tc(c, (first == PH_FC) ? z1 : zin, (first == PH_QKV) ? z1 : z2, tcg);
+            if (false)
 #endif
             ln_rows_to_global(c, (first == PH_FC) ? z1 : zin, (first == PH_QKV) ? z1 : (first == PH_FC) ? z2 : (float*)0, actg);
             phase_end(c);
@@ -1220,6 +1395,16 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_TC
         if (first == PH_LOGITS) { logits_tc(c, P, tcg, logit, gbest); break; }
 #endif
+#if V_TCL
+        if (first != PH_ATT) {
+            TclOut o;
+            o.bias = (first == PH_QKV) ? a.qkvb : (first == PH_FC) ? a.fcb : (const u16*)0;
+            o.sum = (first == PH_PROJ) ? z1 : z2;
+            o.q = qbuf; o.keys = a.keys; o.vals = a.vals; o.gg = gg; o.s_pos = s_pos;
+            tc_contraction(c, first, l, (first == PH_PROJ) ? og : (first == PH_P2) ? gg : tcg, o);
+        }
+#endif
+#if !V_TCL
 #pragma unroll 1
         for (int slab = 0; slab < ((first == PH_ATT) ? 0 : NSLAB); slab++) {
             const int row0 = slab * SB, nrows = min(SB, V_B - row0);
@@ -1360,6 +1545,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
                 TRACE(20 + kind);
             }
         }
+#endif
         if (first == PH_LOGITS) break;
 
         // ---- grid barrier; the next LayerNorm's parameters are fetched while waiting
@@ -1515,6 +1701,26 @@ __device__ int pack_segment(const PackArgs& a, unsigned char* dst, const int* __
     return n;
 }
 
+#if V_TCL
+// The weight image of the tensor-core layer contractions: per layer [QKV | attn-proj | FC | MLP-proj], each a list of
+// (m-tile, k-block) tiles of 128 output columns x 64 fold indices in the shared-memory layout of a K-major operand with
+// the 128-byte swizzle: row r (one output column) = 128 bytes at r * 128, its 16-byte piece p stored at p ^ (r % 8).
+// One block per tile and pass over the grid; the logits read the embedding table itself (by TMA), nothing is packed
+// for them.
+__device__ void pack_body(const PackArgs& a) {
+    for (int tile = blockIdx.x; tile < V_L * TCL_T_LAYER; tile += gridDim.x) {
+        const int l = tile / TCL_T_LAYER, t = tile - l * TCL_T_LAYER;
+        const int kind = t < TCL_T_PROJ ? PH_QKV : t < TCL_T_FC ? PH_PROJ : t < TCL_T_P2 ? PH_FC : PH_P2;
+        const int i = t - tcl_first_tile(kind), mt = i / tcl_ktot(kind), kb = i - mt * tcl_ktot(kind);
+        unsigned char* dst = a.WP + (size_t)tile * TCL_TILE_BYTES;
+        for (int e = threadIdx.x; e < 128 * 64; e += blockDim.x) {
+            // consecutive threads take consecutive output columns: the weights are stored with the output index contiguous
+            const int r = e & 127, k = e >> 7;
+            *reinterpret_cast<u16*>(dst + r * 128 + ((((k >> 3) ^ (r & 7))) << 4) + (k & 7) * 2) = w_elem(a, kind, l, mt * 128 + r, kb * 64 + k);
+        }
+    }
+}
+#else
 // grid: (V_L + 1) blocks per CTA of the step kernel: blockIdx.x = cta * (V_L + 1) + l; l == V_L packs the logits
 __device__ void pack_body(const PackArgs& a) {
     const int cta = blockIdx.x / (V_L + 1), l = blockIdx.x % (V_L + 1);
@@ -1530,3 +1736,4 @@ __device__ void pack_body(const PackArgs& a) {
         pack_segment(a, base + ((size_t)l * (u32)P[PT_LAYER] + seg_of(P, kind).off) * FRAG_BYTES, P, kind, l, wid, nwarp, lane);
     }
 }
+#endif

@@ -555,6 +555,22 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     _groups = math.ceil((D // 16) / 2)
     _nk = math.ceil((F // 16) / max(1, min(F // 16, grid // _groups))) if _groups <= grid else 1 << 30
     ksplit = bool(tune.get('ksplit', B >= 32) and _nk <= KT_D and _groups <= grid)
+    # Tensor cores (tcgen05, accumulators in tensor memory) where the contractions are dense: 64 sequences and more.
+    # The logits as tiles of 128 vocabulary rows x 64 sequences (the fp16 operand of 64 sequences, 64 x D x 2 bytes,
+    # takes the place of the K/V stages, a 128 x 64 tile of the table one ring slot); the four layer contractions as
+    # units of 128 output columns x 64 sequences x a run of 64-wide k-blocks from a packed weight image (where the
+    # widths are multiples of 128 and the operand of a unit, at most kvst x 4 k-blocks, fits the K/V stages): QKV and
+    # FC over the whole fold, the two projections split so that a unit's operand fits.
+    tc = bool(tune.get('tc', True) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
+              and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
+    kbd, kbf = D // 64, F // 64
+    tcl = bool(tc and tune.get('tc_layers', True) and D % 128 == 0 and F % 128 == 0 and kbd <= kvst * 4 and ksplit)
+    ks_proj = ks_p2 = 1
+    if tcl:
+        ks_proj = int(tune.get('tcl_ks_proj', 2 if kbd % 2 == 0 and kbd >= 4 else 1))
+        ks_p2 = int(tune.get('tcl_ks_p2', min(k for k in range(1, kbf + 1) if kbf % k == 0 and kbf // k <= min(kvst * 4, kbd))))
+        if kbd % ks_proj or kbf % ks_p2 or kbf // ks_p2 > kvst * 4:
+            raise ValueError('tcl_ks_proj / tcl_ks_p2 must divide the k-blocks of the fold and leave an operand that fits the K/V stages')
     rec, tiles, notes = place_step(dims, grid, ksplit)
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
@@ -575,7 +591,9 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     # where a chunk still is a full tile of positions at a typical context (measured: no gain at batch 64 with
     # contexts of 512-1024, a loss of 3 % with contexts of 128-384).
     tail_bh, ts = B * H, 1
-    if nch == 1 and B * H > grid and (B * H) % grid and tune.get('tail_split', True):
+    if tcl and nch != 1:
+        raise NotImplementedError('tensor-core layer contractions take the attention output of whole (sequence, head) items')
+    if nch == 1 and B * H > grid and (B * H) % grid and tune.get('tail_split', True) and not tcl:
         left = (B * H) % grid
         want = tune.get('tail_split', True)
         ts = min(grid // left, 8, max(tmax // 2, 1) // 128) if want is True else min(grid // left, int(want))
@@ -587,16 +605,13 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     off_part = off_q + up(B * D)
     off_actg = off_part + up(att_items * (E + 2))
     off_best = off_actg + (up(((B + 8 * NB - 1) // (8 * NB)) * KT_D * NB * atile // 4) if ln_dist else 0)
-    # Logits on tcgen05 tensor cores with accumulators in tensor memory, where the contraction is dense (64
-    # sequences and more): 128 vocabulary rows x 64 sequences per tile. The fp16 operand of 64 sequences
-    # (64 x D x 2 bytes) takes the place of the K/V stages, and a 128 x 64 tile of the table one ring slot.
-    tc_default = True
-    tc = bool(tune.get('tc', tc_default) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
-              and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
     off_tc = off_best + up(2 * B)
     off_gg = off_tc + (up(((B + 63) // 64) * 64 * D * 2 // 4) if tc else 0)
-    # V_KSPLIT: the GELU outputs as operand tiles, per slab [fold tile of F][batch tile]
-    scratch_floats = off_gg + (up(((B + 8 * NB - 1) // (8 * NB)) * (F // 16) * NB * atile // 4) if ksplit else 0)
+    # V_KSPLIT: the GELU outputs as operand tiles, per slab [fold tile of F][batch tile]; with tensor-core layer
+    # contractions as fp16 K-major swizzled rows per slab of 64 sequences, like the attention output behind them
+    tc_slabs = (B + 63) // 64
+    off_og = off_gg + ((up(tc_slabs * 64 * F * 2 // 4) if tcl else up(((B + 8 * NB - 1) // (8 * NB)) * (F // 16) * NB * atile // 4)) if ksplit else 0)
+    scratch_floats = off_og + (up(tc_slabs * 64 * D * 2 // 4) if tcl else 0)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
 
     fixed = smem_fixed(NB)
@@ -614,7 +629,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_TCL=int(tcl), V_TCL_KS_PROJ=ks_proj, V_TCL_KS_P2=ks_p2, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     params, pack_params, tail = _entry_points(res, roles, fb, prompt_len)
@@ -646,6 +661,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         + ['logits', 'finish']
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                   barriers_per_launch=1 + (4 + int(ksplit)) * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
-                  block=(NW + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
-                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc, ksplit=ksplit), roles=roles)
+                  block=(NW + 1) * 32, grid=grid, place=rec, pack_params=pack_params,
+                  packed_bytes=(L * ((3 * D // 128 + D // 128 + F // 128) * kbd + (D // 128) * kbf) * 16384) if tcl else tiles * 512,
+                  dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc, ksplit=ksplit, tcl=tcl,
+                            tcl_ks=(ks_proj, ks_p2), kernel='large'), roles=roles)
     return low
