@@ -430,7 +430,7 @@ def test_host_driven_step_equals_the_device_loop():
 
 
 def test_prefill_in_one_call_and_state_round_trip():
-    """prefill() (prompts to the device once, the kernel feeds itself) against feeding the prompt token by token from
+    """prefill_stepwise() (prompts to the device once, the kernel feeds itself) against feeding the prompt token by token from
     the host; state() / load_state() carry a generation over to a second model"""
     from vesta_gpu_b200.shapes import TINY3
     from vesta_gpu_b200.synth import make_ragged_prompts
@@ -438,7 +438,7 @@ def test_prefill_in_one_call_and_state_round_trip():
     lens, toks = make_ragged_prompts(TINY3, B, 2, 7, seed=9)
     pmax = int(lens.max())
     m, hf = model(TINY3, 13, 'rich', B, pmax + gen + 1, per_sequence_t=True, prompt_len=pmax)
-    m.prefill(toks[:, :pmax], lens)
+    m.prefill_stepwise(toks[:, :pmax], lens)
     m.k.check()
     first = m.x.cpu().numpy().copy()
     assert m.t.cpu().numpy().tolist() == lens.tolist()
@@ -462,6 +462,70 @@ def test_prefill_in_one_call_and_state_round_trip():
     assert np.array_equal(m2.x.cpu().numpy(), want)
     with pytest.raises(ValueError):
         m2.load_state(dict(st, x=st['x'][:2]))
+
+
+@pytest.mark.parametrize('shape_name,batch,rows', [('tiny', 5, 128), ('tiny3', 3, 64), ('tiny', 9, 64)])
+def test_dense_prefill_equals_the_oracle(shape_name, batch, rows):
+    """prefill(): every prompt position of every sequence as a row of a dense pass (rows of one sequence attend to the
+    rows before them, written in the same launch; several launches when the prompts exceed `rows`). Cache, first
+    generated token and the tokens that follow against the oracle, ragged lengths included."""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import SHAPES
+    from vesta_gpu_b200.synth import make_ragged_prompts
+    sh = SHAPES[shape_name]
+    gen = 4
+    lens, toks = make_ragged_prompts(sh, batch, 3, 40, seed=batch)
+    pmax = int(lens.max())
+    m, hf = model(sh, 21, 'rich', batch, pmax + gen + 1, per_sequence_t=True)
+    m.prefill(toks[:, :pmax], lens, rows=rows)
+    m.k.check()
+    assert m.t.cpu().numpy().tolist() == lens.tolist()
+    if shape_name == 'tiny':
+        assert m._prefill_engines[rows].low.dims['tcl']               # tensor-core contractions at widths of 128
+    W = O.upcast(hf.weights)
+    first = m.x.cpu().numpy()
+    keys = m.keys.float().cpu().numpy()
+    got = [m.x.clone()]
+    for _ in range(gen - 1):
+        m.step(); got.append(m.x.clone())
+    got = torch.stack(got, 1).cpu().numpy()
+    for i in range(batch):
+        r = O.decode(sh, W, toks[i, :lens[i]], gen)
+        k_ref = np.zeros_like(keys[i])
+        # the oracle's cache of the prompt positions (decode() keeps it internally: rebuild it step by step)
+        ck, cv = O.new_cache(sh, int(lens[i]))
+        for p in range(int(lens[i])):
+            O.step(sh, W, ck, cv, int(toks[i, p]), p)
+        assert np.abs(keys[i, :, :lens[i]] - ck.astype(np.float32)).max() <= 4e-3, i
+        ref = r['tokens'][lens[i] - 1: lens[i] - 1 + gen]
+        sure = r['margins'][lens[i] - 1: lens[i] - 1 + gen] > MARGIN
+        stop = len(ref) if sure.all() else int(np.argmin(sure))
+        assert np.array_equal(got[i, :stop], ref[:stop]), (i, got[i], ref)
+
+
+def test_dense_prefill_at_full_size_against_the_reference():
+    """GPT-2 small, the eight 128-token prompts of the batch-8 fixture in one dense pass (4 launches of 256 rows, tensor-core
+    contractions): the first generated token of every sequence and the free-running tokens after it equal the reference
+    interpreter's wherever its margin is above the bar"""
+    g = load('gpt2_cfg2')
+    sh, seed, init, prompts, gen, keep, stride = fixture_inputs(g)
+    B, P = prompts.shape
+    m, _ = model(sh, seed, init, B, P + 16)
+    m.prefill(prompts)
+    assert m._prefill_engines[256].low.dims['tcl']
+    toks = [m.x.clone()]
+    for _ in range(11):
+        m.step(); toks.append(m.x.clone())
+    got = torch.stack(toks, 1).cpu().numpy()
+    m.k.check()
+    compared = 0
+    for i in range(B):
+        ref = g[f'tokens_{i}'][P - 1:P - 1 + 12]
+        sure = g[f'margins_{i}'][P - 1:P - 1 + 12] > MARGIN
+        stop = 12 if sure.all() else int(np.argmin(sure))
+        assert np.array_equal(got[i, :stop], ref[:stop]), (i, got[i], ref)
+        compared += stop
+    assert compared >= 4 * B
 
 
 def test_out_of_range_inputs_are_refused_not_executed():

@@ -34,6 +34,16 @@ __device__ __forceinline__ float h2f(u16 h) { float f; asm("cvt.f32.f16 %0, %1;"
 __device__ __forceinline__ u16 f2h(float f) { u16 h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(f)); return h; }
 __device__ __forceinline__ float fast_exp(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f)); return y; }
 
+// tanh-GELU: a * v * (1 + tanh(b * (v + c * v^3))) with tanh(u) = 1 - 2 / (1 + e^(2u)) from the exponential and
+// reciprocal units (absolute error of the tanh about 1e-7; the library tanhf costs some forty instructions)
+__device__ __forceinline__ float gelu_tanh(float v) {
+    const float u = V_GELU_B * (v + V_GELU_C * v * v * v);
+    float e, r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(u * 2.8853900817779268f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+    return V_GELU_A * v * (2.0f - 2.0f * r);
+}
+
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint4& a, u32 b0, u32 b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])

@@ -71,6 +71,10 @@
 // P2 inside the CTA), then LOGITS. Batches above one slab (SB = 8 * V_NB rows: what the operand
 // tiles in shared memory hold) repeat the contraction phases slab by slab; the weight stream of
 // the phase is then read once per slab (from L2 after the first).
+// V_ROWSEQ: the rows of the batch are (cache sequence, position) pairs, several rows may belong to one sequence (a dense
+// pass over prompt positions: every row's K and V are written before any row attends, so a row sees the rows before it).
+// The sequence of row b follows the positions in shared memory.
+#define SEQ_OF(s_pos, b) (V_ROWSEQ ? (s_pos)[V_B + (b)] : (b))
 #define PH_QKV 0
 #define PH_ATT 1
 #define PH_PROJ 2
@@ -121,7 +125,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define MISC_ATT 0                                                // 2 x NW x (V_E + 2) floats (items alternate)
 #define MISC_BEST (((2 * NW * (V_E + 2) * 4) + 15) & ~15)         // SB x NW u64
 #define MISC_POS (MISC_BEST + SB * NW * 8)                        // V_B ints
-#define MISC_STAT ((MISC_POS + V_B * 4 + 15) & ~15)                // 8 x 2 floats
+#define MISC_STAT ((MISC_POS + V_B * 4 * (1 + V_ROWSEQ) + 15) & ~15)  // 8 x 2 floats (after the positions and, with V_ROWSEQ, the cache sequences of the rows)
 #define MISC_FLAG (MISC_STAT + 8 * 8)                             // one int
 #define MISC_STOP (MISC_FLAG + 4)                                 // one int: the consumers are leaving
 #define MISC_ATTSEQ (MISC_FLAG + 12)                              // one u32: attention phases the consumers have opened
@@ -265,8 +269,8 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
             asm volatile("fence.proxy.async.global;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect(bar, 2 * (q + 1) * KV_SMALL * 128);
-            tma_rows(dst, TM + (2 * q) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
-            tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, a.b * V_L + l, bar);
+            tma_rows(dst, TM + (2 * q) * TMAP_BYTES, a.h * V_E, a.s, SEQ_OF(s_pos, a.b) * V_L + l, bar);
+            tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, SEQ_OF(s_pos, a.b) * V_L + l, bar);
             c.kvi++;
         }
         att_advance(a, s_pos, ncta);
@@ -788,7 +792,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                     const u32 stage = n % V_KVST;
                     patch |= 1u << stage;
                     if (c.tid < 16) {
-                        const u16* src = ((c.tid & 8) ? vals : keys) + ((size_t)(pf.b * V_L + l) * V_TMAX + tp) * V_D + (size_t)pf.h * V_E + (c.tid & 7) * 8;
+                        const u16* src = ((c.tid & 8) ? vals : keys) + ((size_t)(SEQ_OF(s_pos, pf.b) * V_L + l) * V_TMAX + tp) * V_D + (size_t)pf.h * V_E + (c.tid & 7) * 8;
                         cp16(side + stage * 256 + c.tid * 16, src);
                     }
                 }
@@ -1140,6 +1144,7 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                 bulk_g2s(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128), opb + ((size_t)slab * ktot + ks * nkb + kb) * (TC_N * 128), TC_N * 128, tc_load_bar(c));
         }
         wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u); c.tcl++;
+        TRACE(60);
 #pragma unroll 1
         for (int kb = 0; kb < nkb; kb++) {
             const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
@@ -1159,6 +1164,7 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
             c.chunk++;
         }
         wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u); c.tcd++;
+        TRACE(61);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         u32 r[32];
         asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -1178,7 +1184,7 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                     const float v = __uint_as_float(r[i]) + bias;
                     if (b < V_B) {
                         if (part == 0) o.q[(size_t)b * V_D + jj] = v;
-                        else if (o.s_pos[b] >= 0) (part == 1 ? o.keys : o.vals)[((size_t)(b * V_L + l) * V_TMAX + o.s_pos[b]) * V_D + jj] = f2h(v);
+                        else if (o.s_pos[b] >= 0) (part == 1 ? o.keys : o.vals)[((size_t)(SEQ_OF(o.s_pos, b) * V_L + l) * V_TMAX + o.s_pos[b]) * V_D + jj] = f2h(v);
                     }
                 }
             } else if (kind == PH_FC) {
@@ -1189,7 +1195,7 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                 for (int i = 0; i < 32; i++) {
                     const int rb = col0 + i;
                     const float v = __uint_as_float(r[i]) + bias;
-                    const float g = V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v)));
+                    const float g = gelu_tanh(v);
                     *reinterpret_cast<u16*>(dst + rb * 128 + ((piece ^ (rb & 7)) << 4)) = f2h(g);
                 }
             } else {
@@ -1200,6 +1206,7 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                 }
             }
         }
+        TRACE(62);
         // every warp is done reading before the next unit's first product overwrites the accumulator (and before the
         // next unit's operand replaces this one in the K/V stages: its products have completed)
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1217,6 +1224,7 @@ struct Args {
     u16 *keys, *vals;
     int* x_out; int* t_out;
     const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
+    const int* row_seq;                         // optional (V_ROWSEQ): cache sequence of every row
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
     const unsigned char* TM;                    // TMA descriptors: eight of the K/V cache, one of the embedding table
@@ -1255,6 +1263,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
             const int tb = __ldcg(a.t + b * V_TSTRIDE), xb = __ldcg(a.x + b);
             bad |= (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
             s_pos[b] = tb;
+#if V_ROWSEQ
+            const int sq = __ldcg(a.row_seq + b);
+            bad |= (sq < 0) | (sq >= V_BSEQ);
+            s_pos[V_B + b] = sq;
+#endif
         }
         // a launch that follows one that gave up does nothing: the abort flag stays until the host clears it
         if (c.tid == 0 && ld_relaxed(a.bar + BAR_ABORT)) bad |= 2;
@@ -1481,13 +1494,13 @@ __device__ __forceinline__ void step_body(const Args& a) {
                                     const int jx = (P[PT_QKV_J0] + jj) * 16 + j_in;
                                     if (jx < V_D) qbuf[(size_t)b * V_D + jx] = v;
                                     else if (s_pos[b] >= 0) {
-                                        const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
+                                        const size_t at = ((size_t)(SEQ_OF(s_pos, b) * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
                                         if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
                                     }
                                 }
                             } else {
                                 // g = gelu(u) -> operand tiles of the MLP projection: fold index = jj*16 + j_in
-                                const float g = (rb < nrows) ? V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))) : 0.f;
+                                const float g = (rb < nrows) ? gelu_tanh(v) : 0.f;
 #if V_KSPLIT
                                 act_store1(gg + (size_t)slab * KT_F * (V_NB * ATILE), rb, (P[PT_FC_J0] + jj) * 16 + j_in, g);
 #else
@@ -1561,13 +1574,20 @@ __device__ __forceinline__ void step_body(const Args& a) {
             else
                 fetch_params(c, a.lnfw, a.lnfb, (const u16*)0, (const u16*)0, 0);
         }
-        if (first == PH_QKV && c.tid == 0) {                                // the producer thread may request this layer's K/V tiles
+        // the producer thread may request this layer's K/V tiles: before the barrier (the consumers patch the row of the
+        // current position in), or after it where several rows of this step may lie in one tile (V_ROWSEQ)
+        if (first == PH_QKV && c.tid == 0 && !V_ROWSEQ) {
             volatile u32* seq = reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ);
             __threadfence_block();
             *seq = *seq + 1;
         }
         TRACE(30 + first);
         phase_wait(c);
+        if (first == PH_QKV && c.tid == 0 && V_ROWSEQ) {
+            volatile u32* seq = reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ);
+            __threadfence_block();
+            *seq = *seq + 1;
+        }
         TICK(3 + 2 * min(ph - l * PH_PER_LAYER, 3));
     }
     TICK(10);

@@ -857,6 +857,7 @@ struct Args {
     u16 *keys, *vals;
     int* x_out; int* t_out;
     const int* prompt; const int* plen;        // optional: tokens fed while t + 1 < plen[b] (V_PLEN > 0)
+    const int* row_seq;                         // (not used by this kernel text: rows are sequences)
     float* S; u32* bar; u64* TS;
     const unsigned char* WP; const int* PT;
     const unsigned char* TM;                    // TMA descriptors of the K/V cache
@@ -1051,7 +1052,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
                 const int j_in = (ln >> 2) + ((i & 2) ? 8 : 0), b = (ln & 3) * 2 + (i & 1);
                 const float v = whole_fold_sum(red, o) + h2f(tile_bias[(o >> 7) * 16 + j_in]);
                 // g = gelu(u) -> operand tiles of the MLP projection: fold index = tile * 16 + j_in
-                if (b < V_B) act_store1(gact, b, (o >> 7) * 16 + j_in, V_GELU_A * v * (1.0f + tanhf(V_GELU_B * (v + V_GELU_C * v * v * v))));
+                if (b < V_B) act_store1(gact, b, (o >> 7) * 16 + j_in, gelu_tanh(v));
             }
             cons_sync();
             TRACE(23);

@@ -79,6 +79,7 @@ class VestaGPT2:
         self.low = lower(text, spec, axis_max={'s': tmax}, batch=batch, per_token=per_token,
                          outputs=('logit', 'next'), feedback={'x': 'next', 't': 1} if feedback else None,
                          timing=timing, grid=sms, prompt_len=prompt_len if feedback else 0, slab_tiles=slab_tiles, tune=tune)
+        self._text, self._tune, self._prefill_engines = text, tune, {}
         self.k = Kernel(self.low, device=dev.index, blocks_per_sm=blocks_per_sm)
         if prompt_len and feedback:
             R = dict(R, prompt=self.prompt, plen=self.plen)
@@ -98,17 +99,51 @@ class VestaGPT2:
         they have"""
         self.k.step_host(self.x, tokens_host, self.next(), next_host)
 
-    def prefill(self, tokens, lengths=None):
-        """consume whole prompts in one call (needs prompt_len >= the longest prompt and per_sequence_t when the
-        lengths differ): the prompts go to the device once, then the kernel feeds itself one position per step,
-        several steps per launch, until every prompt has been read; sequences shorter than the longest start late
-        (negative positions) so that all of them end together. On return x holds the first generated token of every
-        sequence and t its position. tokens: int array (batch, P), lengths: (batch,) or None for P everywhere."""
+    def prefill(self, tokens, lengths=None, rows=None):
+        """consume whole prompts as dense passes: all prompt positions of all sequences are cut into launches of `rows`
+        (sequence, position) rows (default 256, or 128 for short prompts) through the large-batch kernel: tensor-core
+        contractions where the shape allows, every row's K and V written before any row attends, so a row sees the rows
+        of its own sequence before it. On return the cache holds every prompt position, x the first generated token
+        of every sequence and t its position (= its prompt length). tokens: int array (batch, P); lengths: (batch,) or
+        None for P everywhere (lengths that differ need per_sequence_t=True).
+        The reference feeds the prompt one position per step (bench/g0_bench.py:172-173); prefill_stepwise does the same
+        on the device."""
+        import numpy as np
+        tokens = np.asarray(tokens)
+        B, P = tokens.shape
+        if B != self.B:
+            raise ValueError('prefill needs one prompt per sequence of the batch')
+        lens = np.full(B, P, np.int32) if lengths is None else np.asarray(lengths, np.int32)
+        if lens.min() < 1 or lens.max() > P or lens.max() > self.tmax:
+            raise ValueError('prompt lengths must lie in 1..P and fit the cache')
+        if self.t.numel() == 1 and lens.min() != lens.max():
+            raise ValueError('prompts of different lengths need per_sequence_t=True')
+        total = int(lens.sum())
+        rows = int(rows or (256 if total >= 1024 else 128))
+        eng = self._prefill_engines.get(rows)
+        if eng is None:
+            eng = self._prefill_engines[rows] = _PrefillRows(self, rows)
+        self.reset()
+        first = eng.run(tokens, lens)
+        self.x.copy_(first)
+        self.t.copy_(torch.from_numpy(lens[:self.t.numel()].copy()))
+        if hasattr(self, 'prompt'):
+            buf = np.zeros(tuple(self.prompt.shape), np.int32)
+            w = min(P, buf.shape[1])
+            buf[:, :w] = tokens[:, :w]
+            self.prompt.copy_(torch.from_numpy(buf)); self.plen.copy_(torch.from_numpy(np.minimum(lens, buf.shape[1]).astype(np.int32)))
+
+    def prefill_stepwise(self, tokens, lengths=None):
+        """consume whole prompts one position per step, fed on the device (needs prompt_len >= the longest prompt and
+        per_sequence_t when the lengths differ): the prompts go to the device once, then the kernel feeds itself, several
+        steps per launch, until every prompt has been read; sequences shorter than the longest start late (negative
+        positions) so that all of them end together. On return x holds the first generated token of every sequence and
+        t its position. tokens: int array (batch, P), lengths: (batch,) or None for P everywhere."""
         import numpy as np
         tokens = np.asarray(tokens)
         B, P = tokens.shape
         if not hasattr(self, 'prompt') or B != self.B or P > self.prompt.shape[1]:
-            raise ValueError('prefill needs a model built with prompt_len >= the prompt length and the same batch')
+            raise ValueError('prefill_stepwise needs a model built with prompt_len >= the prompt length and the same batch')
         lens = np.full(B, P, np.int32) if lengths is None else np.asarray(lengths, np.int32)
         if lens.min() < 1 or lens.max() > P:
             raise ValueError('prompt lengths must lie in 1..P')
@@ -145,6 +180,49 @@ class VestaGPT2:
     def kv_bytes(self, n_ctx):
         sh = self.shape
         return 2 * sh.L * self.B * n_ctx * sh.D * self.keys.element_size()
+
+
+class _PrefillRows:
+    """The dense prompt pass behind VestaGPT2.prefill: a second lowering of the same program for `rows` rows of
+    (cache sequence, position) that share the model's weights and caches (lower(..., row_seq=True))."""
+
+    def __init__(self, model, rows):
+        dev, sh = model.device, model.shape
+        self.model, self.R = model, rows
+        self.x = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.t = torch.full((rows,), -1, dtype=torch.int32, device=dev)
+        self.seq = torch.zeros(rows, dtype=torch.int32, device=dev)
+        R = {'x': self.x, 't': self.t, **model.W, 'keys': model.keys, 'vals': model.vals}
+        names = {torch.int32: 'i32', torch.float16: 'f16', torch.float32: 'f32'}
+        spec = {n: (tuple(v.shape), names[v.dtype]) for n, v in R.items()}
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        tune = dict(model._tune or {})
+        tune.setdefault('ln_dist', True)            # rows normalised once on the grid: what the tensor-core contractions read
+        self.low = lower(model._text, spec, axis_max={'s': model.tmax}, batch=rows, per_token=('x', 'keys', 'vals', 't'),
+                         outputs=('logit', 'next'), feedback=None, grid=sms, row_seq=True, tune=tune)
+        self.k = Kernel(self.low, device=dev.index)
+        self.k.bind(dict(R, row_seq=self.seq))
+
+    def run(self, tokens, lens):
+        """tokens (B, P), lens (B,) numpy -> int32 tensor (B,) on the device: the token chosen after every prompt"""
+        import numpy as np
+        B, R = tokens.shape[0], self.R
+        seqs = np.repeat(np.arange(B, dtype=np.int32), lens)
+        pos = np.concatenate([np.arange(n, dtype=np.int32) for n in lens])
+        tok = tokens[seqs, pos].astype(np.int32)
+        first = torch.zeros(B, dtype=torch.int32, device=self.model.device)
+        for i in range(0, len(seqs), R):
+            n = min(R, len(seqs) - i)
+            x, t, s = np.zeros(R, np.int32), np.full(R, -1, np.int32), np.zeros(R, np.int32)
+            x[:n], t[:n], s[:n] = tok[i:i + n], pos[i:i + n], seqs[i:i + n]
+            self.x.copy_(torch.from_numpy(x)); self.t.copy_(torch.from_numpy(t)); self.seq.copy_(torch.from_numpy(s))
+            self.k.launch()
+            last = np.flatnonzero(t[:n] == lens[s[:n]] - 1)            # rows that are the last position of their prompt
+            if len(last):
+                rows = torch.from_numpy(last).to(self.model.device)
+                first[torch.from_numpy(s[last].astype(np.int64)).to(self.model.device)] = self.k.view('next')[rows].to(torch.int32)
+        self.k.check()
+        return first
 
 
 DEFAULT_PROGRAM = PROGRAMS / 'gpt2.vst'

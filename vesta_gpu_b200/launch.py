@@ -195,7 +195,7 @@ class Kernel:
             for j, role in enumerate(('keys', 'vals')):
                 t = residue[self.lowered.roles[role]]
                 ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * (2 * q + j)), ctypes.c_void_p(t.data_ptr()),
-                                               d['D'], d['tmax'], d['B'] * d['L'], 64, rows))
+                                               d['D'], d['tmax'], t.shape[0] * d['L'], 64, rows))
         wte = residue[self.lowered.roles['wte']]
         ok(lib().vesta_tensor_map_rows(ctypes.c_void_p(host.data_ptr() + 128 * 8), ctypes.c_void_p(wte.data_ptr()),
                                        d['D'], d['N'], 1, 64, 128))

@@ -313,7 +313,7 @@ def place_step(dims, grid, ksplit=False):
 
 # ------------------------------------------------------------------ assembly
 
-def _entry_points(res, roles, fb, prompt_len, with_tensor_core_arg=True):
+def _entry_points(res, roles, fb, prompt_len, row_seq=False):
     """-> (params, pack_params, text of the two extern "C" kernels that wrap step_body / pack_body)"""
     emitted = {roles['keys'], roles['vals']} | (set(fb) if fb else set())
     params, sig = [], []
@@ -324,6 +324,9 @@ def _entry_points(res, roles, fb, prompt_len, with_tensor_core_arg=True):
     if prompt_len and fb:
         params += [('prompt', 'i32', False), ('plen', 'i32', False)]
         sig += ['const int* __restrict__ X_prompt', 'const int* __restrict__ X_plen']
+    if row_seq:
+        params += [('row_seq', 'i32', False)]
+        sig += ['const int* __restrict__ X_row_seq']
     R = {k: 'R_' + v for k, v in roles.items()}
     step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
                                 'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT',
@@ -337,6 +340,7 @@ def _entry_points(res, roles, fb, prompt_len, with_tensor_core_arg=True):
     else:
         fill.append('a.x_out = 0; a.t_out = 0;')
     fill.append('a.prompt = X_prompt; a.plen = X_plen;' if (prompt_len and fb) else 'a.prompt = 0; a.plen = 0;')
+    fill.append('a.row_seq = X_row_seq;' if row_seq else 'a.row_seq = 0;')
     fill.append('a.S = S; a.bar = bar; a.TS = TS; a.WP = WP; a.PT = PT; a.TM = TM; a.nsteps = nsteps;')
     pack_roles = ('wte', 'qkvw', 'ow', 'fcw', 'pw')
     pack_params = [roles[k] for k in pack_roles]
@@ -449,7 +453,7 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
                              nch=nch, kv_stages=kvst, ring_slots=nslot), roles=roles)
 
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
-          grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None):
+          grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None, row_seq=False):
     """See the module docstring. `res`: name -> (shape, dtype) as the kernel sees them (batched
     where per-token; scalars have shape ()). `axis_max`: bound of the run-time position axis,
     e.g. {'s': tmax}. `grid`: CTAs to place for (one per SM). 't' may be listed in per_token, in
@@ -457,7 +461,11 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     sequence that has not started yet. `prompt_len` > 0 adds two kernel parameters after the
     residues, `prompt` (batch, prompt_len) i32 and `plen` (batch,) i32: the feedback then feeds
     prompt[b][t+1] instead of the model's own choice while t + 1 < plen[b], so that prompts (ragged,
-    or the reference's tokens for teacher forcing) are consumed without a host round trip."""
+    or the reference's tokens for teacher forcing) are consumed without a host round trip. `row_seq=True` makes the rows of
+    the batch (cache sequence, position) pairs: the caches may then hold a different number of sequences than the batch has
+    rows, a parameter `row_seq` (batch,) i32 follows the residues, and every row attends to its sequence's rows up to its own
+    position, those written in the same step included (a dense pass over prompt positions; needs per-sequence positions,
+    no feedback, more than eight rows)."""
     env, ext, recv = recognise(text)
     dims = _dims(env, ext)
     D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
@@ -495,7 +503,10 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                    ('ob', (L, D)), ('ln2w', (L, D)), ('ln2b', (L, D)), ('fcw', (L, D, F)), ('fcb', (L, F)),
                    ('pw', (L, F, D)), ('pb', (L, D)), ('lnfw', (D,)), ('lnfb', (D,))):
         want(r, shp, 'f16')
-    want('keys', (B, L, tmax, H, E), 'f16'); want('vals', (B, L, tmax, H, E), 'f16')
+    bseq = int(res[roles['keys']][0][0]) if row_seq else B
+    if row_seq and (not t_per_token or feedback or B <= 8):
+        raise NotImplementedError('row_seq needs per-sequence positions, no feedback and more than eight rows')
+    want('keys', (bseq, L, tmax, H, E), 'f16'); want('vals', (bseq, L, tmax, H, E), 'f16')
     for r in ('x', 'keys', 'vals'):
         if roles[r] not in per_token:
             raise NotImplementedError(f'{roles[r]} must be a per-token residue')
@@ -507,7 +518,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
             raise NotImplementedError(f'output {o}: only {env["$logit"]} and {env["$next"]} are kept for the host')
 
     tune = dict(tune or {})
-    if B <= 8 and not tune.get('large_kernel') and act_lo is None and not slab_tiles:
+    if B <= 8 and not tune.get('large_kernel') and act_lo is None and not slab_tiles and not row_seq:
         return _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, prompt_len, timing, grid, tune)
 
     # rows per slab (8 per batch tile): the operand tiles of a slab live in shared memory next to the
@@ -534,7 +545,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
 
     def smem_fixed(nb):
         return (kvst * (2 * NW * 16 * 128 + 256 + 16) + 32 + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
-                + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 + 16 + 8 * 8 + 16 + 16)
+                + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 * (2 if row_seq else 1) + 16 + 8 * 8 + 16 + 16)
 
     NB = min((B + 7) // 8, 8)
     if slab_tiles:
@@ -572,6 +583,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
         if kbd % ks_proj or kbf % ks_p2 or kbf // ks_p2 > kvst * 4:
             raise ValueError('tcl_ks_proj / tcl_ks_p2 must divide the k-blocks of the fold and leave an operand that fits the K/V stages')
     rec, tiles, notes = place_step(dims, grid, ksplit)
+    if tcl:
+        NB = 1          # the mma.sync operand tiles are not used: their shared memory goes to the weight ring
 
     # global scratch (floats): host-visible values first, then the kernel's own vectors
     def up(v, a=64):
@@ -629,10 +642,10 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_TCL=int(tcl), V_TCL_KS_PROJ=ks_proj, V_TCL_KS_P2=ks_p2, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_ROWSEQ=int(bool(row_seq)), V_BSEQ=bseq, V_TCL=int(tcl), V_TCL_KS_PROJ=ks_proj, V_TCL_KS_P2=ks_p2, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
-    params, pack_params, tail = _entry_points(res, roles, fb, prompt_len)
+    params, pack_params, tail = _entry_points(res, roles, fb, prompt_len, row_seq)
     src = head + COMMON_TEXT.read_text(encoding='utf-8') + KERNEL_TEXT.read_text(encoding='utf-8') + tail
 
     q = env
