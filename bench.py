@@ -18,6 +18,7 @@ The line of the default run (cfg2) carries, beside the contract's keys:
               memory, launches, and reads the chosen tokens back
 `roofline`    algorithmic bytes per launch (all weights + attended K/V, the reference's byte model,
               vesta/gpt2.py:44-45,54-55) / mean launch duration, against the measured copy bandwidth
+`prefill`     the prompt as dense passes of (sequence, position) rows against one position per step (both untimed in `value`)
 `secondary`   the same measurements for cfg1 (batch 1), taken in the same run
 `strong`      cfg5 (256 ragged sequences split evenly over the N GPUs): tokens/s, us per step and the fraction of the
               byte-model speed-up over one GPU
@@ -399,6 +400,32 @@ class Run:
         same = round(float((torch.stack(seen[:-1], 1) == stream[:, 1:].cpu()).float().mean()), 4) if K > 1 else None
         return times, same
 
+    def prefill_block(self):
+        """the prompt as dense passes (VestaGPT2.prefill: rows of (sequence, position), tensor-core contractions) against
+        the reference's protocol of one position per step; -> dict or None (ragged workloads feed prompts on the device)"""
+        if self.ragged:
+            return None
+        torch, m = self.torch, self.m
+        prompts = self.pd.cpu().numpy()
+
+        def timed(fn, n=3):
+            out = []
+            for _ in range(n):
+                torch.cuda.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                out.append(e0.elapsed_time(e1))
+            return statistics.median(out)
+        m.prefill(prompts); torch.cuda.synchronize()              # builds the second lowering and its weight image, untimed
+        dense = timed(lambda: m.prefill(prompts))
+        first_dense = m.x.clone()
+        step = timed(self.prefill)
+        rows = max(m._prefill_engines)
+        return dict(positions=int(prompts.size), dense_ms=dense, one_position_per_step_ms=step, rows_per_launch=rows,
+                    tensor_core_contractions=bool(m._prefill_engines[rows].low.dims['tcl']),
+                    first_tokens_equal=round(float((first_dense == m.x).float().mean()), 4))
+
     def bytes_per_step(self):
         """algorithmic bytes of one step on one GPU: every weight once + the attended K/V of its sequences"""
         return sum(self.sh.weight_bytes() + self.sh.kv_bytes_per_pos() * sum(c) / self.world for c in self.ctx_lens) / self.K
@@ -482,6 +509,7 @@ def main():
     mark0 = sampler.mark() if sampler else 0
     res, stream = run.measure(args.repeats)
     mark1 = sampler.mark() if sampler else 0
+    prefill = run.prefill_block() if (world == 1 and not args.no_extras) else None
     all_tokens = gather_tokens(stream.to(torch.int32), list(run.mine), run.B * world)
     if rank == 0:
         assert all_tokens.shape == (run.B * world, run.K)
@@ -531,6 +559,8 @@ def main():
                             steps_per_launch=min(args.per_launch, K), contexts=res['contexts'],
                             l2='weights + KV read per step (%.0f MB) exceed the 126 MB L2' % (res['roofline']['bytes_per_step'] / 1e6), cv=res['cv']),
                 clocks=clocks, gpu_launches=res['gpu_launches'], e2e=res['e2e'], roofline=res['roofline'])
+    if prefill:
+        line['prefill'] = prefill
     if secondary:
         line['secondary'] = secondary
     if strong:

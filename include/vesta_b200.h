@@ -89,7 +89,8 @@ void vesta_step_release(void* bound);
  * sums, normally allocated by the caller) in a fixed array inside the library's device image,
  * vesta_static_scratch_bytes() bytes (4 MiB) per GPU for the life of the process. The caller passes
  * the residues (inputs, the KV cache), the packed weights, the plan table and the nine TMA
- * descriptors (vesta_tensor_map_rows, in device memory) it already owns, the
+ * descriptors (vesta_tensor_map_rows, in device memory) it already owns (the KV cache must hold finite values in
+ * unused rows: the attention stages rows in boxes of 32 and weighs the ones past the position with zero), the
  * sizes the lowering reported (scratch_floats, counters) and where the logits and next lie in the
  * scratch; the results are copied to logits_out / next_out (device or pinned host memory) on
  * `stream`. Allocates nothing; a step that needs more scratch than the array holds is refused with

@@ -46,7 +46,7 @@ def stream_tiles(rec, dims, cta):
                                            (GPT2_XL, 1, 148), (GPT2_SMALL, 8, 132), (TINY, 1, 7),
                                            (GPT2_SMALL, 64, 148), (TINY3, 40, 148), (GPT2_SMALL, 256, 132)])
 def test_every_weight_tile_exactly_once(sh, batch, grid):
-    low = lower_for(sh, batch, 64, grid=grid, tune=dict(ksplit=True) if batch >= 40 else None)
+    low = lower_for(sh, batch, 64, grid=grid, tune=dict(ksplit=True, tc_layers=False) if batch >= 40 else None)      # (the mma.sync streams)
     assert low.dims['ksplit'] == (batch >= 40)
     dims = low.dims
     D, F, N, L = dims['D'], dims['F'], dims['N'], dims['L']
@@ -65,6 +65,35 @@ def test_every_weight_tile_exactly_once(sh, batch, grid):
         assert v.min() == 1 and v.max() == 1, k
     # every output tile of the projection has exactly one CTA that starts at fold tile 0, NARROW widths fit
     assert low.place[:, 3].max() <= lw.WN_MAX and low.place[:, 9].max() <= lw.WN_MAX
+
+
+def test_tensor_core_weight_image_covers_every_weight_once():
+    """64 sequences and more at widths that are multiples of 128: the packed image of the layer weights is a list of
+    (m-tile of 128 output columns, k-block of 64 fold indices) tiles per layer and contraction (pack_body / tcl_* in
+    csrc/step_kernel.cuh restated); the units of a phase cover every (slab, m-tile, k-block) exactly once"""
+    for sh, B in ((GPT2_SMALL, 64), (GPT2_SMALL, 256), (TINY, 130)):
+        low = lower_for(sh, B, 64, tune=dict(ln_dist=True))
+        assert low.dims['tcl'] and low.dims['tc'] and low.dims['ksplit']
+        D, F, L = sh.D, sh.F, sh.L
+        kbd, kbf = D // 64, F // 64
+        mt = {'qkv': 3 * D // 128, 'proj': D // 128, 'fc': F // 128, 'p2': D // 128}
+        ktot = {'qkv': kbd, 'proj': kbd, 'fc': kbd, 'p2': kbf}
+        first, t = {}, 0
+        for k in ('qkv', 'proj', 'fc', 'p2'):
+            first[k] = t
+            t += mt[k] * ktot[k]
+        assert low.packed_bytes == L * t * 16384 == 2 * L * (D * 3 * D + D * D + 2 * D * F)      # every weight element once
+        ks = {'qkv': 1, 'proj': define(low, 'V_TCL_KS_PROJ'), 'fc': 1, 'p2': define(low, 'V_TCL_KS_P2')}
+        slabs = (B + 63) // 64
+        for k in first:
+            nkb = ktot[k] // ks[k]
+            assert nkb * ks[k] == ktot[k] and nkb * 8192 <= define(low, 'V_KVST') * 32768       # a unit's operand fits the K/V stages
+            seen = np.zeros((slabs, mt[k], ktot[k]), np.int32)
+            for u in range(slabs * mt[k] * ks[k]):
+                slab, r = divmod(u, mt[k] * ks[k])
+                m, s_ = divmod(r, ks[k])
+                seen[slab, m, s_ * nkb:(s_ + 1) * nkb] += 1
+            assert seen.min() == 1 and seen.max() == 1
 
 
 def test_every_phase_has_the_smallest_possible_largest_share():
@@ -164,8 +193,10 @@ def test_per_sequence_positions():
 
 
 def test_slabs_and_device_side_prompts():
+    low = lower_for(GPT2_SMALL, 64, 1024, tune=dict(tc_layers=False))
+    assert low.dims['NB'] == 4 and '#define V_LN_DIST 1' in low.src        # mma.sync contractions: 32 rows per slab, rows normalised once
     low = lower_for(GPT2_SMALL, 64, 1024)
-    assert low.dims['NB'] == 4 and '#define V_LN_DIST 1' in low.src        # 32 rows per slab, rows normalised once
+    assert low.dims['tcl'] and low.dims['NB'] == 1 and '#define V_LN_DIST 1' in low.src      # tensor-core contractions: no operand tiles in shared memory
     assert low.shared_bytes <= 227 * 1024
     low = lower_for(TINY, 20, 16, slab_tiles=1)
     assert low.dims['NB'] == 1
@@ -198,8 +229,8 @@ def test_tensor_core_logits_are_chosen_where_the_contraction_is_dense():
 def test_attention_items_cover_every_sequence_head_and_position():
     """the item arithmetic of the attention phase (att_item / att_load_item in csrc/step_kernel.cuh) restated: whole
     rounds of one item per (sequence, head), then the leftover pairs split into position chunks"""
-    for sh, B, tmax, tune in ((GPT2_SMALL, 64, 1025, None), (GPT2_SMALL, 1, 384, dict(large_kernel=True)), (TINY3, 60, 6, dict(tail_split=4)),
-                              (GPT2_SMALL, 64, 400, None)):
+    for sh, B, tmax, tune in ((GPT2_SMALL, 64, 1025, dict(tc_layers=False)), (GPT2_SMALL, 1, 384, dict(large_kernel=True)), (TINY3, 60, 6, dict(tail_split=4)),
+                              (GPT2_SMALL, 64, 400, dict(tc_layers=False)), (GPT2_SMALL, 64, 1025, None)):
         low = lower_for(sh, B, tmax, tune=tune)
         nch, tail_bh, ts, H = define(low, 'V_NCH'), define(low, 'V_TAIL_BH'), define(low, 'V_TS'), low.dims['H']
         items = tail_bh * nch + (B * H - tail_bh) * ts
@@ -214,8 +245,10 @@ def test_attention_items_cover_every_sequence_head_and_position():
                 cs = (max(n, 1) + k - 1) // k
                 seen[bh, ch * cs: min(n, (ch + 1) * cs)] += 1
             assert seen.min() == 1 and seen.max() == 1
-        if sh is GPT2_SMALL and B == 64 and tmax == 1025:
+        if sh is GPT2_SMALL and B == 64 and tmax == 1025 and tune:
             assert ts == 4 and tail_bh == 740 and items <= 6 * 148        # five whole rounds and one of quarter items
+        if tune is None:
+            assert ts == 1 and nch == 1 and low.dims['tcl']              # tensor-core contractions take whole (sequence, head) items
 
 
 def small_tile_list(low, cta, pos):

@@ -101,7 +101,7 @@ class VestaGPT2:
 
     def prefill(self, tokens, lengths=None, rows=None):
         """consume whole prompts as dense passes: all prompt positions of all sequences are cut into launches of `rows`
-        (sequence, position) rows (default 256, or 128 for short prompts) through the large-batch kernel: tensor-core
+        (sequence, position) rows (default 1024 from 16 K positions, 256 from 1 K, else 128) through the large-batch kernel: tensor-core
         contractions where the shape allows, every row's K and V written before any row attends, so a row sees the rows
         of its own sequence before it. On return the cache holds every prompt position, x the first generated token
         of every sequence and t its position (= its prompt length). tokens: int array (batch, P); lengths: (batch,) or
@@ -119,7 +119,7 @@ class VestaGPT2:
         if self.t.numel() == 1 and lens.min() != lens.max():
             raise ValueError('prompts of different lengths need per_sequence_t=True')
         total = int(lens.sum())
-        rows = int(rows or (256 if total >= 1024 else 128))
+        rows = int(rows or (1024 if total >= 16384 else 256 if total >= 1024 else 128))
         eng = self._prefill_engines.get(rows)
         if eng is None:
             eng = self._prefill_engines[rows] = _PrefillRows(self, rows)
