@@ -375,6 +375,37 @@ __device__ __forceinline__ float whole_fold_sum(const float* red, int o) {
     return v;
 }
 
+// The sums of one output tile (accumulator layout of mma.m16n8k16: lane (g, t) holds outputs g and g + 8 of sequences
+// 2t and 2t + 1) added to z[b][unit * 16 + ...] with one 16-byte atomic per lane instead of four 4-byte ones: the
+// four lanes g = 4i .. 4i + 3 transpose their 4 x 4 values (four shuffles), after which lane q = g % 4 holds four
+// consecutive outputs of sequence 2t + q % 2 in the tile's half q / 2. A 148-way sum at eight sequences is bound by the
+// number of atomic operations the L2 has to retire.
+__device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v)[4], int lane) {
+    const int g = lane >> 2, t = lane & 3, q = g & 3;
+    if (V_B <= 2) {
+        // one or two sequences: only the lanes with t == 0 hold live sums; plain 4-byte atomics (measured: the
+        // transposition costs more than it saves here)
+        float* o = zu + (size_t)(2 * t) * V_D + g;
+        if (2 * t < V_B) { red_add(o, v[0]); red_add(o + 8, v[2]); }
+        if (2 * t + 1 < V_B) { red_add(o + V_D, v[1]); red_add(o + V_D + 8, v[3]); }
+        return;
+    }
+    const bool odd = q & 1, hi = q & 2;
+    // round 1, partner g ^ 1: even lanes keep registers 0 and 2, odd lanes 1 and 3
+    const float s0 = odd ? v[0] : v[1], s1 = odd ? v[2] : v[3];
+    const float r0 = __shfl_xor_sync(0xffffffffu, s0, 4), r1 = __shfl_xor_sync(0xffffffffu, s1, 4);
+    const float ax = odd ? r0 : v[0], ay = odd ? v[1] : r0;          // register q % 2 of rows (g & ~1), (g & ~1) + 1
+    const float bx = odd ? r1 : v[2], by = odd ? v[3] : r1;          // register 2 + q % 2 of the same rows
+    // round 2, partner g ^ 2: lanes 0, 1 keep the a pair (tile half 0), lanes 2, 3 the b pair (tile half 1)
+    const float t0 = hi ? ax : bx, t1 = hi ? ay : by;
+    const float u0 = __shfl_xor_sync(0xffffffffu, t0, 8), u1 = __shfl_xor_sync(0xffffffffu, t1, 8);
+    const float o0 = hi ? u0 : ax, o1 = hi ? u1 : ay, o2 = hi ? bx : u0, o3 = hi ? by : u1;
+    const int b = 2 * t + (q & 1);
+    if (b < V_B)
+        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     :: "l"(zu + (size_t)b * V_D + (g & ~3) + (hi ? 8 : 0)), "f"(o0), "f"(o1), "f"(o2), "f"(o3) : "memory");
+}
+
 // A slice of US fold tiles for `nunits` output tiles (stream order: output tile major). Warp w takes the output
 // tiles w, w + 8, ... of every ring slot, two at a time (independent chains of products); the sums are added to
 // zt[b][unit * 16 + ...] with fp32 atomics (the other slices of the fold are other CTAs'). The operand tiles of
@@ -385,8 +416,6 @@ __device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nun
     uint4 bop[US];
 #pragma unroll
     for (int r = 0; r < US; r++) bop[r] = lds16(act + r * ATILE + lane * 16);
-    const int g = lane >> 2, t = lane & 3;
-    float* zl = zt + (size_t)(2 * t) * V_D + g;
 #pragma unroll 1
     for (int u0 = 0; u0 < nunits; u0 += upc) {
         const u32 chunk = st & ~ST_DEAD, slot = chunk % V_NSLOT, use = chunk / V_NSLOT;
@@ -406,14 +435,10 @@ __device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nun
                 mma_hl(a0, l0, w0, bop[r]);
                 mma_hl(a1, l1, w1, bop[r]);
             }
-            float* o0 = zl + (u0 + u) * 16;
-            if (2 * t < V_B) { red_add(o0, a0[0] + l0[0]); red_add(o0 + 8, a0[2] + l0[2]); }
-            if (2 * t + 1 < V_B) { red_add(o0 + V_D, a0[1] + l0[1]); red_add(o0 + V_D + 8, a0[3] + l0[3]); }
-            if (two) {
-                float* o1 = o0 + NW * 16;
-                if (2 * t < V_B) { red_add(o1, a1[0] + l1[0]); red_add(o1 + 8, a1[2] + l1[2]); }
-                if (2 * t + 1 < V_B) { red_add(o1 + V_D, a1[1] + l1[1]); red_add(o1 + V_D + 8, a1[3] + l1[3]); }
-            }
+            const float f0[4] = {a0[0] + l0[0], a0[1] + l0[1], a0[2] + l0[2], a0[3] + l0[3]};
+            red_tile(zt + (u0 + u) * 16, f0, lane);
+            const float f1[4] = {a1[0] + l1[0], a1[1] + l1[1], a1[2] + l1[2], a1[3] + l1[3]};
+            if (two) red_tile(zt + (u0 + u + NW) * 16, f1, lane);       // (warp-uniform)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(slot));
