@@ -33,6 +33,8 @@ def stream_tiles(rec, dims, cta):
             qj0_, qnj_, qk0_, qnk_ = [int(v) for v in rec[cta][12:16]]
             seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
                 + narrow('fc', l, fj0, fnj, KT_D) + narrow('p2', l, qj0_, qnj_, qnk_, qk0_)
+        elif dims.get('fuse_proj'):                  # the attention projection is applied per head by the attention items
+            seg = narrow('qkv', l, qj0, qnj, KT_D) + narrow('fc', l, fj0, fnj, KT_D) + wide('p2', l, 0, JT_D, fj0, fnj)
         else:
             seg = narrow('qkv', l, qj0, qnj, KT_D) + wide('proj', l, pj0, pnj, pk0, pnk) \
                 + narrow('fc', l, fj0, fnj, KT_D) + wide('p2', l, 0, JT_D, fj0, fnj)
@@ -60,6 +62,15 @@ def test_every_weight_tile_exactly_once(sh, batch, grid):
         cursor += len(tiles)
         for kind, l, j, k in tiles:
             seen[kind][l, j, k] += 1
+    if dims.get('fuse_proj'):
+        # behind the per-CTA streams: per layer and head the head's 64 rows of the projection, output tile major
+        assert cursor == dims['fuse_base']
+        fus = dims['E'] // 16
+        for l in range(L):
+            for h in range(dims['H']):
+                for i in range((D // 16) * fus):
+                    seen['proj'][l, i // fus, h * fus + i % fus] += 1
+                    cursor += 1
     assert cursor * 512 == low.packed_bytes
     for k, v in seen.items():
         assert v.min() == 1 and v.max() == 1, k
@@ -124,7 +135,7 @@ def test_lowered_fields_match_reference_contract():
     off2, _, shape2 = low.scratch['next']
     assert shape2 == (8,) and off2 >= 8 * 50257 and low.scratch_floats > off2 + 8
     assert low.shared_bytes <= 227 * 1024
-    assert low.barriers_per_launch == 1 + 4 * 12          # the reference needs 113 at batch 8
+    assert low.barriers_per_launch == 1 + 3 * 12          # three per layer (the projection rides on the attention items); the reference needs 113 at batch 8
     assert 'vesta_step' in low.src and 'vesta_pack' in low.src and low.counters >= 64
     assert len(low.plan) >= 8 and all(len(p) == 2 for p in low.plan)
     no_fb = lower_for(GPT2_SMALL, 1, 64, feedback=False)

@@ -8,7 +8,10 @@ typedef unsigned short u16;
 
 #define NW V_NW
 #define NCONS (NW * 32)
-#define NTHREADS (NCONS + 32)
+#ifndef V_NPROD
+#define V_NPROD 1                       // producer warps behind the consumer warps
+#endif
+#define NTHREADS (NCONS + 32 * V_NPROD)
 #define KT_D (V_D / 16)
 #define JT_D (V_D / 16)
 #define KT_F (V_F / 16)
@@ -45,7 +48,7 @@ __device__ __forceinline__ float gelu_tanh(float v) {
 }
 
 __device__ __forceinline__ void mma16816(float (&c)[4], const uint4& a, u32 b0, u32 b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }

@@ -1,5 +1,5 @@
 // The decode step for at most eight sequences (one batch tile of the tensor-core products), written for sm_100a
-// (B200, 148 SMs): one persistent cooperative kernel, one CTA per SM, 8 consumer warps + 1 producer warp.
+// (B200, 148 SMs): one persistent cooperative kernel, one CTA per SM, 8 consumer warps + 2 producer warps.
 //
 // A step of a small batch moves few bytes per phase (GPT-2 small: 96 KB of weights per CTA and layer), so what it
 // costs is the chain of dependent operations between its grid-wide exchanges, not bandwidth. This text keeps that
@@ -72,8 +72,8 @@ struct Ctx {
 #if V_TIMING
 // event trace of one CTA (V_TIMING - 1) in one layer: per warp up to TRACE_EVENTS (id, clock) pairs in shared memory
 #define TRACE_EVENTS 96
-__shared__ u64 trace_[(V_NW + 1) * TRACE_EVENTS];
-__shared__ int trace_n[V_NW + 1];
+__shared__ u64 trace_[(V_NW + 2) * TRACE_EVENTS];
+__shared__ int trace_n[V_NW + 2];
 __shared__ int trace_on;
 __device__ __forceinline__ void trace_event(int id) {
     if ((threadIdx.x & 31) == 0 && *reinterpret_cast<volatile int*>(&trace_on)) {
@@ -158,6 +158,11 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 // a list entry: x = sequence | head << 8 | flags, y = first position, z = positions (0: an empty chunk), w = item
 #define TL_LAST (1 << 16)                        // last tile of its item: the item's result is written after it
 #define TL_PATCH (1 << 17)                       // may be requested before QKV has written the current position's row
+// V_FUSE_PROJ (one chunk per (sequence, head)): the CTA that finishes an item also multiplies its 64 outputs by the 64
+// rows of the projection that belong to the head (JT_D output tiles x 4 fold tiles, one copy per layer and head behind
+// the per-CTA streams of the packed weights, fetched behind the item's K/V tiles) and adds the result into z1: no separate projection phase, one grid barrier less per layer.
+#define FUSE_US (V_E / 16)
+#define FUSE_PER (8 * FUSE_US)                   // eight output tiles (one per warp) per ring slot
 
 // by one thread, once per step: the positions are the same in every layer
 __device__ __noinline__ void build_tile_list(int cta, int ncta, const int* s_pos) {
@@ -254,8 +259,12 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const unsigned
     }
 }
 
-__device__ __noinline__ void producer(u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP,
-                                      const unsigned char* __restrict__ TM, int cta, int ncta, int nsteps) {
+// Two producer threads (lane 0 of two warps), each with a resource of its own and an order of its own:
+//   * the weight producer walks this CTA's stream into the ring. Its order is fixed at lowering time (in the fused mode
+//     the heads of this CTA's attention items are cta + k * grid modulo the head count), so it never waits for
+//     anything but a free slot and runs ahead through barriers and attention phases;
+//   * the K/V producer requests the tiles of the attention phases from the per-step list as stages become free.
+__device__ __noinline__ void producer_weights(u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP, int cta, int ncta, int nsteps) {
     Ctx c;
     c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta; c.ncta = ncta; c.kvi = 0; c.seq = 0;
     const Plan p = load_plan(P);
@@ -268,8 +277,15 @@ __device__ __noinline__ void producer(u32* bar, const int* __restrict__ P, const
 #pragma unroll 1
         for (int l = 0; l < V_L; l++) {
             stream_tiles(c, src, p.qkv_nj * KT_D, per_qkv);
-            if (!c.dead) producer_attention(c, l, TM);
+#if V_FUSE_PROJ
+#pragma unroll 1
+            for (int it = cta; it < ATT_ITEMS && !c.dead; it += ncta) {
+                const unsigned char* hs = WP + ((size_t)V_FUSE_BASE + (size_t)(l * V_H + it % V_H) * (JT_D * FUSE_US)) * FRAG_BYTES;
+                stream_tiles(c, hs, JT_D * FUSE_US, FUSE_PER);
+            }
+#else
             if (!c.dead) stream_tiles(c, src, p.proj_nj * p.proj_nk, per_proj);
+#endif
             if (!c.dead) stream_tiles(c, src, p.fc_nj * KT_D, per_fc);
             if (!c.dead) stream_tiles(c, src, p.fc_nj * JT_D, per_p2);
             if (c.dead) { producer_drain(c); return; }
@@ -280,6 +296,15 @@ __device__ __noinline__ void producer(u32* bar, const int* __restrict__ P, const
             stream_tiles(c, src, width * KT_D, (CH / width) * width);
             if (c.dead) { producer_drain(c); return; }
         }
+    }
+}
+__device__ __noinline__ void producer_kv(u32* bar, const unsigned char* __restrict__ TM, int cta, int ncta, int nsteps) {
+    Ctx c;
+    c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta; c.ncta = ncta; c.kvi = 0; c.seq = 0;
+#pragma unroll 1
+    for (int i = 0; i < nsteps * V_L; i++) {
+        producer_attention(c, i % V_L, TM);
+        if (c.dead) { producer_drain(c); return; }
     }
 }
 
@@ -380,14 +405,15 @@ __device__ __forceinline__ float whole_fold_sum(const float* red, int o) {
 // four lanes g = 4i .. 4i + 3 transpose their 4 x 4 values (four shuffles), after which lane q = g % 4 holds four
 // consecutive outputs of sequence 2t + q % 2 in the tile's half q / 2. A 148-way sum at eight sequences is bound by the
 // number of atomic operations the L2 has to retire.
-__device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v)[4], int lane) {
+// `only` >= 0: only that sequence's sums are added (the operand held one live row).
+__device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v)[4], int lane, int only) {
     const int g = lane >> 2, t = lane & 3, q = g & 3;
     if (V_B <= 2) {
         // one or two sequences: only the lanes with t == 0 hold live sums; plain 4-byte atomics (measured: the
         // transposition costs more than it saves here)
         float* o = zu + (size_t)(2 * t) * V_D + g;
-        if (2 * t < V_B) { red_add(o, v[0]); red_add(o + 8, v[2]); }
-        if (2 * t + 1 < V_B) { red_add(o + V_D, v[1]); red_add(o + V_D + 8, v[3]); }
+        if (2 * t < V_B && (only < 0 || only == 2 * t)) { red_add(o, v[0]); red_add(o + 8, v[2]); }
+        if (2 * t + 1 < V_B && (only < 0 || only == 2 * t + 1)) { red_add(o + V_D, v[1]); red_add(o + V_D + 8, v[3]); }
         return;
     }
     const bool odd = q & 1, hi = q & 2;
@@ -401,7 +427,7 @@ __device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v
     const float u0 = __shfl_xor_sync(0xffffffffu, t0, 8), u1 = __shfl_xor_sync(0xffffffffu, t1, 8);
     const float o0 = hi ? u0 : ax, o1 = hi ? u1 : ay, o2 = hi ? bx : u0, o3 = hi ? by : u1;
     const int b = 2 * t + (q & 1);
-    if (b < V_B)
+    if (b < V_B && (only < 0 || only == b))
         asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
                      :: "l"(zu + (size_t)b * V_D + (g & ~3) + (hi ? 8 : 0)), "f"(o0), "f"(o1), "f"(o2), "f"(o3) : "memory");
 }
@@ -411,7 +437,7 @@ __device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v
 // zt[b][unit * 16 + ...] with fp32 atomics (the other slices of the fold are other CTAs'). The operand tiles of
 // the slice are read once, into registers. One instance per US.
 template <int US>
-__device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nunits, int upc, const unsigned char* act, float* __restrict__ zt) {
+__device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nunits, int upc, const unsigned char* act, float* __restrict__ zt, int only) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint4 bop[US];
 #pragma unroll
@@ -436,9 +462,9 @@ __device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nun
                 mma_hl(a1, l1, w1, bop[r]);
             }
             const float f0[4] = {a0[0] + l0[0], a0[1] + l0[1], a0[2] + l0[2], a0[3] + l0[3]};
-            red_tile(zt + (u0 + u) * 16, f0, lane);
+            red_tile(zt + (u0 + u) * 16, f0, lane, only);
             const float f1[4] = {a1[0] + l1[0], a1[1] + l1[1], a1[2] + l1[2], a1[3] + l1[3]};
-            if (two) red_tile(zt + (u0 + u + NW) * 16, f1, lane);       // (warp-uniform)
+            if (two) red_tile(zt + (u0 + u + NW) * 16, f1, lane, only);       // (warp-uniform)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty_bar(slot));
@@ -446,33 +472,86 @@ __device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nun
     }
     return st;
 }
-__device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, float* zt) {
+__device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, float* zt, int only = -1) {
     switch (us) {
-        case 1: return gemm_fold_slice_n<1>(st, bar, cta, nunits, upc, act, zt);
+        case 1: return gemm_fold_slice_n<1>(st, bar, cta, nunits, upc, act, zt, only);
 #if UMAX >= 2
-        case 2: return gemm_fold_slice_n<2>(st, bar, cta, nunits, upc, act, zt);
+        case 2: return gemm_fold_slice_n<2>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 3
-        case 3: return gemm_fold_slice_n<3>(st, bar, cta, nunits, upc, act, zt);
+        case 3: return gemm_fold_slice_n<3>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 4
-        case 4: return gemm_fold_slice_n<4>(st, bar, cta, nunits, upc, act, zt);
+        case 4: return gemm_fold_slice_n<4>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 5
-        case 5: return gemm_fold_slice_n<5>(st, bar, cta, nunits, upc, act, zt);
+        case 5: return gemm_fold_slice_n<5>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 6
-        case 6: return gemm_fold_slice_n<6>(st, bar, cta, nunits, upc, act, zt);
+        case 6: return gemm_fold_slice_n<6>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 7
-        case 7: return gemm_fold_slice_n<7>(st, bar, cta, nunits, upc, act, zt);
+        case 7: return gemm_fold_slice_n<7>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
 #if UMAX >= 8
-        case 8: return gemm_fold_slice_n<8>(st, bar, cta, nunits, upc, act, zt);
+        case 8: return gemm_fold_slice_n<8>(st, bar, cta, nunits, upc, act, zt, only);
 #endif
         default: return st;                     // the lowering refuses placements with deeper slices
     }
 }
+
+#if V_FUSE_PROJ
+// The projection of one attention item (fused mode): the head's 64 outputs (operand at V_SM_GACT, one live row `only`)
+// times the head's 64 rows of the projection, JT_D output tiles x FUSE_US fold tiles, eight output tiles per ring slot.
+// Several slots are taken at a time (the weight producer has had the whole attention phase to fill them): a warp then
+// runs one independent chain of products per slot, so the chains overlap instead of following one another.
+#define FUSE_GROUP (V_NSLOT - 1 < 6 ? V_NSLOT - 1 : 6)
+__device__ __noinline__ u32 proj_head(u32 st, u32* bar, int cta, float* __restrict__ z1, int only) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint4 bop[FUSE_US];
+#pragma unroll
+    for (int r = 0; r < FUSE_US; r++) bop[r] = lds16(smem + V_SM_GACT + r * ATILE + lane * 16);
+    constexpr int NSL = (JT_D + NW - 1) / NW;                    // ring slots of the item
+#pragma unroll 1
+    for (int s0 = 0; s0 < NSL; s0 += FUSE_GROUP) {
+        const int g = min(FUSE_GROUP, NSL - s0);
+        const u32 chunk = st & ~ST_DEAD;
+        float a[FUSE_GROUP][4], l[FUSE_GROUP][4];
+#pragma unroll
+        for (int i = 0; i < FUSE_GROUP; i++) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) { a[i][k] = 0.f; l[i][k] = 0.f; }
+            if (i < g) wait_full(st, bar, cta, (chunk + i) % V_NSLOT, ((chunk + i) / V_NSLOT) & 1u);
+        }
+        TRACE(53);
+        if (!(st & ST_DEAD)) {
+            const unsigned char* tp[FUSE_GROUP];
+#pragma unroll
+            for (int i = 0; i < FUSE_GROUP; i++) tp[i] = smem + V_SM_RING + ((chunk + (i < g ? i : 0)) % V_NSLOT) * SLOT_BYTES + warp * (FUSE_US * FRAG_BYTES) + lane * 16;
+#pragma unroll
+            for (int r = 0; r < FUSE_US; r++) {
+                // all loads of a round first, then its products: one chain per slot, none waits for another's load
+                uint4 w[FUSE_GROUP];
+#pragma unroll
+                for (int i = 0; i < FUSE_GROUP; i++) w[i] = lds16(tp[i] + r * FRAG_BYTES);
+#pragma unroll
+                for (int i = 0; i < FUSE_GROUP; i++) mma_hl(a[i], l[i], w[i], bop[r]);
+            }
+#pragma unroll
+            for (int i = 0; i < FUSE_GROUP; i++)
+                if (i < g && (s0 + i) * NW + warp < JT_D) {
+                    const float f[4] = {a[i][0] + l[i][0], a[i][1] + l[i][1], a[i][2] + l[i][2], a[i][3] + l[i][3]};
+                    red_tile(z1 + ((s0 + i) * NW + warp) * 16, f, lane, only);
+                }
+        }
+        __syncwarp();
+        if (lane == 0)
+            for (int i = 0; i < g; i++) mbar_arrive(empty_bar((chunk + i) % V_NSLOT));
+        st += (u32)g;
+    }
+    return st;
+}
+#endif
 
 // ---------------------------------------------------------------------------------------------
 // activations -> operand tiles in shared memory
@@ -671,7 +750,7 @@ __device__ __forceinline__ void q_store(u16* __restrict__ qop16, int b, int jx, 
 }
 
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const u32* __restrict__ qbuf,
-                                                float* __restrict__ part, int l, const int* s_pos) {
+                                                float* __restrict__ part, float* __restrict__ z1, int l, const int* s_pos) {
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
     if (ntl == 0) return;
@@ -793,9 +872,15 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
             c.kvn++;
         }
         if (last) {
+#if V_FUSE_PROJ
+            // the operand of the item's projection: four fold tiles (the head's 64 outputs) with one live row
+            if (c.tid >= 64 && c.tid < 64 + FUSE_US * 32) {
+                const int i = c.tid - 64;
+                *reinterpret_cast<uint4*>(smem + V_SM_GACT + (i >> 5) * ATILE + (i & 31) * 16) = make_uint4(0, 0, 0, 0);
+            }
+#endif
             cons_sync();                               // the warps' partial results of the item are in shared memory
             if (c.tid < V_E) {
-                float* out = part + (size_t)e.w * PART_STRIDE;
                 float M = -3.0e38f;
 #pragma unroll
                 for (int w = 0; w < NW; w++) M = fmaxf(M, ms[w * (V_E + 2)]);
@@ -806,9 +891,20 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                     dd += ms[w * (V_E + 2) + 1] * sc;
                     num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
                 }
+#if V_FUSE_PROJ
+                act_store1(smem + V_SM_GACT, e.x & 255, c.tid, dd > 0.f ? __fdividef(num, dd) : 0.f);      // a sequence that has not started attends to nothing
+#else
+                float* out = part + (size_t)e.w * PART_STRIDE;
                 out[2 + c.tid] = num;
                 if (c.tid == 0) { out[0] = M; out[1] = dd; }
+#endif
             }
+#if V_FUSE_PROJ
+            cons_sync();
+            TRACE(48);
+            ctx_set(c, proj_head(ctx_state(c), c.bar, c.cta, z1, e.x & 255));
+            cons_sync();                               // every warp has read the operand before the next item clears it
+#endif
             item++;
 #pragma unroll
             for (int kq = 0; kq < V_E / 16; kq++) { bq[kq][0] = bqn[kq][0]; bq[kq][1] = bqn[kq][1]; }
@@ -903,7 +999,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_TIMING
     __shared__ long long ts_[16];
     if (threadIdx.x == 0) { for (int i = 0; i < 16; i++) ts_[i] = 0; trace_on = 0; }
-    if (threadIdx.x <= V_NW) trace_n[threadIdx.x] = 0;
+    if (threadIdx.x <= V_NW + 1) trace_n[threadIdx.x] = 0;
     long long tlast_ = clock64();
     const u64 t_begin_ = now_ns();
 #endif
@@ -946,8 +1042,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
     __syncthreads();
 
     const int* P = a.PT + c.cta * PT_STRIDE;
-    if (c.warp == NW) {
-        if (c.lane == 0) producer(a.bar, P, a.WP, a.TM, c.cta, c.ncta, nsteps);
+    if (c.warp >= NW) {
+        if (c.lane == 0) {
+            if (c.warp == NW) producer_weights(a.bar, P, a.WP, c.cta, c.ncta, nsteps);
+            else producer_kv(a.bar, a.TM, c.cta, c.ncta, nsteps);
+        }
         return;
     }
     const Plan p = load_plan(P);
@@ -1036,7 +1135,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
         // ---- attention
         TRACE(2);
-        attention_phase(c, a.keys, a.vals, qbuf, part, l, s_pos);
+        attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos);
         TRACE(21);
         TICK(4);
         phase_end(c);
@@ -1046,6 +1145,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         phase_wait(c);
         TICK(5);
 
+#if !V_FUSE_PROJ
         // ---- attention projection + residual
         TRACE(3);
         if (p.proj_nj) {
@@ -1060,6 +1160,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         phase_wait(c);
         TICK(7);
 
+#endif
         // ---- LN2 + FC + GELU + MLP projection + residual
         TRACE(4);
 #pragma unroll 1
@@ -1255,8 +1356,17 @@ __device__ void pack_body(const PackArgs& a) {
     const int n_qkv = p.qkv_nj * KT_D, n_proj = p.proj_nj * p.proj_nk, n_fc = p.fc_nj * KT_D, n_p2 = p.fc_nj * JT_D;
     for (int i = wid; i < n_qkv; i += nwarp) pack_tile(a, dst + (size_t)i * FRAG_BYTES, PK_QKV, l, p.qkv_j0 + i % p.qkv_nj, i / p.qkv_nj, lane);
     dst += (size_t)n_qkv * FRAG_BYTES;
+#if V_FUSE_PROJ
+    // the heads' slices of the projection (64 rows each, output tile major), one copy per layer and head behind the
+    // per-CTA streams; the blocks of the first CTAs pack them
+    for (int h = cta; h < V_H; h += gridDim.x / (V_L + 1)) {
+        unsigned char* hd = a.WP + ((size_t)V_FUSE_BASE + (size_t)(l * V_H + h) * (JT_D * FUSE_US)) * FRAG_BYTES;
+        for (int i = wid; i < JT_D * FUSE_US; i += nwarp) pack_tile(a, hd + (size_t)i * FRAG_BYTES, PK_PROJ, l, i / FUSE_US, h * FUSE_US + i % FUSE_US, lane);
+    }
+#else
     for (int i = wid; i < n_proj; i += nwarp) pack_tile(a, dst + (size_t)i * FRAG_BYTES, PK_PROJ, l, p.proj_j0 + i / p.proj_nk, p.proj_k0 + i % p.proj_nk, lane);
     dst += (size_t)n_proj * FRAG_BYTES;
+#endif
     for (int i = wid; i < n_fc; i += nwarp) pack_tile(a, dst + (size_t)i * FRAG_BYTES, PK_FC, l, p.fc_j0 + i % p.fc_nj, i / p.fc_nj, lane);
     dst += (size_t)n_fc * FRAG_BYTES;
     for (int i = wid; i < n_p2; i += nwarp) pack_tile(a, dst + (size_t)i * FRAG_BYTES, PK_P2, l, i / p.fc_nj, p.fc_j0 + i % p.fc_nj, lane);

@@ -380,6 +380,28 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     def att_cost(k):
         return math.ceil(B * H * k / grid) * (1500 + 1300 * math.ceil(math.ceil(tmax / k) / 128)) + 80 * k
     nch = int(tune.get('nch', min(range(1, 17), key=lambda k: (att_cost(k), k))))
+    # One chunk per (sequence, head): the CTA that finishes an item also applies the head's 64 rows of the attention
+    # projection (streamed behind the item's K/V tiles) and adds the result into z1; the projection phase and its grid
+    # barrier disappear. With several chunks per pair the partial results have to be merged first, by a phase of its own.
+    fuse = bool(tune.get('fuse_proj', nch == 1))
+    if fuse:
+        nch = 1
+        fus = E // 16                                                    # fold tiles of one head
+        # the per-CTA streams lose their projection segment; the heads' slices follow them, one copy each (items of the
+        # same head on different CTAs read the same tiles: from L2 after the first)
+        base = 0
+        for c in range(grid):
+            rec[c, 4:8] = 0
+            layer = int(rec[c, 3]) * KT_D + int(rec[c, 9]) * KT_D + (D // 16) * int(rec[c, 9])
+            rec[c, 0], rec[c, 1] = base, layer
+            base += L * layer + int(rec[c, 11]) * KT_D
+        fuse_base = base
+        base += L * H * (D // 16) * fus
+        if base >= 2 ** 31:
+            raise NotImplementedError('packed weights exceed the 32-bit tile index')
+        tiles = base
+        umax = max(int(rec[:, 9].max()), fus)
+        notes = dict(notes, proj_units=B * H, proj_nk=fus, tiles_total=int(base))
     att_items = B * H * nch
     maxtl = math.ceil(att_items / grid) * math.ceil(math.ceil(tmax / nch) / 128)
     # K/V stages of 32 KB: two tiles in flight where a CTA has several per layer, one (and a deeper weight ring) otherwise
@@ -395,10 +417,10 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
 
     # shared memory: [weight ring | K/V stages | operand tiles | GELU operand tiles | partial sums | parameters | misc | barriers]
     ch = CHUNK_TILES
-    budget = SMEM_LIMIT - (8192 if timing else 0)
+    budget = SMEM_LIMIT - (9216 if timing else 0)
     prm_bytes = 10 * D + wn * 32               # gain and shift as fp32, two bias vectors as fp16
     misc_bytes = 2 * nw * (E + 2) * 4 + 8 * nw * 8 + 32 + 512 + 16 + maxtl * 16
-    fixed = kvst * 32768 + KT_D * 576 + _up(wn * 576, 128) + nw * wn * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
+    fixed = kvst * 32768 + KT_D * 576 + _up(max(wn, E // 16 if fuse else 0) * 576, 128) + nw * wn * 512 + _up(prm_bytes, 16) + _up(misc_bytes, 16)
     nslot = min((budget - fixed - 2 * kvst * 8 - 64) // (ch * 512 + 16), 16)
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget')
@@ -406,17 +428,17 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     sm_kv = sm_ring + nslot * ch * 512
     sm_act = sm_kv + kvst * 32768
     sm_gact = sm_act + KT_D * 576
-    sm_red = sm_gact + _up(wn * 576, 128)
+    sm_red = sm_gact + _up(max(wn, E // 16 if fuse else 0) * 576, 128)
     sm_prm = sm_red + nw * wn * 512
     sm_misc = sm_prm + _up(prm_bytes, 16)
     sm_bars = sm_misc + _up(misc_bytes, 16)
     shared = sm_bars + (2 * nslot + 2 * kvst) * 8
 
     scale = dims['scale']
-    defs = dict(V_NW=nw, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
+    defs = dict(V_NW=nw, V_NPROD=2, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
                 V_EPS=_f32(dims['eps']), V_SCALE=_f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5),
                 V_GELU_A=_f32(dims['gelu'][0]), V_GELU_B=_f32(dims['gelu'][1]), V_GELU_C=_f32(dims['gelu'][2]),
-                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_WN=wn, V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
+                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_WN=wn, V_FUSE_PROJ=int(fuse), V_FUSE_BASE=(fuse_base if fuse else 0), V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0,
                 V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q, V_OFF_PART=off_part, V_OFF_BEST=off_best,
@@ -437,7 +459,8 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
         (f'{q["$sc"]}, {q["$mx"]}, {q["$ex"]}, {q["$w"]}, {q["$o"]} (attention)',
          f'one item per (sequence, head, 1/{nch} of the positions), dealt round-robin over the CTAs, cut into tiles of 128 positions once per step; '
          f'K/V tiles by TMA ({kvst} stages), online softmax in registers, merged by the projection'),
-        (f'{q["$oo"]}, {q["$z1"]}', f'fold slices: {notes["proj_units"]} units of up to {WG} output tiles x {notes["proj_nk"]} fold tiles, whole output tiles per warp, fp32 atomics'),
+        (f'{q["$oo"]}, {q["$z1"]}', (f'per (sequence, head) item, by the CTA that finished its attention: the head\'s {E} rows of the projection x all output tiles, fp32 atomics into {q["$z1"]} (no phase of its own)' if fuse
+                                      else f'fold slices: {notes["proj_units"]} units of up to {WG} output tiles x {notes["proj_nk"]} fold tiles, whole output tiles per warp, fp32 atomics')),
         (f'{q["$m2"]}, {q["$v2"]}, {q["$b"]} (LN2)', ln_how),
         (f'{q["$u"]}, {q["$g"]}', f'whole fold, {min(rec[:, 9])}-{max(rec[:, 9])} f tiles per CTA, GELU in the epilogue, result stays in shared memory'),
         (f'{q["$z2"]}', 'fold slice = the CTA\'s own f tiles, whole output tiles per warp, fp32 atomics'),
@@ -447,10 +470,10 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     ]
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] + ['logits', 'finish']
     return Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
-                   barriers_per_launch=1 + 4 * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
-                   block=(nw + 1) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
+                   barriers_per_launch=1 + (3 if fuse else 4) * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
+                   block=(nw + 2) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
                    dims=dict(dims, B=B, NB=1, tmax=tmax, notes=notes, WG=WG, chunk_tiles=ch, tc=False, ksplit=False, kernel='small', warps=nw,
-                             nch=nch, kv_stages=kvst, ring_slots=nslot), roles=roles)
+                             nch=nch, kv_stages=kvst, ring_slots=nslot, fuse_proj=fuse, fuse_base=(fuse_base if fuse else 0)), roles=roles)
 
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
           grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None, row_seq=False):
