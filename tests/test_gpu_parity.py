@@ -16,7 +16,7 @@ def model(sh, seed, init, batch, tmax, **kw):
     return VestaGPT2(hf, batch=batch, tmax=tmax, **kw), hf
 
 
-def run_fixture(name, seqs=None):
+def run_fixture(name, seqs=None, tune=None):
     """teacher-forced decode of the fixture's sequences as one batch; every step's token and every
     kept step's logits against the reference interpreter's"""
     g = load(name)
@@ -24,7 +24,7 @@ def run_fixture(name, seqs=None):
     seqs = list(range(prompts.shape[0])) if seqs is None else seqs
     P = prompts.shape[1]
     steps = P + gen
-    m, _ = model(sh, seed, init, len(seqs), steps)
+    m, _ = model(sh, seed, init, len(seqs), steps, tune=tune)
     m.reset()
     feed = np.stack([teacher_tokens(g, i, P) for i in seqs])           # [B, steps]
     feed_d = torch.from_numpy(feed).cuda()
@@ -58,6 +58,38 @@ def test_tiny3_fixture_vocab_not_multiple_of_16():
 
 def test_gpt2_small_rich_init():
     run_fixture('gpt2_rich_b1')
+
+
+@pytest.mark.parametrize('name', ['tiny_b3', 'gpt2_rich_b1'])
+def test_fixed_point_sums_against_the_reference(name):
+    """tune={'ordered': True}: the state vectors as 64-bit fixed point, combined with integer atomics"""
+    run_fixture(name, tune=dict(ordered=True))
+
+
+@pytest.mark.parametrize('batch', [1, 8])
+def test_ordered_mode_gives_the_same_bits_on_every_run(batch):
+    """GPT-2 small: 16 prompt tokens and 64 free-running steps, twice from the same state. With fixed-point sums (integer
+    atomics: associative, so the arrival order of the partial sums does not matter) tokens, logits and the K/V cache of
+    the two runs are bit-identical; the reference reduces in a fixed order (vesta/lower.py:1045-1047) for the same end."""
+    from vesta_gpu_b200.shapes import GPT2_SMALL
+    from vesta_gpu_b200.synth import make_prompts
+    P, G = 16, 64
+    prompts = torch.from_numpy(make_prompts(GPT2_SMALL, batch, P, seed=7).copy()).cuda()
+    m, _ = model(GPT2_SMALL, 0, 'baseline', batch, P + G + 1, tune=dict(ordered=True))
+    assert m.low.dims['ordered']
+
+    def run():
+        m.reset()
+        for t in range(P):
+            m.x.copy_(prompts[:, t]); m.step()
+        toks = [m.x.clone()]
+        for _ in range(G):
+            m.step(); toks.append(m.x.clone())
+        m.k.check()
+        return torch.stack(toks, 1).clone(), m.logits().clone(), m.keys.clone(), m.vals.clone()
+    a, b = run(), run()
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
 
 
 def test_gpt2_small_batch1_config():

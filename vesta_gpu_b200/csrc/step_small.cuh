@@ -48,6 +48,29 @@
 
 extern __shared__ __align__(1024) unsigned char smem[];
 
+// The state vectors z (the sums the projections add into) are fp32, combined with floating-point atomics in arrival
+// order: the last bits of a sum then depend on the order. V_FIXED (lowering option `ordered`) keeps them as 64-bit
+// fixed point (36 fractional bits: finer than fp32 for |z| < 2^27) combined with integer atomics: integer addition is
+// associative, so every run gives the same bits whatever the order, at the price of 8-byte scalar atomics and loads.
+#if V_FIXED
+typedef long long zacc;
+#define ZSCALE 68719476736.0f
+__device__ __forceinline__ zacc to_acc(float v) { return __float2ll_rn(v * ZSCALE); }
+__device__ __forceinline__ float from_acc(zacc v) { return __ll2float_rn(v) * (1.0f / ZSCALE); }
+__device__ __forceinline__ void acc_add(zacc* p, float v) {
+    asm volatile("red.relaxed.gpu.global.add.u64 [%0], %1;" :: "l"(p), "l"(to_acc(v)) : "memory");
+}
+__device__ __forceinline__ float2 acc_load2(const zacc* p) {
+    const longlong2 v = __ldcg(reinterpret_cast<const longlong2*>(p));
+    return make_float2(from_acc(v.x), from_acc(v.y));
+}
+#else
+typedef float zacc;
+__device__ __forceinline__ zacc to_acc(float v) { return v; }
+__device__ __forceinline__ void acc_add(zacc* p, float v) { red_add(p, v); }
+__device__ __forceinline__ float2 acc_load2(const zacc* p) { return __ldcg(reinterpret_cast<const float2*>(p)); }
+#endif
+
 // shared memory: the offsets come from the lowering (V_SM_*); inside the last block:
 #define MISC_ATT 0                                   // 2 x NW x (V_E + 2) floats: the warps' partial results of an item
 #define MISC_BEST (2 * NW * (V_E + 2) * 4)           // 8 x NW u64
@@ -406,14 +429,14 @@ __device__ __forceinline__ float whole_fold_sum(const float* red, int o) {
 // consecutive outputs of sequence 2t + q % 2 in the tile's half q / 2. A 148-way sum at eight sequences is bound by the
 // number of atomic operations the L2 has to retire.
 // `only` >= 0: only that sequence's sums are added (the operand held one live row).
-__device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v)[4], int lane, int only) {
+__device__ __forceinline__ void red_tile(zacc* __restrict__ zu, const float (&v)[4], int lane, int only) {
     const int g = lane >> 2, t = lane & 3, q = g & 3;
-    if (V_B <= 2) {
-        // one or two sequences: only the lanes with t == 0 hold live sums; plain 4-byte atomics (measured: the
-        // transposition costs more than it saves here)
-        float* o = zu + (size_t)(2 * t) * V_D + g;
-        if (2 * t < V_B && (only < 0 || only == 2 * t)) { red_add(o, v[0]); red_add(o + 8, v[2]); }
-        if (2 * t + 1 < V_B && (only < 0 || only == 2 * t + 1)) { red_add(o + V_D, v[1]); red_add(o + V_D + 8, v[3]); }
+    if (V_B <= 2 || V_FIXED) {
+        // one or two sequences (only the lanes with t == 0 hold live sums: the transposition costs more than it
+        // saves, measured), or fixed-point sums: scalar atomics
+        zacc* o = zu + (size_t)(2 * t) * V_D + g;
+        if (2 * t < V_B && (only < 0 || only == 2 * t)) { acc_add(o, v[0]); acc_add(o + 8, v[2]); }
+        if (2 * t + 1 < V_B && (only < 0 || only == 2 * t + 1)) { acc_add(o + V_D, v[1]); acc_add(o + V_D + 8, v[3]); }
         return;
     }
     const bool odd = q & 1, hi = q & 2;
@@ -427,9 +450,11 @@ __device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v
     const float u0 = __shfl_xor_sync(0xffffffffu, t0, 8), u1 = __shfl_xor_sync(0xffffffffu, t1, 8);
     const float o0 = hi ? u0 : ax, o1 = hi ? u1 : ay, o2 = hi ? bx : u0, o3 = hi ? by : u1;
     const int b = 2 * t + (q & 1);
+#if !V_FIXED
     if (b < V_B && (only < 0 || only == b))
         asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
                      :: "l"(zu + (size_t)b * V_D + (g & ~3) + (hi ? 8 : 0)), "f"(o0), "f"(o1), "f"(o2), "f"(o3) : "memory");
+#endif
 }
 
 // A slice of US fold tiles for `nunits` output tiles (stream order: output tile major). Warp w takes the output
@@ -437,7 +462,7 @@ __device__ __forceinline__ void red_tile(float* __restrict__ zu, const float (&v
 // zt[b][unit * 16 + ...] with fp32 atomics (the other slices of the fold are other CTAs'). The operand tiles of
 // the slice are read once, into registers. One instance per US.
 template <int US>
-__device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nunits, int upc, const unsigned char* act, float* __restrict__ zt, int only) {
+__device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nunits, int upc, const unsigned char* act, zacc* __restrict__ zt, int only) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint4 bop[US];
 #pragma unroll
@@ -472,7 +497,7 @@ __device__ __noinline__ u32 gemm_fold_slice_n(u32 st, u32* bar, int cta, int nun
     }
     return st;
 }
-__device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, float* zt, int only = -1) {
+__device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nunits, int us, int upc, const unsigned char* act, zacc* zt, int only = -1) {
     switch (us) {
         case 1: return gemm_fold_slice_n<1>(st, bar, cta, nunits, upc, act, zt, only);
 #if UMAX >= 2
@@ -506,7 +531,7 @@ __device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nu
 // Several slots are taken at a time (the weight producer has had the whole attention phase to fill them): a warp then
 // runs one independent chain of products per slot, so the chains overlap instead of following one another.
 #define FUSE_GROUP (V_NSLOT - 1 < 6 ? V_NSLOT - 1 : 6)
-__device__ __noinline__ u32 proj_head(u32 st, u32* bar, int cta, float* __restrict__ z1, int only) {
+__device__ __noinline__ u32 proj_head(u32 st, u32* bar, int cta, zacc* __restrict__ z1, int only) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint4 bop[FUSE_US];
 #pragma unroll
@@ -612,7 +637,7 @@ __device__ __forceinline__ void split_h2(float x, float y, u32& hi, u32& lo) {
 #define LN_ROWS (V_B <= 1 ? 1 : V_B <= 2 ? 2 : V_B <= 4 ? 4 : 8)
 #define LN_WPR (NW / LN_ROWS)
 #define LNI ((KT_D + 8 * LN_WPR - 1) / (8 * LN_WPR))
-__device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restrict__ z, float* __restrict__ init) {
+__device__ __noinline__ void ln_to_act(int cta, int ncta, const zacc* __restrict__ z, zacc* __restrict__ init) {
     unsigned char* act = smem + V_SM_ACT;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned char* prm = smem + V_SM_PRM;
@@ -620,7 +645,7 @@ __device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restric
     const int u = lane >> 2, t = lane & 3;
     const int rb = warp / LN_WPR, wi = warp % LN_WPR;
     const bool live = rb < V_B;
-    const float* row = z + (size_t)rb * V_D + 2 * t;
+    const zacc* row = z + (size_t)rb * V_D + 2 * t;
     float2 v0[LNI], v1[LNI];
     float s = 0.f;
 #pragma unroll
@@ -628,8 +653,8 @@ __device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restric
         const int kt = u + 8 * (wi + LN_WPR * i);
         v0[i] = make_float2(0.f, 0.f); v1[i] = make_float2(0.f, 0.f);
         if (live && kt < KT_D) {
-            v0[i] = __ldcg(reinterpret_cast<const float2*>(row + kt * 16));
-            v1[i] = __ldcg(reinterpret_cast<const float2*>(row + kt * 16 + 8));
+            v0[i] = acc_load2(row + kt * 16);
+            v1[i] = acc_load2(row + kt * 16 + 8);
         }
     }
 #pragma unroll
@@ -679,9 +704,9 @@ __device__ __noinline__ void ln_to_act(int cta, int ncta, const float* __restric
             *reinterpret_cast<uint4*>(dst + kt * ATILE) = out;
             if (init && ((KT_D <= V_MAXGRID) ? (kt == cta) : ((kt % ncta) == cta))) {
                 const u32 i0 = *reinterpret_cast<const u32*>(prm + PRM_INIT + k * 2), i1 = *reinterpret_cast<const u32*>(prm + PRM_INIT + (k + 8) * 2);
-                float* o = init + (size_t)rb * V_D + k;
-                red_add(o, v0[i].x + h_lo(i0)); red_add(o + 1, v0[i].y + h_hi(i0));
-                red_add(o + 8, v1[i].x + h_lo(i1)); red_add(o + 9, v1[i].y + h_hi(i1));
+                zacc* o = init + (size_t)rb * V_D + k;
+                acc_add(o, v0[i].x + h_lo(i0)); acc_add(o + 1, v0[i].y + h_hi(i0));
+                acc_add(o + 8, v1[i].x + h_lo(i1)); acc_add(o + 9, v1[i].y + h_hi(i1));
             }
         }
     }
@@ -750,7 +775,7 @@ __device__ __forceinline__ void q_store(u16* __restrict__ qop16, int b, int jx, 
 }
 
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const u32* __restrict__ qbuf,
-                                                float* __restrict__ part, float* __restrict__ z1, int l, const int* s_pos) {
+                                                float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos) {
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
     if (ntl == 0) return;
@@ -1057,7 +1082,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
     float* red = reinterpret_cast<float*>(smem + V_SM_RED);
     const u16* tile_bias = reinterpret_cast<const u16*>(smem + V_SM_PRM + PRM_TILE);
     u64* wbest = reinterpret_cast<u64*>(smem + V_SM_MISC + MISC_BEST);
-    float* Z = a.S + V_OFF_Z;
+    zacc* Z = reinterpret_cast<zacc*>(a.S + V_OFF_Z);
     u32* qbuf = reinterpret_cast<u32*>(a.S + V_OFF_Q);
     float* part = a.S + V_OFF_PART;
     float* logit = a.S + V_OFF_LOGIT;
@@ -1076,8 +1101,8 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
         const int b = i / V_D, d = i - b * V_D;
-        Z[i] = h2f(a.wte[(size_t)__ldcg(a.x + b) * V_D + d]) + h2f(a.wpe[(size_t)max(s_pos[b], 0) * V_D + d]);
-        Z[ZS + i] = 0.f;
+        Z[i] = to_acc(h2f(a.wte[(size_t)__ldcg(a.x + b) * V_D + d]) + h2f(a.wpe[(size_t)max(s_pos[b], 0) * V_D + d]));
+        Z[ZS + i] = 0;
     }
     TICK(0);
     phase_end(c);
@@ -1088,9 +1113,9 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
 #pragma unroll 1
     for (int l = 0; l < V_L; l++) {
-        float* zin = Z + (size_t)((2 * l) % 3) * ZS;          // layer input
-        float* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
-        float* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
+        zacc* zin = Z + (size_t)((2 * l) % 3) * ZS;          // layer input
+        zacc* z1 = Z + (size_t)((2 * l + 1) % 3) * ZS;
+        zacc* z2 = Z + (size_t)((2 * l + 2) % 3) * ZS;
 #if V_TIMING
         if (c.tid == 0) trace_on = (c.cta == V_TIMING - 1) && (l == V_L / 2) && (step == 0);
 #endif
@@ -1102,7 +1127,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
             *seq = *seq + 1;
         }
 #pragma unroll 1
-        for (int i = gtid; i < V_B * V_D; i += gthreads) z2[i] = 0.f;      // the MLP adds into it two barriers later
+        for (int i = gtid; i < V_B * V_D; i += gthreads) z2[i] = 0;      // the MLP adds into it two barriers later
         ln_to_act(c.cta, c.ncta, zin, z1);                             // starts z1 = z + ob
         TRACE(10);
         if (p.qkv_nj) {
@@ -1164,7 +1189,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         // ---- LN2 + FC + GELU + MLP projection + residual
         TRACE(4);
 #pragma unroll 1
-        for (int i = gtid; i < V_B * V_D; i += gthreads) zin[i] = 0.f;     // the next layer's projection adds into it
+        for (int i = gtid; i < V_B * V_D; i += gthreads) zin[i] = 0;     // the next layer's projection adds into it
         ln_to_act(c.cta, c.ncta, z1, z2);                              // starts z2 = z1 + pb
         TRACE(13);
         if (p.fc_nj) {
@@ -1202,8 +1227,8 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #if V_TIMING
         if (c.tid == 0) trace_on = 0;
 #endif
-        float* zfin = Z + (size_t)((2 * V_L) % 3) * ZS;
-        ln_to_act(c.cta, c.ncta, zfin, (float*)0);
+        zacc* zfin = Z + (size_t)((2 * V_L) % 3) * ZS;
+        ln_to_act(c.cta, c.ncta, zfin, (zacc*)0);
         u64 best[2] = {0ull, 0ull};
         logits_phase(c, p, act, logit, best);
         // argmax: per row the max over the lanes that hold it (equal lane & 3), the warps, the CTAs
