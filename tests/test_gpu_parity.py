@@ -201,6 +201,40 @@ def test_against_oracle_other_batches(batch):
     m.k.check()
 
 
+@pytest.mark.parametrize('batch,ctx,tune', [(8, 3, None), (8, 40, None), (7, 40, dict(fuse_proj=False, nch=2)), (8, 40, dict(ordered=True)), (2, 40, None)])
+def test_more_attention_items_than_ctas_at_small_batch(batch, ctx, tune):
+    """twenty heads: 160 (sequence, head) pairs at eight sequences, so twelve CTAs hold two attention items per layer (and,
+    in the fused mode, apply the projection of two heads); short and longer contexts, the unfused mode with two position
+    chunks per pair, fixed-point sums; against the oracle on seeded caches"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import HEADS20 as sh
+    from vesta_gpu_b200.synth import make_cache
+    steps = 3
+    m, hf = model(sh, 17, 'rich', batch, ctx + steps, tune=tune)
+    assert m.low.dims['kernel'] == 'small'
+    W = O.upcast(hf.weights)
+    caches = []
+    m.reset()
+    for b in range(batch):
+        k0, v0 = make_cache(sh, 500 + b, ctx)
+        ck, cv = O.new_cache(sh, ctx + steps)
+        ck[:, :ctx] = k0; cv[:, :ctx] = v0
+        caches.append((ck, cv))
+        m.keys[b, :, :ctx].copy_(torch.from_numpy(k0)); m.vals[b, :, :ctx].copy_(torch.from_numpy(v0))
+    m.t.fill_(ctx)
+    x = np.array([(b * 37 + 5) % sh.N for b in range(batch)], np.int32)
+    for s_ in range(steps):
+        m.x.copy_(torch.from_numpy(x)); m.step()
+        lg, nx = m.logits().cpu().numpy(), m.next().cpu().numpy()
+        for b in range(batch):
+            ref, rn = O.step(sh, W, caches[b][0], caches[b][1], int(x[b]), ctx + s_)
+            assert np.abs(lg[b] - ref).max() < TIGHT, (s_, b)
+            if O.margin(ref) > MARGIN:
+                assert int(nx[b]) == rn
+            x[b] = rn
+    m.k.check()
+
+
 @pytest.mark.parametrize('batch,slab_tiles,tune', [
     (20, 1, None), (20, None, None), (9, 1, None), (33, 2, None),
     (20, 1, dict(ln_dist=True, act_lo=True)),          # rows normalised once on the grid, tiles through global memory

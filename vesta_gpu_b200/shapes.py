@@ -48,4 +48,7 @@ GPT2_XL = Shape('gpt2_xl', L=48, D=1600, H=25, E=64, F=6400, N=50257, C=1024)
 TINY = Shape('tiny', L=2, D=128, H=2, E=64, F=256, N=211, C=64)
 TINY3 = Shape('tiny3', L=3, D=192, H=3, E=64, F=320, N=333, C=96)
 
-SHAPES = {s.name: s for s in (GPT2_SMALL, GPT2_XL, TINY, TINY3)}
+# twenty heads on two layers: at eight sequences more (sequence, head) pairs than SMs, so CTAs hold several attention items
+HEADS20 = Shape('heads20', L=2, D=1280, H=20, E=64, F=512, N=517, C=48)
+
+SHAPES = {s.name: s for s in (GPT2_SMALL, GPT2_XL, TINY, TINY3, HEADS20)}
