@@ -277,14 +277,16 @@ def test_batches_above_one_slab(batch, slab_tiles, tune):
 @pytest.mark.parametrize('batch,tune', [
     (64, None),                                         # one slab of 64 sequences
     (70, None),                                         # two slabs, the second with six live rows
-    (130, dict(tcl_ks_proj=2, tcl_ks_p2=2)),            # three slabs; both projections split over the fold
-    (64, dict(tcl_ks_p2=4)),                            # the MLP projection one k-block per unit
+    (130, None),                                        # three row blocks of 64, the last with two live rows
+    (64, dict(tcl_rb=32)),                              # two row blocks of 32
+    (130, dict(tcl_rb=32, tcl_nw=16)),                  # five row blocks of 32 x units of 16 output columns
+    (64, dict(tcl_rb=64, tcl_nw=16)),                   # one row block: every CTA reads the operand of all 64 sequences
     (64, dict(tc_layers=False)),                        # the same batch with the layer contractions on mma.sync
 ])
 def test_tensor_core_layer_contractions(batch, tune):
-    """64 sequences and more at widths that are multiples of 128: QKV, attention projection, FC and MLP projection as
-    tcgen05 units (accumulators in tensor memory, weights from the packed operand image, operands written by the
-    previous phase as fp16 swizzled rows), against the oracle over several steps (K/V emit and attention included)"""
+    """64 sequences and more: QKV, attention projection, FC and MLP projection as tcgen05 units (a block of sequences as
+    the rows of the product, accumulators in tensor memory, weights from the packed operand image, operands written by
+    the previous phase as fp16 swizzled rows), against the oracle over several steps (K/V emit and attention included)"""
     from oracle import gpt2_numpy as O
     from vesta_gpu_b200.shapes import TINY
     from vesta_gpu_b200.synth import make_prompts

@@ -79,32 +79,39 @@ def test_every_weight_tile_exactly_once(sh, batch, grid):
 
 
 def test_tensor_core_weight_image_covers_every_weight_once():
-    """64 sequences and more at widths that are multiples of 128: the packed image of the layer weights is a list of
-    (m-tile of 128 output columns, k-block of 64 fold indices) tiles per layer and contraction (pack_body / tcl_* in
-    csrc/step_kernel.cuh restated); the units of a phase cover every (slab, m-tile, k-block) exactly once"""
-    for sh, B in ((GPT2_SMALL, 64), (GPT2_SMALL, 256), (TINY, 130)):
-        low = lower_for(sh, B, 64, tune=dict(ln_dist=True))
+    """64 sequences and more: the packed image of the layer weights is a list of (fold part, output block) blocks of
+    V_TCL_NW output columns x D fold indices per layer and contraction (pack_body / tcl_* in csrc/step_kernel.cuh
+    restated); the runs of units of the CTAs cover every (row block, fold part, output block) exactly once, the
+    operand of a row block fits the K/V stages and a unit's weights a whole number of ring slots"""
+    for sh, B, tune in ((GPT2_SMALL, 64, {}), (GPT2_SMALL, 256, {}), (TINY, 130, {}), (TINY, 130, dict(tcl_nw=16, tcl_rb=32))):
+        low = lower_for(sh, B, 64, tune=dict(tune, ln_dist=True))
         assert low.dims['tcl'] and low.dims['tc'] and low.dims['ksplit']
         D, F, L = sh.D, sh.F, sh.L
-        kbd, kbf = D // 64, F // 64
-        mt = {'qkv': 3 * D // 128, 'proj': D // 128, 'fc': F // 128, 'p2': D // 128}
-        ktot = {'qkv': kbd, 'proj': kbd, 'fc': kbd, 'p2': kbf}
-        first, t = {}, 0
-        for k in ('qkv', 'proj', 'fc', 'p2'):
-            first[k] = t
-            t += mt[k] * ktot[k]
-        assert low.packed_bytes == L * t * 16384 == 2 * L * (D * 3 * D + D * D + 2 * D * F)      # every weight element once
-        ks = {'qkv': 1, 'proj': define(low, 'V_TCL_KS_PROJ'), 'fc': 1, 'p2': define(low, 'V_TCL_KS_P2')}
-        slabs = (B + 63) // 64
-        for k in first:
-            nkb = ktot[k] // ks[k]
-            assert nkb * ks[k] == ktot[k] and nkb * 8192 <= define(low, 'V_KVST') * 32768       # a unit's operand fits the K/V stages
-            seen = np.zeros((slabs, mt[k], ktot[k]), np.int32)
-            for u in range(slabs * mt[k] * ks[k]):
-                slab, r = divmod(u, mt[k] * ks[k])
-                m, s_ = divmod(r, ks[k])
-                seen[slab, m, s_ * nkb:(s_ + 1) * nkb] += 1
+        rb_rows, nw = low.dims['tcl_unit']
+        assert rb_rows == define(low, 'V_TCL_RB') and nw == define(low, 'V_TCL_NW')
+        assert rb_rows == tune.get('tcl_rb', 64)
+        uk = D // 64
+        ub = nw * 128 * uk
+        nfb = {'qkv': 3 * D // nw, 'proj': D // nw, 'fc': F // nw, 'p2': D // nw}
+        nks = {'qkv': 1, 'proj': 1, 'fc': 1, 'p2': F // D}
+        assert low.packed_bytes == L * sum(nfb[k] * nks[k] for k in nfb) * ub == 2 * L * (D * 3 * D + D * D + 2 * D * F)   # every weight element once
+        slot = define(low, 'V_CH') * 512
+        spu = -(-ub // slot)
+        assert define(low, 'V_NSLOT') % spu == 0 and define(low, 'V_NSLOT') >= spu
+        assert uk * rb_rows * 128 <= define(low, 'V_KVST') * 32768                  # the operand of a row block fits the K/V stages
+        nrb = -(-B // rb_rows)
+        for k in nfb:
+            n = nrb * nks[k] * nfb[k]
+            seen = np.zeros((nrb, nks[k], nfb[k]), np.int32)
+            for cta in range(low.grid):
+                for u in range(cta * n // low.grid, (cta + 1) * n // low.grid):
+                    r, rest = divmod(u, nks[k] * nfb[k])
+                    s_, f_ = divmod(rest, nfb[k])
+                    seen[r, s_, f_] += 1
             assert seen.min() == 1 and seen.max() == 1
+    # 64 sequences at GPT-2 small: 72 QKV units of 64 sequences x 32 output columns (18 of 128 x 64 before)
+    low = lower_for(GPT2_SMALL, 64, 64, tune=dict(ln_dist=True))
+    assert -(-64 // low.dims['tcl_unit'][0]) * (3 * 768 // low.dims['tcl_unit'][1]) == 72
 
 
 def test_every_phase_has_the_smallest_possible_largest_share():

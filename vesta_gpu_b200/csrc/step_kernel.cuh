@@ -282,30 +282,43 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
 // ---------------------------------------------------------------------------------------------
 #define TC_SLABS_P ((V_B + 63) / 64)
 #if V_TCL
-// Layer contractions on the tensor cores (V_TCL: 64 sequences and more). A unit = one accumulator tile: 128 output
-// columns (m-tile) x one slab of 64 sequences x a run of k-blocks (64 fold indices each); units are dealt round-robin
-// over the CTAs. QKV and FC take the whole fold per unit (their epilogues need complete sums: bias, q / K / V emit,
-// GELU); the two projections split the fold V_TCL_KS_PROJ / V_TCL_KS_P2 ways and add into the vector the LayerNorm pass
-// started. The weights come from a packed copy in the shared-memory image of the operand (K-major rows of 128 bytes,
-// 128-byte swizzle), per layer [QKV | attn-proj | FC | MLP-proj], each ordered (m-tile, k-block).
-#define TCL_TILE_BYTES 16384
+// Layer contractions on the tensor cores (V_TCL: 64 sequences and more). The sequences are the rows of the tcgen05
+// product (operand A, M = 64 of which the first V_TCL_RB are a block of sequences: the rest of the accumulator is
+// never read), V_TCL_NW output columns of the weights its N. A unit = a block of V_TCL_RB sequences x V_TCL_NW
+// output columns x TCL_UK k-blocks of 64 fold indices (the whole fold of width V_D; the MLP projection, whose fold
+// is V_F, has V_F / V_D units per output block, their sums combined with atomics). Small units occupy all CTAs at
+// 64 sequences (QKV: 2 x 72 units), their weights (V_TCL_NW x V_D x 2 bytes, one bulk copy) are already in the ring
+// when the phase starts, and in the epilogue a thread holds consecutive output columns of one sequence: K / V
+// rows, GELU outputs and queries leave in 16-byte stores. Units are numbered (row block, fold part, output block)
+// and every CTA takes a contiguous run, so that its units share the operand of the row block.
+// The weights come from a packed copy in the shared-memory image of operand B (K-major rows of 128 bytes, 128-byte
+// swizzle): per layer [QKV | attn-proj | FC | MLP-proj], per (fold part, output block) TCL_UK tiles of V_TCL_NW rows.
 #define TCL_KB_D (V_D / 64)
 #define TCL_KB_F (V_F / 64)
-#define TCL_T_PROJ ((3 * V_D / 128) * TCL_KB_D)
-#define TCL_T_FC (TCL_T_PROJ + (V_D / 128) * TCL_KB_D)
-#define TCL_T_P2 (TCL_T_FC + (V_F / 128) * TCL_KB_D)
-#define TCL_T_LAYER (TCL_T_P2 + (V_D / 128) * TCL_KB_F)
-__device__ __forceinline__ int tcl_mt(int kind) { return kind == PH_QKV ? 3 * V_D / 128 : kind == PH_FC ? V_F / 128 : V_D / 128; }
-__device__ __forceinline__ int tcl_ks(int kind) { return kind == PH_PROJ ? V_TCL_KS_PROJ : kind == PH_P2 ? V_TCL_KS_P2 : 1; }
+#define TCL_UK TCL_KB_D                                        // k-blocks per unit
+#define TCL_UB (V_TCL_NW * 128 * TCL_UK)                       // bytes of a unit's weights
+#define TCL_SPU ((TCL_UB + V_CH * FRAG_BYTES - 1) / (V_CH * FRAG_BYTES))    // ring slots per unit
+#define TCL_A_KB (V_TCL_RB * 128)                              // bytes of the operand of a row block per k-block
+#define TCL_NRB ((V_B + V_TCL_RB - 1) / V_TCL_RB)
+#define TCL_W_PROJ (3 * V_D / V_TCL_NW)                        // weight blocks of a layer before the attention projection's
+#define TCL_W_FC (TCL_W_PROJ + V_D / V_TCL_NW)
+#define TCL_W_P2 (TCL_W_FC + V_F / V_TCL_NW)
+#define TCL_W_LAYER (TCL_W_P2 + (V_D / V_TCL_NW) * (TCL_KB_F / TCL_UK))
+__device__ __forceinline__ int tcl_nfb(int kind) { return kind == PH_QKV ? 3 * V_D / V_TCL_NW : kind == PH_FC ? V_F / V_TCL_NW : V_D / V_TCL_NW; }
+__device__ __forceinline__ int tcl_nks(int kind) { return kind == PH_P2 ? TCL_KB_F / TCL_UK : 1; }
 __device__ __forceinline__ int tcl_ktot(int kind) { return kind == PH_P2 ? TCL_KB_F : TCL_KB_D; }
-__device__ __forceinline__ int tcl_nkb(int kind) { return kind == PH_PROJ ? TCL_KB_D / V_TCL_KS_PROJ : kind == PH_P2 ? TCL_KB_F / V_TCL_KS_P2 : TCL_KB_D; }
-__device__ __forceinline__ int tcl_units(int kind) { return TC_SLABS_P * tcl_mt(kind) * tcl_ks(kind); }
-__device__ __forceinline__ int tcl_first_tile(int kind) { return kind == PH_QKV ? 0 : kind == PH_PROJ ? TCL_T_PROJ : kind == PH_FC ? TCL_T_FC : TCL_T_P2; }
-__device__ __forceinline__ void tcl_unit(int kind, int u, int& slab, int& mt, int& ks) {
-    const int per = tcl_mt(kind) * tcl_ks(kind);
-    slab = u / per;
-    const int r = u - slab * per;
-    mt = r / tcl_ks(kind); ks = r - mt * tcl_ks(kind);
+__device__ __forceinline__ int tcl_units(int kind) { return TCL_NRB * tcl_nks(kind) * tcl_nfb(kind); }
+__device__ __forceinline__ int tcl_first_block(int kind) { return kind == PH_QKV ? 0 : kind == PH_PROJ ? TCL_W_PROJ : kind == PH_FC ? TCL_W_FC : TCL_W_P2; }
+__device__ __forceinline__ void tcl_unit(int kind, int u, int& rb, int& ks, int& fb) {
+    const int per = tcl_nks(kind) * tcl_nfb(kind);
+    rb = u / per;
+    const int r = u - rb * per;
+    ks = r / tcl_nfb(kind); fb = r - ks * tcl_nfb(kind);
+}
+// the run of units of CTA `cta`
+__device__ __forceinline__ void tcl_run(int kind, int cta, int ncta, int& u0, int& u1) {
+    const int n = tcl_units(kind);
+    u0 = (int)(((long long)cta * n) / ncta); u1 = (int)(((long long)(cta + 1) * n) / ncta);
 }
 #endif
 #define TMAP_WTE 8                               // index of the embedding table's descriptor at TM (after the eight of K and V)
@@ -355,23 +368,24 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
 #endif
 #if V_TCL
         {
-            // the weight tiles (128 output columns x 64 k, 16 KB, the shared-memory image of the tensor-core operand) of
-            // this CTA's units, one per ring slot; the same tile serves every slab of 64 sequences (from L2 after the first)
-            const int nkb = tcl_nkb(first);
+            // the weights of this CTA's units, one bulk copy per unit into TCL_SPU consecutive ring slots (the first
+            // slot's barrier counts the bytes; the others are passed so that every slot keeps its turn)
+            int u0, u1;
+            tcl_run(first, cta, ncta, u0, u1);
 #pragma unroll 1
-            for (int u = cta; u < tcl_units(first); u += ncta) {
-                int slab, mt, ks;
-                tcl_unit(first, u, slab, mt, ks);
-                const unsigned char* src = WP + ((size_t)l * TCL_T_LAYER + tcl_first_tile(first) + (size_t)mt * tcl_ktot(first) + ks * nkb) * TCL_TILE_BYTES;
+            for (int u = u0; u < u1; u++) {
+                int rb, ks, fb;
+                tcl_unit(first, u, rb, ks, fb);
+                const unsigned char* src = WP + ((size_t)l * TCL_W_LAYER + tcl_first_block(first) + (size_t)ks * tcl_nfb(first) + fb) * TCL_UB;
+                const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
 #pragma unroll 1
-                for (int kb = 0; kb < nkb; kb++) {
-                    const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-                    wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
-                    if (c.dead) { producer_drain(c); return; }
-                    mbar_expect(full_bar(c, slot), TCL_TILE_BYTES);
-                    bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src + (size_t)kb * TCL_TILE_BYTES, TCL_TILE_BYTES, full_bar(c, slot));
-                    c.chunk++;
-                }
+                for (u32 i = 0; i < TCL_SPU; i++) wait_mbar(c, empty_bar(c, slot + i), (use & 1u) ^ 1u, 0x200u);
+                if (c.dead) { producer_drain(c); return; }
+                mbar_expect(full_bar(c, slot), TCL_UB);
+                bulk_g2s(smem_u32(smem + SM_RING) + slot * (V_CH * FRAG_BYTES), src, TCL_UB, full_bar(c, slot));
+#pragma unroll 1
+                for (u32 i = 1; i < TCL_SPU; i++) mbar_arrive(full_bar(c, slot + i));
+                c.chunk += TCL_SPU;
             }
             continue;
         }
@@ -975,12 +989,30 @@ __device__ __forceinline__ u64 tc_desc(u32 smem_addr) {
 // instruction descriptor: fp32 accumulate, fp16 A and B, both K-major, N = 64, M = 128
 #define TC_IDESC ((1u << 4) | ((u32)(TC_N >> 3) << 17) | ((u32)(TC_M >> 4) << 24))
 
-__device__ __forceinline__ void tc_mma(u32 d_tmem, u64 adesc, u64 bdesc, u32 accumulate) {
+__device__ __forceinline__ void tc_mma(u32 d_tmem, u64 adesc, u64 bdesc, u32 accumulate, u32 idesc = TC_IDESC) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate) : "memory");
+                 :: "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void tc_commit(u32 bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+// The four products of one k-block of 64, for a warp that walks here as a whole: every lane carries the (uniform)
+// descriptors, the lane that `elect_one` chose issues. Measured on B200 (48 products of 64 x 32 x 16 in a loop):
+// issued by thread 0 inside a divergent branch, or under a predicate computed as lane == 0, a product costs 65 to
+// 115 cycles (the descriptors pass from ordinary to uniform registers one by one); under the predicate of elect.sync
+// it costs what the tensor core takes to read its operands from shared memory at 128 bytes per cycle
+// ((rows of A + rows of B) x 32 bytes: 48 cycles at 128 x 64, 24 at 64 x 32). Polling warps beside it, more commits,
+// the operand addresses and the data made no difference.
+__device__ __forceinline__ u32 elect_one() {
+    u32 leader;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(leader));
+    return leader;
+}
+__device__ __forceinline__ void tc_mma_kb(u32 d_tmem, u64 adesc, u64 bdesc, bool first_kb, u32 idesc, u32 leader) {
+#pragma unroll
+    for (int k = 0; k < TC_KB / 16; k++)
+        asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\tsetp.ne.b32 q, %5, 0;\n\t@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                     :: "r"(d_tmem), "l"(adesc + 2 * k), "l"(bdesc + 2 * k), "r"(idesc), "r"((first_kb && k == 0) ? 0u : 1u), "r"(leader) : "memory");
 }
 
 // the normalised rows of the final state as operand B in global memory: row r of slab r / 64, block k / 64,
@@ -1043,6 +1075,8 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
     const int rows = P[PT_LOG_NJ] * 16, n0 = P[PT_LOG_J0] * 16;
     const int mtiles = (rows + TC_M - 1) / TC_M;
     const int quarter = c.warp & 3, col0 = (c.warp >> 2) * 32;       // this warp reads lanes 32*quarter.., columns col0..col0+31
+    const int wu = __shfl_sync(0xffffffffu, c.warp, 0);              // the warp index as a value the compiler knows to be uniform
+    const u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
 #pragma unroll 1
     for (int slab = 0; slab < TC_SLABS; slab++) {
         // operand B of the slab: one bulk copy per block of 64 k into the K/V stages
@@ -1058,19 +1092,46 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
         u64 mybest = 0;                                              // best (value, index) of sequence slab*64 + col0 + lane in this CTA's rows
 #pragma unroll 1
         for (int mt = 0; mt < mtiles; mt++) {
+#if V_TCL
+            // warp 0 alone waits for the slots and issues (see tc_contraction); the others meet it at the block barrier
+            if (wu == 0) {
+                const u32 leader = elect_one();
+#pragma unroll 1
+                for (int kb = 0; kb < TC_NKB; kb++) {
+                    const u32 slot = (c.chunk + kb) % V_NSLOT, use = (c.chunk + kb) / V_NSLOT;
+                    wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+                    const u32 slot_u = __shfl_sync(0xffffffffu, slot, 0);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    if (!(__shfl_sync(0xffffffffu, c.dead ? 1 : 0, 0) != 0)) {
+                        tc_mma_kb(tmem_u, tc_desc(smem_u32(c.smem + SM_RING) + slot_u * (V_CH * FRAG_BYTES)), tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128)),
+                                  kb == 0, TC_IDESC, leader);
+                        if (leader) {
+                            tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
+                            if (kb == TC_NKB - 1) tc_commit(tc_done_bar(c));
+                        }
+                    } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+                    __syncwarp();
+                }
+                wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u);
+            }
+            c.chunk += TC_NKB; c.tcd++;
+            cons_sync();
+#else
 #pragma unroll 1
             for (int kb = 0; kb < TC_NKB; kb++) {
                 const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
                 wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
-                if (c.warp == 0) {
-                    if (c.lane == 0 && !c.dead) {
+                if (wu == 0) {
+                    const u32 slot_u = __shfl_sync(0xffffffffu, slot, 0);
+                    if (!(__shfl_sync(0xffffffffu, c.dead ? 1 : 0, 0) != 0)) {
+                        const u32 leader = elect_one();
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                        const u64 ad = tc_desc(smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES));
-                        const u64 bd = tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128));
-#pragma unroll
-                        for (int k = 0; k < TC_KB / 16; k++) tc_mma(tmem, ad + 2 * k, bd + 2 * k, (kb | k) ? 1u : 0u);   // 32 bytes further per step of 16 k
-                        tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
-                        if (kb == TC_NKB - 1) tc_commit(tc_done_bar(c));
+                        tc_mma_kb(tmem_u, tc_desc(smem_u32(c.smem + SM_RING) + slot_u * (V_CH * FRAG_BYTES)), tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128)),
+                                  kb == 0, TC_IDESC, leader);                    // 32 bytes further per step of 16 k
+                        if (leader) {
+                            tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
+                            if (kb == TC_NKB - 1) tc_commit(tc_done_bar(c));
+                        }
                     } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
                     __syncwarp();
                 } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
@@ -1078,6 +1139,7 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
             }
             // the accumulators of this tile: thread = vocabulary row, registers = 32 sequences
             wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u); c.tcd++;
+#endif
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             u32 r[32];
             asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -1113,12 +1175,14 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
 }
 
 #if V_TCL
-// One layer contraction on the tensor cores: this CTA's units of `kind`, one after the other. Per unit: the operand of
-// its slab (64 sequences x the unit's k-blocks, fp16, K-major swizzled rows written to global memory by the previous
-// phase) is bulk-copied into the K/V stages, which are idle outside the attention phase; the weight tiles arrive in
-// the ring; one thread issues four tcgen05.mma (128 x 64 x 16) per k-block and commits them to the slot's empty
-// barrier, after the last k-block to the "done" barrier; then the eight warps read the accumulator (thread = output
-// column, registers = 32 sequences) and run the epilogue of the kind.
+// One layer contraction on the tensor cores: this CTA's run of units of `kind`, one after the other. Per unit: the
+// operand of its row block (V_TCL_RB sequences x TCL_UK k-blocks, fp16, K-major swizzled rows written to global memory
+// by the previous phase) is bulk-copied into the K/V stages, which are idle outside the attention phase, unless the
+// previous unit left it there; the unit's weights are in the ring (usually since before the phase started); one
+// lane issues 4 x TCL_UK tcgen05.mma (64 x V_TCL_NW x 16: rows beyond the row block read whatever follows it in
+// shared memory, their accumulator lanes are never read) and commits them to the slots' empty barriers and the
+// "done" barrier; then the warps whose quarter of the tensor-memory lanes holds sequences read the accumulator
+// (thread = sequence, 16 consecutive output columns) and run the epilogue of the kind.
 struct TclOut {
     const u16 *bias;                 // QKV / FC: bias of the layer (halves), 0 otherwise
     float* sum;                      // the projections: the vector their partial sums are added into
@@ -1127,82 +1191,138 @@ struct TclOut {
     unsigned char* gg;               // FC: GELU output as the operand of the MLP projection
     const int* s_pos;
 };
+#define TCL_M 64
+#define TCL_IDESC ((1u << 4) | ((u32)(V_TCL_NW >> 3) << 17) | ((u32)(TCL_M >> 4) << 24))
+#define TCL_EW (V_TCL_NW / 2)                      // output columns per epilogue thread: 8 or 16
+__device__ __forceinline__ void tcl_ld(u32 (&r)[16], u32 addr) {
+#if TCL_EW == 16
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+                   "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(addr) : "memory");
+#else
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(addr) : "memory");
+#endif
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// The products of one unit, issued by a whole warp (`leader` comes from elect_one).
+__device__ __forceinline__ void tcl_issue(u32 tmem, u32 a_addr, u32 b_addr, u32 leader) {
+    const u64 ad = tc_desc(a_addr), bd = tc_desc(b_addr);
+#pragma unroll 1
+    for (int kb = 0; kb < TCL_UK; kb++)
+        tc_mma_kb(tmem, ad + (u64)((kb * TCL_A_KB) >> 4), bd + (u64)((kb * (V_TCL_NW * 128)) >> 4), kb == 0, TCL_IDESC, leader);
+}
 __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const unsigned char* __restrict__ opb, const TclOut& o) {
     const u32 tmem = *reinterpret_cast<const volatile u32*>(c.smem + SM_MISC + MISC_TMEM);
-    const int nkb = tcl_nkb(kind), ktot = tcl_ktot(kind);
-    const int quarter = c.warp & 3, col0 = (c.warp >> 2) * 32;       // this warp reads lanes 32*quarter.., columns col0..col0+31
+    const int ktot = tcl_ktot(kind);
+    // A product of 64 rows leaves row m in tensor-memory lane 32 * (m / 16) + m % 16: the first 16 lanes of a warp's
+    // quarter hold sequences, the others nothing.
+    const int quarter = c.warp & 3, col0 = (c.warp >> 2) * TCL_EW;   // this warp reads lanes 32*quarter.., columns col0..col0+TCL_EW-1
+    const int wu = __shfl_sync(0xffffffffu, c.warp, 0);              // the warp index as a value the compiler knows to be uniform
+    const u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+    int u0, u1, staged = -1;
+    tcl_run(kind, c.cta, c.ncta, u0, u1);
 #pragma unroll 1
-    for (int u = c.cta; u < tcl_units(kind); u += c.ncta) {
-        int slab, mt, ks;
-        tcl_unit(kind, u, slab, mt, ks);
-        if (c.tid == 0) {
-            asm volatile("fence.proxy.async.global;" ::: "memory");          // the operand was written by other CTAs with ordinary stores
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect(tc_load_bar(c), (u32)nkb * (TC_N * 128));
+    for (int u = u0; u < u1; u++) {
+        int rb, ks, fb;
+        tcl_unit(kind, u, rb, ks, fb);
+        // Warp 0 alone waits (for the operand, the weights and the products) and issues; the others go straight to the
+        // block barrier below.
+        const bool load = (rb * 64 + ks != staged);                          // (row block, fold part) of the operand in the stages
+        staged = rb * 64 + ks;
+        const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
+        if (wu == 0) {
+            if (load) {
+                if (c.lane == 0) {
+                    asm volatile("fence.proxy.async.global;" ::: "memory");      // the operand was written by other CTAs with ordinary stores
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_expect(tc_load_bar(c), (u32)TCL_UK * TCL_A_KB);
+                    // rows rb * V_TCL_RB .. of slab (rb * V_TCL_RB) / 64: V_TCL_RB rows of 128 bytes inside every 64-row k-block tile
+                    const unsigned char* src = opb + ((size_t)((rb * V_TCL_RB) / 64) * ktot + (size_t)ks * TCL_UK) * (TC_N * 128) + ((rb * V_TCL_RB) % 64) * 128;
 #pragma unroll 1
-            for (int kb = 0; kb < nkb; kb++)
-                bulk_g2s(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128), opb + ((size_t)slab * ktot + ks * nkb + kb) * (TC_N * 128), TC_N * 128, tc_load_bar(c));
-        }
-        wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u); c.tcl++;
-        TRACE(60);
-#pragma unroll 1
-        for (int kb = 0; kb < nkb; kb++) {
-            const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
-            wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
-            if (c.warp == 0) {
-                if (c.lane == 0 && !c.dead) {
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const u64 ad = tc_desc(smem_u32(c.smem + SM_RING) + slot * (V_CH * FRAG_BYTES));
-                    const u64 bd = tc_desc(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128));
-#pragma unroll
-                    for (int k = 0; k < TC_KB / 16; k++) tc_mma(tmem, ad + 2 * k, bd + 2 * k, (kb | k) ? 1u : 0u);
-                    tc_commit(empty_bar(c, slot));               // the slot is free once these products have read it
-                    if (kb == nkb - 1) tc_commit(tc_done_bar(c));
-                } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
+                    for (int kb = 0; kb < TCL_UK; kb++)
+                        bulk_g2s(smem_u32(c.smem + SM_KV) + kb * TCL_A_KB, src + (size_t)kb * (TC_N * 128), TCL_A_KB, tc_load_bar(c));
+                }
                 __syncwarp();
-            } else if (c.lane == 0) mbar_arrive(empty_bar(c, slot));
-            c.chunk++;
-        }
-        wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u); c.tcd++;
-        TRACE(61);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        u32 r[32];
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-                       "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
-                       "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                     : "r"(tmem + ((u32)(quarter * 32) << 16) + (u32)col0) : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int j = mt * 128 + quarter * 32 + c.lane;                      // this thread's output column
-        if (!c.dead) {
-            if (kind == PH_QKV) {
-                const float bias = h2f(o.bias[(size_t)l * 3 * V_D + j]);
-                const int part = j / V_D, jj = j - part * V_D;               // 0: query, 1: key, 2: value
+                wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u);
+            }
+            TRACE(60);
+            wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
+            TRACE(63);
+            const bool dead_u = __shfl_sync(0xffffffffu, c.dead ? 1 : 0, 0) != 0;
+            if (!dead_u) {
+                const u32 leader = elect_one();
+                const u32 slot_u = __shfl_sync(0xffffffffu, slot, 0);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                tcl_issue(tmem_u, smem_u32(c.smem + SM_KV), smem_u32(c.smem + SM_RING) + slot_u * (V_CH * FRAG_BYTES), leader);
+                if (leader) {
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int b = slab * TC_N + col0 + i;
-                    const float v = __uint_as_float(r[i]) + bias;
-                    if (b < V_B) {
-                        if (part == 0) o.q[(size_t)b * V_D + jj] = v;
-                        else if (o.s_pos[b] >= 0) (part == 1 ? o.keys : o.vals)[((size_t)(SEQ_OF(o.s_pos, b) * V_L + l) * V_TMAX + o.s_pos[b]) * V_D + jj] = f2h(v);
+                    for (u32 i = 0; i < TCL_SPU; i++) tc_commit(empty_bar(c, slot + i));     // the slots are free once these products have read them
+                    tc_commit(tc_done_bar(c));
+                }
+            } else if (c.lane == 0) {
+#pragma unroll
+                for (u32 i = 0; i < TCL_SPU; i++) mbar_arrive(empty_bar(c, slot + i));
+            }
+            __syncwarp();
+            TRACE(64);
+            wait_mbar(c, tc_done_bar(c), c.tcd & 1u, 0x700u);
+            TRACE(61);
+        }
+        if (load) c.tcl++;
+        c.tcd++;
+        c.chunk += TCL_SPU;
+        cons_sync();                                                         // the products are done (warp 0 saw them complete)
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (quarter * 16 < V_TCL_RB && !c.dead) {
+            u32 r[16];
+            tcl_ld(r, tmem + ((u32)(quarter * 32) << 16) + (u32)col0);
+            const int row = rb * V_TCL_RB + quarter * 16 + c.lane;           // this thread's sequence (row of the batch) where lane < 16
+            const int j = fb * V_TCL_NW + col0;                              // its first output column
+            if (c.lane < 16 && row < V_B) {
+                if (kind == PH_QKV || kind == PH_FC) {
+                    const u16* bp = o.bias + (size_t)l * (kind == PH_QKV ? 3 * V_D : V_F) + j;
+#pragma unroll
+                    for (int i = 0; i < TCL_EW; i += 8) {
+                        const uint4 hb = __ldg(reinterpret_cast<const uint4*>(bp + i));
+                        r[i + 0] = __float_as_uint(__uint_as_float(r[i + 0]) + h_lo(hb.x)); r[i + 1] = __float_as_uint(__uint_as_float(r[i + 1]) + h_hi(hb.x));
+                        r[i + 2] = __float_as_uint(__uint_as_float(r[i + 2]) + h_lo(hb.y)); r[i + 3] = __float_as_uint(__uint_as_float(r[i + 3]) + h_hi(hb.y));
+                        r[i + 4] = __float_as_uint(__uint_as_float(r[i + 4]) + h_lo(hb.z)); r[i + 5] = __float_as_uint(__uint_as_float(r[i + 5]) + h_hi(hb.z));
+                        r[i + 6] = __float_as_uint(__uint_as_float(r[i + 6]) + h_lo(hb.w)); r[i + 7] = __float_as_uint(__uint_as_float(r[i + 7]) + h_hi(hb.w));
                     }
                 }
-            } else if (kind == PH_FC) {
-                const float bias = h2f(o.bias[(size_t)l * V_F + j]);
-                unsigned char* dst = o.gg + ((size_t)slab * TCL_KB_F + (j >> 6)) * (TC_N * 128) + (j & 7) * 2;
-                const int piece = (j & 63) >> 3;
+                if (kind == PH_QKV) {
+                    const int part = j / V_D, jj = j - part * V_D;           // 0: query, 1: key, 2: value (a unit never straddles two)
+                    if (part == 0) {
+                        float4* dst = reinterpret_cast<float4*>(o.q + (size_t)row * V_D + jj);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int rb = col0 + i;
-                    const float v = __uint_as_float(r[i]) + bias;
-                    const float g = gelu_tanh(v);
-                    *reinterpret_cast<u16*>(dst + rb * 128 + ((piece ^ (rb & 7)) << 4)) = f2h(g);
-                }
-            } else {
+                        for (int i = 0; i < TCL_EW; i += 4)
+                            dst[i >> 2] = make_float4(__uint_as_float(r[i]), __uint_as_float(r[i + 1]), __uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                    } else if (o.s_pos[row] >= 0) {
+                        uint4* dst = reinterpret_cast<uint4*>((part == 1 ? o.keys : o.vals) + ((size_t)(SEQ_OF(o.s_pos, row) * V_L + l) * V_TMAX + o.s_pos[row]) * V_D + jj);
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const int b = slab * TC_N + col0 + i;
-                    if (b < V_B) red_add(o.sum + (size_t)b * V_D + j, __uint_as_float(r[i]));
+                        for (int i = 0; i < TCL_EW; i += 8)
+                            dst[i >> 3] = make_uint4(pack_h2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), pack_h2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3])),
+                                                     pack_h2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5])), pack_h2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7])));
+                    }
+                } else if (kind == PH_FC) {
+                    const int rs = row & 63;                                 // row inside its slab of 64
+                    unsigned char* dst = o.gg + ((size_t)(row >> 6) * TCL_KB_F + (j >> 6)) * (TC_N * 128) + rs * 128;
+#pragma unroll
+                    for (int i = 0; i < TCL_EW; i += 8) {
+                        const int piece = ((j + i) & 63) >> 3;
+                        float g[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) g[e] = gelu_tanh(__uint_as_float(r[i + e]));
+                        *reinterpret_cast<uint4*>(dst + ((piece ^ (rs & 7)) << 4)) =
+                            make_uint4(pack_h2(g[0], g[1]), pack_h2(g[2], g[3]), pack_h2(g[4], g[5]), pack_h2(g[6], g[7]));
+                    }
+                } else {
+                    float* dst = o.sum + (size_t)row * V_D + j;
+#pragma unroll
+                    for (int i = 0; i < TCL_EW; i += 4)
+                        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     :: "l"(dst + i), "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])), "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])) : "memory");
                 }
             }
         }
@@ -1282,7 +1402,8 @@ __device__ __forceinline__ void step_body(const Args& a) {
     if (c.tid == 0) {
         *stop = 0;
         if (c.cta == 0) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" :: "l"(a.bar + BAR_STEP), "r"(0u) : "memory");   // nobody reads it before the first barrier
-        for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), NW); }
+        // (with tensor-core layer contractions nothing but tensor-core products reads the ring: their commit is the one arrival)
+        for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), V_TCL ? 1 : NW); }
         for (int s = 0; s < V_KVST; s++) { mbar_init(kv_bar(c, s), 1); mbar_init(kv_empty_bar(c, s), NW); }
         *reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ) = 0;
         mbar_init(tc_load_bar(c), 1); mbar_init(tc_done_bar(c), 1);
@@ -1723,20 +1844,21 @@ __device__ int pack_segment(const PackArgs& a, unsigned char* dst, const int* __
 
 #if V_TCL
 // The weight image of the tensor-core layer contractions: per layer [QKV | attn-proj | FC | MLP-proj], each a list of
-// (m-tile, k-block) tiles of 128 output columns x 64 fold indices in the shared-memory layout of a K-major operand with
-// the 128-byte swizzle: row r (one output column) = 128 bytes at r * 128, its 16-byte piece p stored at p ^ (r % 8).
-// One block per tile and pass over the grid; the logits read the embedding table itself (by TMA), nothing is packed
-// for them.
+// (fold part, output block) blocks of TCL_UK tiles; a tile = V_TCL_NW output columns x 64 fold indices in the
+// shared-memory layout of a K-major operand with the 128-byte swizzle: row r (one output column) = 128 bytes at
+// r * 128, its 16-byte piece p stored at p ^ (r % 8). One block of threads per weight block and pass over the grid;
+// the logits read the embedding table itself (by TMA), nothing is packed for them.
 __device__ void pack_body(const PackArgs& a) {
-    for (int tile = blockIdx.x; tile < V_L * TCL_T_LAYER; tile += gridDim.x) {
-        const int l = tile / TCL_T_LAYER, t = tile - l * TCL_T_LAYER;
-        const int kind = t < TCL_T_PROJ ? PH_QKV : t < TCL_T_FC ? PH_PROJ : t < TCL_T_P2 ? PH_FC : PH_P2;
-        const int i = t - tcl_first_tile(kind), mt = i / tcl_ktot(kind), kb = i - mt * tcl_ktot(kind);
-        unsigned char* dst = a.WP + (size_t)tile * TCL_TILE_BYTES;
-        for (int e = threadIdx.x; e < 128 * 64; e += blockDim.x) {
+    for (int blk = blockIdx.x; blk < V_L * TCL_W_LAYER; blk += gridDim.x) {
+        const int l = blk / TCL_W_LAYER, t = blk - l * TCL_W_LAYER;
+        const int kind = t < TCL_W_PROJ ? PH_QKV : t < TCL_W_FC ? PH_PROJ : t < TCL_W_P2 ? PH_FC : PH_P2;
+        const int i = t - tcl_first_block(kind), ks = i / tcl_nfb(kind), fb = i - ks * tcl_nfb(kind);
+        unsigned char* dst = a.WP + (size_t)blk * TCL_UB;
+        for (int e = threadIdx.x; e < V_TCL_NW * 64 * TCL_UK; e += blockDim.x) {
             // consecutive threads take consecutive output columns: the weights are stored with the output index contiguous
-            const int r = e & 127, k = e >> 7;
-            *reinterpret_cast<u16*>(dst + r * 128 + ((((k >> 3) ^ (r & 7))) << 4) + (k & 7) * 2) = w_elem(a, kind, l, mt * 128 + r, kb * 64 + k);
+            const int r = e % V_TCL_NW, kk = e / V_TCL_NW, kb = kk >> 6, k = kk & 63;
+            *reinterpret_cast<u16*>(dst + (size_t)kb * (V_TCL_NW * 128) + r * 128 + ((((k >> 3) ^ (r & 7))) << 4) + (k & 7) * 2) =
+                w_elem(a, kind, l, fb * V_TCL_NW + r, (ks * TCL_UK + kb) * 64 + k);
         }
     }
 }

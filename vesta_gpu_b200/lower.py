@@ -594,20 +594,26 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     ksplit = bool(tune.get('ksplit', B >= 32) and _nk <= KT_D and _groups <= grid)
     # Tensor cores (tcgen05, accumulators in tensor memory) where the contractions are dense: 64 sequences and more.
     # The logits as tiles of 128 vocabulary rows x 64 sequences (the fp16 operand of 64 sequences, 64 x D x 2 bytes,
-    # takes the place of the K/V stages, a 128 x 64 tile of the table one ring slot); the four layer contractions as
-    # units of 128 output columns x 64 sequences x a run of 64-wide k-blocks from a packed weight image (where the
-    # widths are multiples of 128 and the operand of a unit, at most kvst x 4 k-blocks, fits the K/V stages): QKV and
-    # FC over the whole fold, the two projections split so that a unit's operand fits.
+    # takes the place of the K/V stages, a 128 x 64 tile of the table one ring slot). The four layer contractions with
+    # the sequences as the rows of the product: units of a block of `tcl_rb` sequences (64; 32 measured slower at 64 sequences)
+    # x `tcl_nw` output columns (32) x the D / 64 k-blocks of a fold of width D (the MLP projection in F / D parts,
+    # combined with atomics), from a packed weight image; where the operand of a row block fits the K/V stages and a
+    # unit's weights a whole number of ring slots (which divides the slots a logits tile row takes, so that a unit never
+    # wraps around the ring). Measured on B200 against units of 128 output columns x 64 sequences
+    # (18 to 24 units per phase at 64 sequences, the other CTAs waiting): see the profile of batch 64.
     tc = bool(tune.get('tc', True) and B >= 64 and ln_dist and not act_lo and D % 64 == 0
               and 64 * D * 2 <= kvst * 2 * NW * 16 * 128 and ch * 512 == 16384)
     kbd, kbf = D // 64, F // 64
-    tcl = bool(tc and tune.get('tc_layers', True) and D % 128 == 0 and F % 128 == 0 and kbd <= kvst * 4 and ksplit)
-    ks_proj = ks_p2 = 1
-    if tcl:
-        ks_proj = int(tune.get('tcl_ks_proj', 2 if kbd % 2 == 0 and kbd >= 4 else 1))
-        ks_p2 = int(tune.get('tcl_ks_p2', min(k for k in range(1, kbf + 1) if kbf % k == 0 and kbf // k <= min(kvst * 4, kbd))))
-        if kbd % ks_proj or kbf % ks_p2 or kbf // ks_p2 > kvst * 4:
-            raise ValueError('tcl_ks_proj / tcl_ks_p2 must divide the k-blocks of the fold and leave an operand that fits the K/V stages')
+    tcl_nw = int(tune.get('tcl_nw', 32))
+    tcl_rb = int(tune.get('tcl_rb', 64))
+    if tcl_nw not in (16, 32) or tcl_rb not in (32, 64):
+        raise ValueError('tcl_nw must be 16 or 32, tcl_rb 32 or 64')
+    tcl_spu = -(-(tcl_nw * 128 * kbd) // 16384)
+    # (the product reads 64 rows from the start of every k-block of the operand: the last one reaches past the stages,
+    # into the operand tiles of the mma.sync path, which this mode leaves unused)
+    kv_bytes = kvst * 2 * NW * 16 * 128
+    tcl = bool(tc and tune.get('tc_layers', True) and D % tcl_nw == 0 and F % D == 0 and kbd % tcl_spu == 0 and kbd * tcl_rb * 128 <= kv_bytes
+               and (kbd - 1) * tcl_rb * 128 + 8192 <= kv_bytes + KT_D * atile and ksplit)
     rec, tiles, notes = place_step(dims, grid, ksplit)
     if tcl:
         NB = 1          # the mma.sync operand tiles are not used: their shared memory goes to the weight ring
@@ -658,6 +664,10 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     if nslot < 2:
         raise NotImplementedError('model too wide for the shared-memory budget at this batch')
     nslot = min(nslot, 16)
+    if tcl:
+        nslot = nslot // tcl_spu * tcl_spu          # a unit's weights take tcl_spu consecutive slots and never wrap
+        if nslot < tcl_spu:
+            raise NotImplementedError('the weights of a tensor-core unit do not fit the ring')
     shared = fixed + nslot * (ch * 512 + 16) + 512
 
     def f32(v):
@@ -668,7 +678,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_ROWSEQ=int(bool(row_seq)), V_BSEQ=bseq, V_TCL=int(tcl), V_TCL_KS_PROJ=ks_proj, V_TCL_KS_P2=ks_p2, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_ROWSEQ=int(bool(row_seq)), V_BSEQ=bseq, V_TCL=int(tcl), V_TCL_NW=tcl_nw, V_TCL_RB=tcl_rb, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     params, pack_params, tail = _entry_points(res, roles, fb, prompt_len, row_seq)
@@ -701,7 +711,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     low = Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
                   barriers_per_launch=1 + (4 + int(ksplit)) * L + ((2 * L + 1) if ln_dist else 0), plan=plan, sites=sites, counters=32 + max(grid, 1024),
                   block=(NW + 1) * 32, grid=grid, place=rec, pack_params=pack_params,
-                  packed_bytes=(L * ((3 * D // 128 + D // 128 + F // 128) * kbd + (D // 128) * kbf) * 16384) if tcl else tiles * 512,
+                  packed_bytes=(L * (3 * D + D + F + D * (F // D)) // tcl_nw * (tcl_nw * 128 * kbd)) if tcl else tiles * 512,
                   dims=dict(dims, B=B, NB=NB, tmax=tmax, notes=notes, WG=wg, chunk_tiles=ch, tc=tc, ksplit=ksplit, tcl=tcl,
-                            tcl_ks=(ks_proj, ks_p2), kernel='large'), roles=roles)
+                            tcl_unit=(tcl_rb, tcl_nw), kernel='large'), roles=roles)
     return low
