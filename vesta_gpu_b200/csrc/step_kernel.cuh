@@ -205,6 +205,7 @@ __device__ __forceinline__ void phase_wait(Ctx& c) {
 #define KV_STAGE_BYTES (2 * KV_TILE_BYTES)       // K rows then V rows
 #define TMAP_BYTES 128                           // descriptors at TM: K, V with boxes of 32 rows, of 64, of 96, of 128; then the embedding table
 
+#if !V_TCL
 struct AttIter { int it, s, hi, b, h; };         // item index, next position, end of its chunk
 
 // (sequence, head), chunk and chunk count of item `it`
@@ -229,6 +230,50 @@ __device__ __forceinline__ void att_advance(AttIter& a, const int* s_pos, int nc
     a.s += KV_POS;
     if (a.s >= a.hi) { a.it += ncta; att_load_item(a, s_pos, ncta); }
 }
+__device__ __forceinline__ void att_begin(AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta) { a.it = cta; att_load_item(a, s_pos, ncta); }
+__device__ __forceinline__ void att_advance(AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta) { att_advance(a, s_pos, ncta); }
+// the item after the current one of this CTA, as (sequence, head); false when there is none
+__device__ __forceinline__ bool att_peek(const AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta, int& b, int& h) {
+    if (a.it + ncta >= ATT_ITEMS) return false;
+    int ch, nch;
+    att_item(a.it + ncta, b, h, ch, nch);
+    return true;
+}
+#else
+// With tensor-core layer contractions (64 sequences and more, one work item per (sequence, head)) the items are dealt
+// by length: the sequences are ranked by context length at the start of every step (longest first; the ranks live in
+// the unused mma.sync operand tiles), the items in (rank, head) order go round-robin over the CTAs, every other round
+// in reverse, so that the sums of lengths per CTA stay close whatever the contexts are (the items of the last,
+// partial round are the shortest); the heads of a sequence still run on neighbouring CTAs at the same time (they
+// share the rows of the cache). Consumer warps and the producer thread walk the items the same way.
+// Measured and not kept: ranges of a cost line per CTA (contiguous items: 23 % slower, the CTAs no longer read the
+// same cache rows at the same time), and cutting the items of the last round into runs of tiles merged by the CTA
+// that finishes last (no gain at 64 sequences: a run costs its fixed part again).
+struct AttIter { int r, b, h, s, hi; };
+__device__ __forceinline__ int* att_order(unsigned char* smem) { return reinterpret_cast<int*>(smem + SM_ACT); }
+__device__ __forceinline__ bool att_valid(const AttIter& a) { return a.r >= 0; }
+__device__ __forceinline__ void att_load_item(AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta) {
+    // (the grid is the lowered one: the placement of the weights depends on it too)
+    const int i = a.r * V_MAXGRID + (((a.r & 1) && V_ATT_SNAKE) ? V_MAXGRID - 1 - cta : cta);
+    if (i >= V_B * V_H) { a.r = -1; return; }
+    const int sb = i / V_H;
+    a.h = i - sb * V_H; a.b = att_order(smem)[sb];
+    a.s = 0; a.hi = max(s_pos[a.b] + 1, 0);
+}
+__device__ __forceinline__ bool att_has_rows(const AttIter& a) { return a.hi > a.s; }      // a sequence that has not started: an item without data
+__device__ __forceinline__ void att_advance(AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta) {
+    a.s += KV_POS;
+    if (a.s >= a.hi) { a.r++; att_load_item(a, smem, s_pos, cta, ncta); }
+}
+__device__ __forceinline__ void att_begin(AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta) { a.r = 0; att_load_item(a, smem, s_pos, cta, ncta); }
+__device__ __forceinline__ bool att_peek(const AttIter& a, unsigned char* smem, const int* s_pos, int cta, int ncta, int& b, int& h) {
+    AttIter n = a;
+    n.r++;
+    att_load_item(n, smem, s_pos, cta, ncta);
+    b = n.b; h = n.h;
+    return att_valid(n);
+}
+#endif
 __device__ __forceinline__ u32 kv_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + stage) * 8; }
 __device__ __forceinline__ u32 kv_empty_bar(const Ctx& c, u32 stage) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST + 2 + stage) * 8; }
 
@@ -254,8 +299,8 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
         }
         __threadfence_block();
     }
-    AttIter a; a.it = c.cta;
-    att_load_item(a, s_pos, ncta);
+    AttIter a;
+    att_begin(a, c.smem, s_pos, c.cta, ncta);
 #pragma unroll 1
     while (att_valid(a) && !c.dead) {
         if (att_has_rows(a)) {
@@ -273,7 +318,7 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
             tma_rows(dst + KV_TILE_BYTES, TM + (2 * q + 1) * TMAP_BYTES, a.h * V_E, a.s, SEQ_OF(s_pos, a.b) * V_L + l, bar);
             c.kvi++;
         }
-        att_advance(a, s_pos, ncta);
+        att_advance(a, c.smem, s_pos, c.cta, ncta);
     }
 }
 
@@ -781,11 +826,31 @@ __device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* 
     }
 }
 
+#if V_TCL
+// The sequences ranked by context length, longest first (ties by index): order[rank] = sequence. Rebuilt when the
+// positions of a step are known; every thread ranks its sequences against all (the positions are read as broadcasts
+// from shared memory). All consumer warps; ends with a block-wide sync.
+__device__ __noinline__ void att_plan(Ctx& c, const int* s_pos) {
+    int* order = att_order(c.smem);
+#pragma unroll 1
+    for (int b = c.tid; b < V_B; b += NCONS) {
+        const int n = s_pos[b];
+        int rank = 0;
+#pragma unroll 4
+        for (int o = 0; o < V_B; o++) { const int m = s_pos[o]; rank += (m > n || (m == n && o < b)) ? 1 : 0; }
+        order[rank] = b;
+    }
+    __threadfence_block();
+    cons_sync();
+}
+
+#endif
+
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const float* __restrict__ qbuf,
                                                 float* __restrict__ part, int l, const int* s_pos, const unsigned char* __restrict__ TM, unsigned char* __restrict__ og) {
     const int g = c.lane >> 2, t = c.lane & 3;
     AttIter cur, pf;
-    cur.it = c.cta; att_load_item(cur, s_pos, c.ncta);
+    att_begin(cur, c.smem, s_pos, c.cta, c.ncta);
     if (!att_valid(cur)) return;
     u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
 #pragma unroll
@@ -812,7 +877,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 }
                 n++;
             }
-            att_advance(pf, s_pos, c.ncta);
+            att_advance(pf, c.smem, s_pos, c.cta, c.ncta);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
@@ -827,12 +892,10 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     while (att_valid(cur)) {
         if (V_B <= 16) TRACE(44);
         const bool last = cur.s + KV_POS >= cur.hi;
-        const int next_it = cur.it + c.ncta;
-        if (last && next_it < ATT_ITEMS) {
+        if (last) {
             // the next item's query is requested now and used after this tile
-            int nb_, nh_, ch_, nch_;
-            att_item(next_it, nb_, nh_, ch_, nch_);
-            att_load_q(bqn, qbuf, nb_, nh_, g, t);
+            int nb_, nh_;
+            if (att_peek(cur, c.smem, s_pos, c.cta, c.ncta, nb_, nh_)) att_load_q(bqn, qbuf, nb_, nh_, g, t);
         }
         const int cnt = min(KV_POS, cur.hi - cur.s);
         if (cnt > 0) {
@@ -951,7 +1014,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
 #pragma unroll
                 for (int i = 0; i < 4; i++) o[mt][i] = 0.f;
         }
-        att_advance(cur, s_pos, c.ncta);
+        att_advance(cur, c.smem, s_pos, c.cta, c.ncta);
     }
     cp_wait();                                         // (the phase ends with a block-wide sync before anything else uses this memory)
 }
@@ -1465,6 +1528,9 @@ __device__ __forceinline__ void step_body(const Args& a) {
         for (int b = c.tid; b < V_B; b += NCONS) s_pos[b] = __ldcg(a.t + b * V_TSTRIDE);
         cons_sync();
     }
+#if V_TCL
+    att_plan(c, s_pos);
+#endif
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
 #pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {

@@ -613,7 +613,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     # into the operand tiles of the mma.sync path, which this mode leaves unused)
     kv_bytes = kvst * 2 * NW * 16 * 128
     tcl = bool(tc and tune.get('tc_layers', True) and D % tcl_nw == 0 and F % D == 0 and kbd % tcl_spu == 0 and kbd * tcl_rb * 128 <= kv_bytes
-               and (kbd - 1) * tcl_rb * 128 + 8192 <= kv_bytes + KT_D * atile and ksplit)
+               and (kbd - 1) * tcl_rb * 128 + 8192 <= kv_bytes + KT_D * atile and B * 4 <= KT_D * atile and ksplit)
     rec, tiles, notes = place_step(dims, grid, ksplit)
     if tcl:
         NB = 1          # the mma.sync operand tiles are not used: their shared memory goes to the weight ring
@@ -678,7 +678,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
                 V_GELU_C=f32(dims['gelu'][2]), V_NSLOT=nslot, V_CH=ch, V_TPW=tpw, V_KVST=kvst, V_ACT_LO=int(bool(act_lo)),
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0, V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q,
-                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_ROWSEQ=int(bool(row_seq)), V_BSEQ=bseq, V_TCL=int(tcl), V_TCL_NW=tcl_nw, V_TCL_RB=tcl_rb, V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
+                V_MAXGRID=grid, V_LN_DIST=int(ln_dist), V_OFF_ACTG=off_actg, V_OFF_PART=off_part, V_OFF_BEST=off_best, V_TC=int(tc), V_OFF_TC=off_tc, V_ROWSEQ=int(bool(row_seq)), V_BSEQ=bseq, V_TCL=int(tcl), V_TCL_NW=tcl_nw, V_TCL_RB=tcl_rb, V_ATT_SNAKE=int(tune.get('att_snake', 1)), V_OFF_OG=off_og, V_KSPLIT=int(ksplit), V_OFF_GG=off_gg, V_NCH=nch, V_TAIL_BH=tail_bh, V_TS=ts, V_WAIT_NS=f"{int(tune.get('wait_ns', 500_000_000))}ull")
     head = ''.join(f'#define {k} {v}\n' for k, v in defs.items())
 
     params, pack_params, tail = _entry_points(res, roles, fb, prompt_len, row_seq)
