@@ -571,16 +571,18 @@ def test_dense_prefill_equals_the_oracle(shape_name, batch, rows):
         assert np.array_equal(got[i, :stop], ref[:stop]), (i, got[i], ref)
 
 
-def test_dense_prefill_at_full_size_against_the_reference():
-    """GPT-2 small, the eight 128-token prompts of the batch-8 fixture in one dense pass (4 launches of 256 rows, tensor-core
-    contractions): the first generated token of every sequence and the free-running tokens after it equal the reference
-    interpreter's wherever its margin is above the bar"""
+@pytest.mark.parametrize('rows', [None, 256])
+def test_dense_prefill_at_full_size_against_the_reference(rows):
+    """GPT-2 small, the eight 128-token prompts of the batch-8 fixture in one dense pass (one launch of 1024 rows by
+    default, or 4 launches of 256; tensor-core contractions; logits only for the slab that holds the last positions): the
+    first generated token of every sequence and the free-running tokens after it equal the reference interpreter's
+    wherever its margin is above the bar"""
     g = load('gpt2_cfg2')
     sh, seed, init, prompts, gen, keep, stride = fixture_inputs(g)
     B, P = prompts.shape
     m, _ = model(sh, seed, init, B, P + 16)
-    m.prefill(prompts)
-    assert m._prefill_engines[256].low.dims['tcl']
+    m.prefill(prompts, rows=rows)
+    assert m._prefill_engines[rows or 1024].low.dims['tcl']
     toks = [m.x.clone()]
     for _ in range(11):
         m.step(); toks.append(m.x.clone())

@@ -75,6 +75,7 @@
 // pass over prompt positions: every row's K and V are written before any row attends, so a row sees the rows before it).
 // The sequence of row b follows the positions in shared memory.
 #define SEQ_OF(s_pos, b) (V_ROWSEQ ? (s_pos)[V_B + (b)] : (b))
+#define ROW_NO_LOGITS 0x40000000              // mark in row_seq[b]: nobody reads the logits of this row
 #define PH_QKV 0
 #define PH_ATT 1
 #define PH_PROJ 2
@@ -376,7 +377,7 @@ __device__ __noinline__ void producer_drain(Ctx& c) {
     }
 }
 __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* __restrict__ P, const unsigned char* __restrict__ WP,
-                                      const unsigned char* __restrict__ TM, int cta, int ncta, int nsteps) {
+                                      const unsigned char* __restrict__ TM, int cta, int ncta, int nsteps, int log_slabs) {
     Ctx c;
     c.smem = smem; c.bar = bar; c.chunk = 0; c.dead = false; c.cta = cta; c.kvi = 0; c.tcl = 0;
     const int* s_pos = reinterpret_cast<const int*>(smem + SM_MISC + MISC_POS);
@@ -397,7 +398,7 @@ __device__ __noinline__ void producer(unsigned char* smem, u32* bar, const int* 
             // 128 rows x 64 k of the embedding table per slot, by tensor copy; once per slab of 64 sequences
             const int rows = P[PT_LOG_NJ] * 16, mtiles = (rows + 127) / 128;
 #pragma unroll 1
-            for (int i = 0; i < TC_SLABS_P * mtiles * (V_D / 64); i++) {
+            for (int i = 0; i < log_slabs * mtiles * (V_D / 64); i++) {
                 const int kb = i % (V_D / 64), mt = (i / (V_D / 64)) % mtiles;
                 const u32 slot = c.chunk % V_NSLOT, use = c.chunk / V_NSLOT;
                 wait_mbar(c, empty_bar(c, slot), (use & 1u) ^ 1u, 0x200u);
@@ -1133,7 +1134,7 @@ __device__ __forceinline__ void ln_rows_to_tc(Ctx& c, const float* __restrict__ 
 }
 
 __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, const unsigned char* __restrict__ tcg,
-                                          float* __restrict__ logit, u64* __restrict__ gbest) {
+                                          float* __restrict__ logit, u64* __restrict__ gbest, int log_slabs) {
     const u32 tmem = *reinterpret_cast<const volatile u32*>(c.smem + SM_MISC + MISC_TMEM);
     const int rows = P[PT_LOG_NJ] * 16, n0 = P[PT_LOG_J0] * 16;
     const int mtiles = (rows + TC_M - 1) / TC_M;
@@ -1141,7 +1142,7 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
     const int wu = __shfl_sync(0xffffffffu, c.warp, 0);              // the warp index as a value the compiler knows to be uniform
     const u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
 #pragma unroll 1
-    for (int slab = 0; slab < TC_SLABS; slab++) {
+    for (int slab = 0; slab < log_slabs; slab++) {
         // operand B of the slab: one bulk copy per block of 64 k into the K/V stages
         if (c.tid == 0 && mtiles > 0) {
             asm volatile("fence.proxy.async.global;" ::: "memory");          // the operand was written by other CTAs with ordinary stores
@@ -1447,7 +1448,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
             bad |= (tb >= V_TMAX) | (tb >= V_CPOS) | (xb < 0) | (xb >= V_N);
             s_pos[b] = tb;
 #if V_ROWSEQ
-            const int sq = __ldcg(a.row_seq + b);
+            const int sq = __ldcg(a.row_seq + b) & ~ROW_NO_LOGITS;
             bad |= (sq < 0) | (sq >= V_BSEQ);
             s_pos[V_B + b] = sq;
 #endif
@@ -1460,6 +1461,20 @@ __device__ __forceinline__ void step_body(const Args& a) {
         }
     }
     const int nsteps = max(a.nsteps, 1);
+    // slabs of 64 rows whose logits are wanted: all of them, or (rows of a dense prompt pass) the slabs that hold the
+    // rows without the ROW_NO_LOGITS mark, which the host places first
+    int log_slabs = TC_SLABS_P;
+#if V_ROWSEQ
+    {
+        int want = 0;
+#pragma unroll 1
+        for (int i = 0; i < (V_B + NTHREADS - 1) / NTHREADS; i++) {
+            const int b = c.tid + i * NTHREADS;
+            want += __syncthreads_count(b < V_B && !(__ldcg(a.row_seq + b) & ROW_NO_LOGITS));
+        }
+        log_slabs = (want + 63) / 64;
+    }
+#endif
     int* flag = reinterpret_cast<int*>(smem + SM_MISC + MISC_FLAG);
     volatile int* stop = reinterpret_cast<volatile int*>(smem + SM_MISC + MISC_STOP);
     if (c.tid == 0) {
@@ -1490,7 +1505,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #endif
     const int* P = a.PT + c.cta * PT_STRIDE;
     if (c.warp == NW) {
-        if (c.lane == 0) producer(smem, a.bar, P, a.WP, a.TM, c.cta, c.ncta, nsteps);
+        if (c.lane == 0) producer(smem, a.bar, P, a.WP, a.TM, c.cta, c.ncta, nsteps, log_slabs);
         return;
     }
 
@@ -1593,7 +1608,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         }
 #endif
 #if V_TC
-        if (first == PH_LOGITS) { logits_tc(c, P, tcg, logit, gbest); break; }
+        if (first == PH_LOGITS) { logits_tc(c, P, tcg, logit, gbest, log_slabs); break; }
 #endif
 #if V_TCL
         if (first != PH_ATT) {

@@ -101,7 +101,7 @@ class VestaGPT2:
 
     def prefill(self, tokens, lengths=None, rows=None):
         """consume whole prompts as dense passes: all prompt positions of all sequences are cut into launches of `rows`
-        (sequence, position) rows (default 1024 from 16 K positions, 256 from 1 K, else 128) through the large-batch kernel: tensor-core
+        (sequence, position) rows (default 1024 from 1 K positions, 256 from 256, else 128) through the large-batch kernel: tensor-core
         contractions where the shape allows, every row's K and V written before any row attends, so a row sees the rows
         of its own sequence before it. On return the cache holds every prompt position, x the first generated token
         of every sequence and t its position (= its prompt length). tokens: int array (batch, P); lengths: (batch,) or
@@ -119,7 +119,7 @@ class VestaGPT2:
         if self.t.numel() == 1 and lens.min() != lens.max():
             raise ValueError('prompts of different lengths need per_sequence_t=True')
         total = int(lens.sum())
-        rows = int(rows or (1024 if total >= 16384 else 256 if total >= 1024 else 128))
+        rows = int(rows or (1024 if total >= 1024 else 256 if total >= 256 else 128))
         eng = self._prefill_engines.get(rows)
         if eng is None:
             eng = self._prefill_engines[rows] = _PrefillRows(self, rows)
@@ -215,9 +215,17 @@ class _PrefillRows:
             n = min(R, len(seqs) - i)
             x, t, s = np.zeros(R, np.int32), np.full(R, -1, np.int32), np.zeros(R, np.int32)
             x[:n], t[:n], s[:n] = tok[i:i + n], pos[i:i + n], seqs[i:i + n]
-            self.x.copy_(torch.from_numpy(x)); self.t.copy_(torch.from_numpy(t)); self.seq.copy_(torch.from_numpy(s))
+            # Only the last position of a prompt needs logits: those rows go first (the order of the rows is free), all
+            # others carry the kernel's "nobody reads these logits" mark, and the logits phase runs for the slabs of
+            # 64 rows that hold an unmarked row (none, in most launches of a long prompt).
+            want = np.zeros(R, bool)
+            want[:n] = t[:n] == lens[s[:n]] - 1
+            order = np.argsort(~want, kind='stable')
+            x, t, s, want = x[order], t[order], s[order], want[order]
+            self.x.copy_(torch.from_numpy(x)); self.t.copy_(torch.from_numpy(t))
+            self.seq.copy_(torch.from_numpy(np.where(want, s, s | ROW_NO_LOGITS).astype(np.int32)))
             self.k.launch()
-            last = np.flatnonzero(t[:n] == lens[s[:n]] - 1)            # rows that are the last position of their prompt
+            last = np.flatnonzero(want)                                # rows that are the last position of their prompt
             if len(last):
                 rows = torch.from_numpy(last).to(self.model.device)
                 first[torch.from_numpy(s[last].astype(np.int64)).to(self.model.device)] = self.k.view('next')[rows].to(torch.int32)
@@ -225,4 +233,5 @@ class _PrefillRows:
         return first
 
 
+ROW_NO_LOGITS = 0x40000000         # mark in row_seq (csrc/step_kernel.cuh): nobody reads the logits of this row
 DEFAULT_PROGRAM = PROGRAMS / 'gpt2.vst'
