@@ -134,7 +134,7 @@ __device__ __forceinline__ Seg seg_of(const int* __restrict__ P, int kind) {
 #define MISC_SIDE (MISC_FLAG + 16)                                // per K/V stage: the K row and the V row of the current position
 #define SM_MISC_BYTES (MISC_SIDE + V_KVST * 256)
 #define SM_BARS ((SM_MISC + SM_MISC_BYTES + 15) & ~15)
-#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + 2 * V_KVST + 2) * 8)        // + operand-loaded and products-done barriers of the tensor-core logits
+#define SM_TOTAL (SM_BARS + (2 * V_NSLOT + 2 * V_KVST + 4) * 8)        // + operand-loaded (three thirds) and products-done barriers of the tensor-core phases
 
 struct Ctx {
     unsigned char* smem;
@@ -345,6 +345,7 @@ __device__ __forceinline__ void producer_attention(Ctx& c, int l, const int* s_p
 #define TCL_UB (V_TCL_NW * 128 * TCL_UK)                       // bytes of a unit's weights
 #define TCL_SPU ((TCL_UB + V_CH * FRAG_BYTES - 1) / (V_CH * FRAG_BYTES))    // ring slots per unit
 #define TCL_A_KB (V_TCL_RB * 128)                              // bytes of the operand of a row block per k-block
+#define TCL_GS ((TCL_UK + 2) / 3)                              // k-blocks per third of a unit's fold
 #define TCL_NRB ((V_B + V_TCL_RB - 1) / V_TCL_RB)
 #define TCL_W_PROJ (3 * V_D / V_TCL_NW)                        // weight blocks of a layer before the attention projection's
 #define TCL_W_FC (TCL_W_PROJ + V_D / V_TCL_NW)
@@ -1042,7 +1043,9 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
 #define TC_SLABS ((V_B + TC_N - 1) / TC_N)
 #define TC_B_BYTES (TC_N * V_D * 2)               // operand B of one slab
 #define TC_COLS 64                                // tensor-memory columns: one accumulator tile
-__device__ __forceinline__ u32 tc_load_bar(const Ctx& c) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST) * 8; }
+// operand loaded: g = 0 (the whole operand, or its first third), 1 and 2 (the other thirds: the layer contractions start
+// their products when a third has landed); the three complete once per operand, so one counter gives their parity
+__device__ __forceinline__ u32 tc_load_bar(const Ctx& c, int g = 0) { return smem_u32(c.smem + SM_BARS) + (g == 0 ? 2 * V_NSLOT + V_KVST : 2 * V_NSLOT + 2 * V_KVST + 1 + g) * 8; }
 __device__ __forceinline__ u32 tc_done_bar(const Ctx& c) { return smem_u32(c.smem + SM_BARS) + (2 * V_NSLOT + V_KVST + 1) * 8; }
 
 // shared-memory matrix descriptor of a K-major operand in the 128-byte swizzle: rows of 128 bytes, groups of 8 rows
@@ -1148,6 +1151,7 @@ __device__ __forceinline__ void logits_tc(Ctx& c, const int* __restrict__ P, con
             asm volatile("fence.proxy.async.global;" ::: "memory");          // the operand was written by other CTAs with ordinary stores
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_expect(tc_load_bar(c), TC_B_BYTES);
+            mbar_arrive(tc_load_bar(c, 1)); mbar_arrive(tc_load_bar(c, 2));      // (their turn passes: one counter for the three)
 #pragma unroll 1
             for (int kb = 0; kb < TC_NKB; kb++)
                 bulk_g2s(smem_u32(c.smem + SM_KV) + kb * (TC_N * 128), tcg + (size_t)slab * TC_B_BYTES + (size_t)kb * (TC_N * 128), TC_N * 128, tc_load_bar(c));
@@ -1270,10 +1274,10 @@ __device__ __forceinline__ void tcl_ld(u32 (&r)[16], u32 addr) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 // The products of one unit, issued by a whole warp (`leader` comes from elect_one).
-__device__ __forceinline__ void tcl_issue(u32 tmem, u32 a_addr, u32 b_addr, u32 leader) {
+__device__ __forceinline__ void tcl_issue(u32 tmem, u32 a_addr, u32 b_addr, u32 leader, int k0, int k1) {
     const u64 ad = tc_desc(a_addr), bd = tc_desc(b_addr);
 #pragma unroll 1
-    for (int kb = 0; kb < TCL_UK; kb++)
+    for (int kb = k0; kb < k1; kb++)
         tc_mma_kb(tmem, ad + (u64)((kb * TCL_A_KB) >> 4), bd + (u64)((kb * (V_TCL_NW * 128)) >> 4), kb == 0, TCL_IDESC, leader);
 }
 __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const unsigned char* __restrict__ opb, const TclOut& o) {
@@ -1300,25 +1304,42 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                 if (c.lane == 0) {
                     asm volatile("fence.proxy.async.global;" ::: "memory");      // the operand was written by other CTAs with ordinary stores
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    mbar_expect(tc_load_bar(c), (u32)TCL_UK * TCL_A_KB);
                     // rows rb * V_TCL_RB .. of slab (rb * V_TCL_RB) / 64: V_TCL_RB rows of 128 bytes inside every 64-row k-block tile
                     const unsigned char* src = opb + ((size_t)((rb * V_TCL_RB) / 64) * ktot + (size_t)ks * TCL_UK) * (TC_N * 128) + ((rb * V_TCL_RB) % 64) * 128;
+#pragma unroll
+                    for (int g = 0; g < 3; g++) {
+                        const int k0 = min(g * TCL_GS, TCL_UK), k1 = min(k0 + TCL_GS, TCL_UK);
+                        if (k1 > k0) mbar_expect(tc_load_bar(c, g), (u32)(k1 - k0) * TCL_A_KB); else mbar_arrive(tc_load_bar(c, g));
+                        if (V_TCL_RB == 64) {
+                            // whole 64-row tiles follow one another in global and in shared memory: one copy per third
+                            // (issuing a bulk copy costs the thread about 230 cycles, whatever its size)
+                            if (k1 > k0) bulk_g2s(smem_u32(c.smem + SM_KV) + k0 * TCL_A_KB, src + (size_t)k0 * (TC_N * 128), (u32)(k1 - k0) * TCL_A_KB, tc_load_bar(c, g));
+                        } else {
 #pragma unroll 1
-                    for (int kb = 0; kb < TCL_UK; kb++)
-                        bulk_g2s(smem_u32(c.smem + SM_KV) + kb * TCL_A_KB, src + (size_t)kb * (TC_N * 128), TCL_A_KB, tc_load_bar(c));
+                            for (int kb = k0; kb < k1; kb++)
+                                bulk_g2s(smem_u32(c.smem + SM_KV) + kb * TCL_A_KB, src + (size_t)kb * (TC_N * 128), TCL_A_KB, tc_load_bar(c, g));
+                        }
+                    }
                 }
                 __syncwarp();
-                wait_mbar(c, tc_load_bar(c), c.tcl & 1u, 0x600u);
             }
-            TRACE(60);
             wait_mbar(c, full_bar(c, slot), use & 1u, 0x300u);
             TRACE(63);
+            const u32 slot_u = __shfl_sync(0xffffffffu, slot, 0);
+            // the products of a third of the fold as soon as that third of the operand has landed
+#pragma unroll 1
+            for (int g = 0; g < 3; g++) {
+                if (load) wait_mbar(c, tc_load_bar(c, g), c.tcl & 1u, 0x600u);
+                if (g == 0) TRACE(60);
+                if (!(__shfl_sync(0xffffffffu, c.dead ? 1 : 0, 0) != 0)) {
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    tcl_issue(tmem_u, smem_u32(c.smem + SM_KV), smem_u32(c.smem + SM_RING) + slot_u * (V_CH * FRAG_BYTES), elect_one(),
+                              min(g * TCL_GS, TCL_UK), min((g + 1) * TCL_GS, TCL_UK));
+                }
+            }
             const bool dead_u = __shfl_sync(0xffffffffu, c.dead ? 1 : 0, 0) != 0;
             if (!dead_u) {
                 const u32 leader = elect_one();
-                const u32 slot_u = __shfl_sync(0xffffffffu, slot, 0);
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                tcl_issue(tmem_u, smem_u32(c.smem + SM_KV), smem_u32(c.smem + SM_RING) + slot_u * (V_CH * FRAG_BYTES), leader);
                 if (leader) {
 #pragma unroll
                     for (u32 i = 0; i < TCL_SPU; i++) tc_commit(empty_bar(c, slot + i));     // the slots are free once these products have read them
@@ -1484,7 +1505,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
         for (int s = 0; s < V_NSLOT; s++) { mbar_init(full_bar(c, s), 1); mbar_init(empty_bar(c, s), V_TCL ? 1 : NW); }
         for (int s = 0; s < V_KVST; s++) { mbar_init(kv_bar(c, s), 1); mbar_init(kv_empty_bar(c, s), NW); }
         *reinterpret_cast<volatile u32*>(smem + SM_MISC + MISC_ATTSEQ) = 0;
-        mbar_init(tc_load_bar(c), 1); mbar_init(tc_done_bar(c), 1);
+        mbar_init(tc_load_bar(c, 0), 1); mbar_init(tc_load_bar(c, 1), 1); mbar_init(tc_load_bar(c, 2), 1); mbar_init(tc_done_bar(c), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // operand tiles and K/V stages start as zero: rows of a batch tile beyond the batch stay zero for the whole

@@ -571,7 +571,7 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
 
     def smem_fixed(nb):
         return (kvst * (2 * NW * 16 * 128 + 256 + 16) + 32 + KT_D * nb * atile + WN_MAX * nb * atile + NW * nb * 512
-                + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 * (2 if row_seq else 1) + 16 + 8 * 8 + 16 + 16)
+                + (3 * D + WN_MAX * 16) * 2 + 16 + 2 * NW * (E + 2) * 4 + 16 + 8 * nb * NW * 8 + B * 4 * (2 if row_seq else 1) + 16 + 8 * 8 + 16 + 32)
 
     NB = min((B + 7) // 8, 8)
     if slab_tiles:
