@@ -1312,7 +1312,6 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
                         if (k1 > k0) mbar_expect(tc_load_bar(c, g), (u32)(k1 - k0) * TCL_A_KB); else mbar_arrive(tc_load_bar(c, g));
                         if (V_TCL_RB == 64) {
                             // whole 64-row tiles follow one another in global and in shared memory: one copy per third
-                            // (issuing a bulk copy costs the thread about 230 cycles, whatever its size)
                             if (k1 > k0) bulk_g2s(smem_u32(c.smem + SM_KV) + k0 * TCL_A_KB, src + (size_t)k0 * (TC_N * 128), (u32)(k1 - k0) * TCL_A_KB, tc_load_bar(c, g));
                         } else {
 #pragma unroll 1
