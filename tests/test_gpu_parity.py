@@ -598,6 +598,36 @@ def test_dense_prefill_at_full_size_against_the_reference(rows):
     assert compared >= 4 * B
 
 
+@pytest.mark.parametrize('batch', [3, 70])
+@pytest.mark.parametrize('without', [('qkvb', 'fcb'), ('ln1b', 'qkvb', 'ob', 'ln2b', 'fcb', 'pb', 'lnfb')])
+def test_program_without_shifts_or_biases(batch, without):
+    """a program that leaves out additive parameters (both kernel texts; at 70 sequences the tensor-core contractions):
+    the kernel reads zeros in their place; against the oracle with those parameters set to zero, which is the same
+    arithmetic as the shorter statements"""
+    from oracle import gpt2_numpy as O
+    from vesta_gpu_b200.shapes import TINY
+    from vesta_gpu_b200.synth import make_prompts
+    steps = 5
+    m, hf = model(TINY, 5, 'rich', batch, steps, without=without, tune=dict(ln_dist=True) if batch > 8 else None)
+    assert m.low.dims['absent'] == sorted(without) and not set(without) & set(m.W)
+    weights = dict(hf.weights)
+    for n in without:
+        weights[n] = np.zeros_like(weights[n])
+    W = O.upcast(weights)
+    feed = make_prompts(TINY, batch, steps, seed=batch)
+    caches = [O.new_cache(TINY, steps) for _ in range(batch)]
+    m.reset()
+    for t in range(steps):
+        m.x.copy_(torch.from_numpy(feed[:, t].copy()).cuda()); m.step()
+        lg = m.logits().cpu().numpy(); nx = m.next().cpu().numpy()
+        for i in range(0, batch, max(1, batch // 6)):
+            ref, rn = O.step(TINY, W, caches[i][0], caches[i][1], int(feed[i, t]), t)
+            assert np.abs(lg[i] - ref).max() < TIGHT, (t, i)
+            if O.margin(ref) > MARGIN:
+                assert int(nx[i]) == rn
+    m.k.check()
+
+
 def test_out_of_range_inputs_are_refused_not_executed():
     from vesta_gpu_b200.shapes import TINY
     m, _ = model(TINY, 3, 'rich', 2, 8)

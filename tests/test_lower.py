@@ -204,6 +204,28 @@ def test_renamed_program_is_recognised():
     assert low.roles['qkvw'] == 'proj3w' and 'R_proj3w' in low.src
 
 
+@pytest.mark.parametrize('without', [('qkvb',), ('ln1b', 'ln2b', 'lnfb'), ('ob', 'pb'), ('ln1b', 'qkvb', 'ob', 'ln2b', 'fcb', 'pb', 'lnfb')])
+@pytest.mark.parametrize('batch', [1, 70])
+def test_programs_without_shifts_or_biases_are_placed(without, batch):
+    """the additive parameters may be absent from a program (a model without biases, LayerNorms without shift): the
+    statements are matched without their last term, the residues are neither received nor bound, and the kernel gets one
+    vector of zeros in their place; the interpreter of the reference runs such a program as it stands"""
+    text = decode_program(TINY, without=without)
+    assert all(f'residue {n}[' not in text for n in without)
+    spec = {k: v for k, v in residue_spec(TINY, batch, 16).items() if k not in without}
+    low = lw.lower(text, spec, {'s': 16}, batch=batch, per_token=('x', 'keys', 'vals'), outputs=('logit', 'next'),
+                   tune=dict(ln_dist=True) if batch > 8 else None)
+    names = [p[0] for p in low.params]
+    assert names[-1] == '_zeros' and not set(without) & set(names)
+    assert low.dims['absent'] == sorted(without) and low.dims['zeros_len'] >= TINY.L * max(3 * TINY.D, TINY.F)
+    assert all(low.roles[n] == '_zeros' for n in without) and 'X_zeros' in low.src
+    # a residue that is supplied but not received is still an error; a multiplicative parameter cannot be left out
+    with pytest.raises(ValueError):
+        lw.lower(text, residue_spec(TINY, batch, 16), {'s': 16}, batch=batch, per_token=('x', 'keys', 'vals'))
+    with pytest.raises(NotImplementedError):
+        lw.lower(decode_program(TINY).replace(' * ln1w[l, d]', ''), residue_spec(TINY, 1, 16), {'s': 16}, batch=1, per_token=('x', 'keys', 'vals'))
+
+
 def test_per_sequence_positions():
     low = lower_for(TINY, 4, 32, per_sequence_t=True)
     assert '#define V_TSTRIDE 1' in low.src

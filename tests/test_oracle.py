@@ -119,3 +119,27 @@ def test_gpt2_small_deep_context_samples(name):
     """the batch-64 config at context 600 and at the last positions of a 1024-row cache (1021..1023), ragged batches of
     32, 64 and 256 with contexts 64..512"""
     check_samples(name)
+
+
+def test_program_without_additive_parameters_in_the_reference_interpreter():
+    """the statements without their shift / bias term, as vesta_gpu_b200 accepts them, evaluated by the reference
+    interpreter itself (when a copy of the reference is installed): the same logits as the oracle computes with
+    those parameters set to zero, which is what the GPU tests compare the kernel with"""
+    import os
+    from vesta_gpu_b200.program_text import decode_program, ADDITIVE
+    from vesta_gpu_b200.shapes import TINY
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(here, 'oracle', '_ref', 'vesta', 'interp.py')):
+        pytest.skip('no copy of the reference installed (python oracle/make_ref.py <checkout>)')
+    from vesta.interp import run
+    raw = make_weights(TINY, 5, 'rich')
+    for without in (('qkvb', 'fcb'), ADDITIVE):
+        text = decode_program(TINY, without=without)
+        Wz = O.upcast({k: (np.zeros_like(v) if k in without else v) for k, v in raw.items()})
+        Wr = {k: v for k, v in O.upcast(raw).items() if k not in without}
+        keys, vals = O.new_cache(TINY, 4)
+        rk, rv = O.new_cache(TINY, 4)
+        for t, x in enumerate((7, 100, 3)):
+            ref, _ = O.step(TINY, Wz, keys, vals, x, t)
+            env = run(text, dict(Wr, x=x, t=t, keys=rk, vals=rv))
+            assert np.abs(np.asarray(env['logit'][0]) - ref).max() < 1e-5, (without, t)

@@ -46,9 +46,10 @@ def shape_of(W, heads=None):
 
 class VestaGPT2:
     def __init__(self, hf, dtype='f16', batch=1, tmax=1024, feedback=True, program=None, timing=False,
-                 blocks_per_sm=None, per_sequence_t=False, device=None, prompt_len=0, slab_tiles=None, tune=None):
+                 blocks_per_sm=None, per_sequence_t=False, device=None, prompt_len=0, slab_tiles=None, tune=None, without=()):
         """program: path of a .vst file; default: the step program for the sizes of the weights
-        (identical to programs/gpt2.vst for GPT-2 small). per_sequence_t: every sequence keeps its
+        (identical to programs/gpt2.vst for GPT-2 small), `without` naming the shifts and biases it leaves out
+        (program_text.ADDITIVE). Weights the program does not receive are not bound. per_sequence_t: every sequence keeps its
         own position t[b] (ragged batches); default one position for the whole batch as in the
         reference. prompt_len > 0 adds the buffers `prompt` (batch, prompt_len) and `plen` (batch,): the
         kernel then feeds prompt[b][t+1] while t + 1 < plen[b] and its own choice afterwards."""
@@ -71,9 +72,14 @@ class VestaGPT2:
         spec = {n: (((batch,) if per_sequence_t else ()), 'i32') if n == 't' else (tuple(v.shape), names[v.dtype])
                 for n, v in R.items() if n not in ('prompt', 'plen')}
         if program is None:
-            text = decode_program(sh)
+            text = decode_program(sh, without=tuple(without))
         else:
             text = open(program, encoding='utf-8').read()
+        from .lower import recognise
+        recv = set(recognise(text)[2])
+        self.W = {n: v for n, v in self.W.items() if n in recv}
+        R = {n: v for n, v in R.items() if n in recv}
+        spec = {n: v for n, v in spec.items() if n in recv}
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
         per_token = ('x', 'keys', 'vals') + (('t',) if per_sequence_t else ())
         self.low = lower(text, spec, axis_max={'s': tmax}, batch=batch, per_token=per_token,

@@ -168,6 +168,9 @@ class Kernel:
         """fix the argument list once (launches then cost one call) and pack the weights"""
         L = lib()
         vals = []
+        if any(name == '_zeros' for name, _, _ in self.lowered.params) and '_zeros' not in residue:
+            # additive parameters the program does not have (lower.OPTIONAL_TERMS): the kernel reads zeros for them
+            residue = dict(residue, _zeros=torch.zeros(self.lowered.dims['zeros_len'], dtype=torch.float16, device=self.device))
         for name, dt, _ in self.lowered.params:
             t = residue[name]
             assert t.is_cuda and t.dtype == TORCH_DT[dt] and t.is_contiguous(), (name, t.dtype, dt)

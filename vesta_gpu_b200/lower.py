@@ -133,6 +133,14 @@ LAYER_PATTERNS = [
     ('GELU', '$g[$f] = $ga * $u[$f] * ($one + tanh($gb * ($u[$f] + $gc * $u[$f] * $u[$f] * $u[$f])))'),
     ('MLP-proj + residual 2', '$z2[$d] = $z1[$d] + (fold sum $f: $g[$f] * $pw[$l, $f, $d]) + $pb[$l, $d]'),
 ]
+# The additive parameters (the shifts of the three LayerNorms, the biases of the four contractions) may be absent from a
+# program: the statement is then matched without its last term and the kernel reads a vector of zeros in its place.
+OPTIONAL_TERMS = {
+    'LN1': (' + $ln1b[$l, $d]', 'ln1b'), 'QKV': (' + $qkvb[$l, $j]', 'qkvb'), 'residual 1': (' + $ob[$l, $d]', 'ob'),
+    'LN2': (' + $ln2b[$l, $d]', 'ln2b'), 'FC': (' + $fcb[$l, $f]', 'fcb'), 'MLP-proj + residual 2': (' + $pb[$l, $d]', 'pb'),
+    'LNf': (' + $lnfb[$d]', 'lnfb'),
+}
+ZEROS = '_zeros'                 # name of the kernel parameter that stands in for absent additive parameters
 HEAD_PATTERNS = [
     ('LNf mean', '$m3 = fold sum $d: $zL[$d] / $D'),
     ('LNf variance', '$v3 = fold sum $d: ($zL[$d] - $m3) * ($zL[$d] - $m3) / $D'),
@@ -162,11 +170,24 @@ def recognise(text):
     env = {}
 
     def need(label, pat_text, node):
+        trial = dict(env)
         try:
-            _unify(_pattern(pat_text), node, env)
+            _unify(_pattern(pat_text), node, trial)
         except Mismatch as err:
+            term, role = OPTIONAL_TERMS.get(label, (None, None))
+            if term and pat_text.endswith(term):
+                trial = dict(env)
+                try:
+                    _unify(_pattern(pat_text[:-len(term)]), node, trial)
+                except Mismatch:
+                    trial = None
+                if trial is not None:
+                    trial['$' + role] = None              # absent: zeros
+                    env.clear(); env.update(trial)
+                    return
             raise NotImplementedError(
                 f'statement {_show(node)!r} is not the {label} statement of a decode step: {err}') from None
+        env.clear(); env.update(trial)
 
     if len(rest) != 2 + len(HEAD_PATTERNS) or not isinstance(rest[1], sx.StepFold):
         raise NotImplementedError('not a decode-step program: expected embed, one `fold step` over the layers, '
@@ -327,7 +348,11 @@ def _entry_points(res, roles, fb, prompt_len, row_seq=False):
     if row_seq:
         params += [('row_seq', 'i32', False)]
         sig += ['const int* __restrict__ X_row_seq']
-    R = {k: 'R_' + v for k, v in roles.items()}
+    if ZEROS in roles.values():
+        # additive parameters the program does not have: one vector of zeros (allocated by Kernel.bind) stands for all
+        params += [(ZEROS, 'f16', False)]
+        sig += ['const unsigned short* __restrict__ X_zeros']
+    R = {k: ('X_zeros' if v == ZEROS else 'R_' + v) for k, v in roles.items()}
     step_sig = ', '.join(sig + ['float* __restrict__ S', 'unsigned* bar', 'unsigned long long* TS',
                                 'const unsigned char* __restrict__ WP', 'const int* __restrict__ PT',
                                 'const unsigned char* __restrict__ TM', 'int nsteps'])
@@ -497,7 +522,12 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     D, H, E, F, N, L = dims['D'], dims['H'], dims['E'], dims['F'], dims['N'], dims['L']
     B = int(batch)
     roles = {k: env['$' + k] for k in ROLE_KEYS}
+    absent = sorted(k for k, v in roles.items() if v is None)
+    roles = {k: (ZEROS if v is None else v) for k, v in roles.items()}
+    dims = dict(dims, absent=absent, zeros_len=L * max(3 * D, F))      # (the longest additive parameter: one vector of zeros serves all)
     for role, name in roles.items():
+        if name == ZEROS:
+            continue
         if name not in res:
             raise NameError(f'residue {name} not supplied')
         if name not in recv:
@@ -514,6 +544,8 @@ def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None,
     t_per_token = t_name in per_token
 
     def want(role, shape, dt):
+        if roles[role] == ZEROS:
+            return
         got_shape, got_dt = res[roles[role]]
         if tuple(got_shape) != tuple(shape) or got_dt != dt:
             raise ValueError(f'residue {roles[role]}: expected {tuple(shape)} {dt}, got {tuple(got_shape)} {got_dt}')

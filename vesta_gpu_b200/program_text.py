@@ -13,7 +13,32 @@ def _num(v):
     return repr(int(v)) if float(v) == int(v) else repr(float(v))
 
 
-def decode_program(sh: Shape, eps=0.00001) -> str:
+ADDITIVE = ('ln1b', 'qkvb', 'ob', 'ln2b', 'fcb', 'pb', 'lnfb')     # the shifts and biases a program may leave out
+
+
+def decode_program(sh: Shape, eps=0.00001, without=()) -> str:
+    """without: names from ADDITIVE; the program then neither receives nor adds those parameters (a model without
+    biases, a LayerNorm without shift)"""
+    D, H, E, F, N, J, L = sh.D, sh.H, sh.E, sh.F, sh.N, sh.J, sh.L
+    text = _decode_program(sh, eps)
+    if not without:
+        return text
+    terms = {'ln1b': ' + ln1b[l, d]', 'qkvb': ' + qkvb[l, j]', 'ob': ' + ob[l, d]', 'ln2b': ' + ln2b[l, d]',
+             'fcb': ' + fcb[l, f]', 'pb': ' + pb[l, d]', 'lnfb': ' + lnfb[d]'}
+    out = []
+    for line in text.split('\n'):
+        for name in without:
+            if line.startswith(f'residue {name}['):
+                line = None
+                break
+            if line.endswith(terms[name]):
+                line = line[:-len(terms[name])]
+        if line is not None:
+            out.append(line)
+    return '\n'.join(out)
+
+
+def _decode_program(sh: Shape, eps=0.00001) -> str:
     D, H, E, F, N, J, L = sh.D, sh.H, sh.E, sh.F, sh.N, sh.J, sh.L
     scale = _num(E ** 0.5)
     lines = [
