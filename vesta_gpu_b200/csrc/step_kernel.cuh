@@ -812,20 +812,36 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
 // Result per item: (running max, sum, unnormalised o[V_E]).
 // ---------------------------------------------------------------------------------------------
 // B operand of the scores: the query of (b, h), head in column 0 (lanes with g == 0), remainder in column 1 (g == 1)
-__device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* __restrict__ qbuf, int b, int h, int g, int t) {
+// in two halves: the loads (the values are not touched, so the warp does not wait for them) and, when the operand is
+// needed, the conversion
+__device__ __forceinline__ void att_fetch_q(float2 (&raw)[V_E / 16][2], const float* __restrict__ qbuf, int b, int h, int g, int t) {
     const float* qp = qbuf + (size_t)b * V_D + h * V_E;
+#pragma unroll
+    for (int kq = 0; kq < V_E / 16; kq++) {
+        raw[kq][0] = make_float2(0.f, 0.f); raw[kq][1] = make_float2(0.f, 0.f);
+        if (g < 2) {
+            raw[kq][0] = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
+            raw[kq][1] = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
+        }
+    }
+}
+__device__ __forceinline__ void att_pack_q(u32 (&bq)[V_E / 16][2], const float2 (&raw)[V_E / 16][2], int g) {
     const float sc = V_SCALE_IS_POW2 ? (1.0f / V_SCALE) : 1.0f;        // exact when the divisor is a power of two
 #pragma unroll
     for (int kq = 0; kq < V_E / 16; kq++) {
         bq[kq][0] = 0; bq[kq][1] = 0;
         if (g < 2) {
-            const float2 a0 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t));
-            const float2 a1 = __ldcg(reinterpret_cast<const float2*>(qp + kq * 16 + 2 * t + 8));
+            const float2 a0 = raw[kq][0], a1 = raw[kq][1];
             const u32 h0 = pack_h2(a0.x * sc, a0.y * sc), h1 = pack_h2(a1.x * sc, a1.y * sc);
             bq[kq][0] = g == 0 ? h0 : pack_h2(a0.x * sc - h_lo(h0), a0.y * sc - h_hi(h0));
             bq[kq][1] = g == 0 ? h1 : pack_h2(a1.x * sc - h_lo(h1), a1.y * sc - h_hi(h1));
         }
     }
+}
+__device__ __forceinline__ void att_load_q(u32 (&bq)[V_E / 16][2], const float* __restrict__ qbuf, int b, int h, int g, int t) {
+    float2 raw[V_E / 16][2];
+    att_fetch_q(raw, qbuf, b, h, g, t);
+    att_pack_q(bq, raw, g);
 }
 
 #if V_TCL
@@ -854,9 +870,10 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     AttIter cur, pf;
     att_begin(cur, c.smem, s_pos, c.cta, c.ncta);
     if (!att_valid(cur)) return;
-    u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
+    u32 bq[V_E / 16][2];                             // the query of this item
+    float2 qn[V_E / 16][2];                          // the query of the next one as loaded (converted when the item starts)
 #pragma unroll
-    for (int kq = 0; kq < V_E / 16; kq++) { bqn[kq][0] = 0; bqn[kq][1] = 0; }
+    for (int kq = 0; kq < V_E / 16; kq++) { qn[kq][0] = make_float2(0.f, 0.f); qn[kq][1] = make_float2(0.f, 0.f); }
     att_load_q(bq, qbuf, cur.b, cur.h, g, t);        // requested first: its trip to L2 overlaps the walk below
     // The first V_KVST tiles may have been requested before the barrier: where one holds the current position of its
     // sequence, that row is fetched now into a side buffer (one per stage) and moved into the tile when it is used.
@@ -897,7 +914,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         if (last) {
             // the next item's query is requested now and used after this tile
             int nb_, nh_;
-            if (att_peek(cur, c.smem, s_pos, c.cta, c.ncta, nb_, nh_)) att_load_q(bqn, qbuf, nb_, nh_, g, t);
+            if (att_peek(cur, c.smem, s_pos, c.cta, c.ncta, nb_, nh_)) att_fetch_q(qn, qbuf, nb_, nh_, g, t);
         }
         const int cnt = min(KV_POS, cur.hi - cur.s);
         if (cnt > 0) {
@@ -1008,8 +1025,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
             }
             // start the next item
             item++;
-#pragma unroll
-            for (int kq = 0; kq < V_E / 16; kq++) { bq[kq][0] = bqn[kq][0]; bq[kq][1] = bqn[kq][1]; }
+            att_pack_q(bq, qn, g);
             m = -3.0e38f; den = 0.f;
 #pragma unroll
             for (int mt = 0; mt < V_E / 16; mt++)
