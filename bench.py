@@ -61,7 +61,7 @@ REF_DIR = os.path.join(ROOT, 'oracle', '_ref')          # an installed copy of t
 NCU_CAPTURE = {
     'cfg2': dict(bytes=292.2e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
     'cfg1': dict(bytes=257.6e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
-    'cfg3': dict(bytes=1484.8e6, positions=513.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b64.md (two steps at contexts 513 and 514) by the K/V bytes of this run\'s contexts'),
+    'cfg3': dict(bytes=1484.9e6, positions=513.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b64.md (two steps at contexts 513 and 514) by the K/V bytes of this run\'s contexts'),
 }
 NCU_SOURCE = 'no capture of this workload for the current kernel: see profiles/'
 
