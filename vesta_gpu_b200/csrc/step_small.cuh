@@ -304,7 +304,14 @@ __device__ __noinline__ void producer_weights(u32* bar, const int* __restrict__ 
 #pragma unroll 1
             for (int it = cta; it < ATT_ITEMS && !c.dead; it += ncta) {
                 const unsigned char* hs = WP + ((size_t)V_FUSE_BASE + (size_t)(l * V_H + it % V_H) * (JT_D * FUSE_US)) * FRAG_BYTES;
+#if V_FUSE_X
+                // only this CTA's share of the head's output tiles (the items of a head exchange their outputs)
+                const int xb = it / V_H, j0 = (xb * JT_D) / V_B, j1 = ((xb + 1) * JT_D) / V_B;
+                hs += (size_t)j0 * FUSE_US * FRAG_BYTES;
+                stream_tiles(c, hs, (j1 - j0) * FUSE_US, FUSE_PER);
+#else
                 stream_tiles(c, hs, JT_D * FUSE_US, FUSE_PER);
+#endif
             }
 #else
             if (!c.dead) stream_tiles(c, src, p.proj_nj * p.proj_nk, per_proj);
@@ -576,6 +583,62 @@ __device__ __noinline__ u32 proj_head(u32 st, u32* bar, int cta, zacc* __restric
     }
     return st;
 }
+#if V_FUSE_X
+// Exchange inside a head (every CTA holds at most one item): the V_B CTAs with the items of head h write their 64 outputs
+// to global memory as (value, tag) pairs in one 8-byte store each, the tag being the number of the attention phase
+// since the launch began (the buffer is cleared when a launch begins); a reader polls the pairs it needs until their
+// tags are this phase's (bounded): the data is its own flag, no counter, no fence, no second trip to L2.
+#define BAR_WHERE_HEAD 0xA00u
+__device__ __forceinline__ void x_put(u64* p, float v, u32 tag) {
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" :: "l"(p), "l"(((u64)tag << 32) | (u64)__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ u64 x_peek(const u64* p) {
+    u64 v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __noinline__ bool x_get_slow(u32* bar, const u64* p, u32 tag, int cta, float& out) {
+    const u64 t0 = now_ns();
+    u32 spins = 0;
+    for (;;) {
+        const u64 v = x_peek(p);
+        if ((u32)(v >> 32) == tag) { out = __uint_as_float((u32)v); return true; }
+        if ((++spins & 63u) == 0) {
+            if (ld_relaxed(bar + BAR_ABORT)) return false;
+            if (now_ns() - t0 > WAIT_NS) { give_up(bar, BAR_WHERE_HEAD, cta); return false; }
+        }
+    }
+}
+// This CTA's share [j0, j1) of the head's output tiles times the outputs of all V_B sequences (operand at V_SM_GACT, all
+// rows live): eight output tiles per ring slot, one per warp.
+__device__ __noinline__ u32 proj_head_x(u32 st, u32* bar, int cta, zacc* __restrict__ z1, int j0, int j1) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint4 bop[FUSE_US];
+#pragma unroll
+    for (int r = 0; r < FUSE_US; r++) bop[r] = lds16(smem + V_SM_GACT + r * ATILE + lane * 16);
+#pragma unroll 1
+    for (int jb = j0; jb < j1; jb += NW) {
+        const u32 chunk = st & ~ST_DEAD;
+        wait_full(st, bar, cta, chunk % V_NSLOT, (chunk / V_NSLOT) & 1u);
+        TRACE(53);
+        if (!(st & ST_DEAD) && jb + warp < j1) {
+            const unsigned char* tp = smem + V_SM_RING + (chunk % V_NSLOT) * SLOT_BYTES + warp * (FUSE_US * FRAG_BYTES) + lane * 16;
+            float a[4] = {0.f, 0.f, 0.f, 0.f}, l[4] = {0.f, 0.f, 0.f, 0.f};
+            uint4 w[FUSE_US];
+#pragma unroll
+            for (int r = 0; r < FUSE_US; r++) w[r] = lds16(tp + r * FRAG_BYTES);
+#pragma unroll
+            for (int r = 0; r < FUSE_US; r++) mma_hl(a, l, w[r], bop[r]);
+            const float f[4] = {a[0] + l[0], a[1] + l[1], a[2] + l[2], a[3] + l[3]};
+            red_tile(z1 + (jb + warp) * 16, f, lane, -1);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_bar(chunk % V_NSLOT));
+        st += 1u;
+    }
+    return st;
+}
+#endif
 #endif
 
 // ---------------------------------------------------------------------------------------------
@@ -775,7 +838,10 @@ __device__ __forceinline__ void q_store(u16* __restrict__ qop16, int b, int jx, 
 }
 
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const u32* __restrict__ qbuf,
-                                                float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos) {
+                                                float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos, u32 xphase) {
+#if V_FUSE_X
+    u64* xo = reinterpret_cast<u64*>(part);                                    // [head][sequence][V_E] (value, tag): the items' outputs
+#endif
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
     if (ntl == 0) return;
@@ -916,7 +982,10 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                     dd += ms[w * (V_E + 2) + 1] * sc;
                     num += ms[w * (V_E + 2) + 2 + c.tid] * sc;
                 }
-#if V_FUSE_PROJ
+#if V_FUSE_X
+                // the item's outputs for the other CTAs of its head (a sequence that has not started attends to nothing)
+                x_put(xo + ((size_t)((e.x >> 8) & 255) * V_B + (e.x & 255)) * V_E + c.tid, dd > 0.f ? __fdividef(num, dd) : 0.f, xphase);
+#elif V_FUSE_PROJ
                 act_store1(smem + V_SM_GACT, e.x & 255, c.tid, dd > 0.f ? __fdividef(num, dd) : 0.f);      // a sequence that has not started attends to nothing
 #else
                 float* out = part + (size_t)e.w * PART_STRIDE;
@@ -924,7 +993,28 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 if (c.tid == 0) { out[0] = M; out[1] = dd; }
 #endif
             }
-#if V_FUSE_PROJ
+#if V_FUSE_X
+            {
+                const int xb = e.x & 255, xh = (e.x >> 8) & 255;
+                TRACE(48);
+                // the outputs of all V_B sequences for this head as the operand of the projection (this CTA's own come
+                // back the same way): every thread polls the pairs it converts
+#pragma unroll 1
+                for (int i = c.tid; i < V_B * V_E; i += NCONS) {
+                    const int b2 = i / V_E, k = i - b2 * V_E;
+                    const u64* src = xo + ((size_t)xh * V_B + b2) * V_E + k;
+                    float v = 0.f;
+                    const u64 got = x_peek(src);
+                    if ((u32)(got >> 32) == xphase) v = __uint_as_float((u32)got);
+                    else if (c.dead || !x_get_slow(c.bar, src, xphase, c.cta, v)) { c.dead = true; v = 0.f; }
+                    act_store1(smem + V_SM_GACT, b2, k, v);
+                }
+                cons_sync();
+                if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
+                ctx_set(c, proj_head_x(ctx_state(c), c.bar, c.cta, z1, (xb * JT_D) / V_B, ((xb + 1) * JT_D) / V_B));
+                cons_sync();                           // every warp has read the operand before the next item clears it
+            }
+#elif V_FUSE_PROJ
             cons_sync();
             TRACE(48);
             ctx_set(c, proj_head(ctx_state(c), c.bar, c.cta, z1, e.x & 255));
@@ -1097,6 +1187,12 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (c.tid < V_B) s_pos[c.tid] = __ldcg(a.t + c.tid * V_TSTRIDE);
         cons_sync();
     }
+#if V_FUSE_X
+    if (step == 0 && c.cta == 0) {
+        // the tags of the heads' exchange buffer (a launch counts its attention phases from one; read after the next barrier)
+        for (int i = c.tid; i < V_H * V_B * V_E; i += NCONS) reinterpret_cast<u64*>(part)[i] = 0ull;
+    }
+#endif
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
 #pragma unroll 1
     for (int i = gtid; i < V_B * V_D; i += gthreads) {
@@ -1160,7 +1256,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
         // ---- attention
         TRACE(2);
-        attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos);
+        attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos, (u32)(step * V_L + l + 1));
         TRACE(21);
         TICK(4);
         phase_end(c);
