@@ -142,7 +142,9 @@ def test_lowered_fields_match_reference_contract():
     off2, _, shape2 = low.scratch['next']
     assert shape2 == (8,) and off2 >= 8 * 50257 and low.scratch_floats > off2 + 8
     assert low.shared_bytes <= 227 * 1024
-    assert low.barriers_per_launch == 1 + 3 * 12          # three per layer (the projection rides on the attention items); the reference needs 113 at batch 8
+    assert low.barriers_per_launch == 1 + 2 * 12          # two per layer (query / K / V and the heads' outputs travel as tagged values between the CTAs that need them); the reference needs 113 at batch 8
+    assert lower_for(GPT2_SMALL, 8, 384, tune=dict(qkv_exchange=False)).barriers_per_launch == 1 + 3 * 12
+    assert lower_for(GPT2_SMALL, 8, 384, tune=dict(fuse_proj=False)).barriers_per_launch == 1 + 4 * 12
     assert 'vesta_step' in low.src and 'vesta_pack' in low.src and low.counters >= 64
     assert len(low.plan) >= 8 and all(len(p) == 2 for p in low.plan)
     no_fb = lower_for(GPT2_SMALL, 1, 64, feedback=False)

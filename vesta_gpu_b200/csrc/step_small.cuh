@@ -202,7 +202,7 @@ __device__ __noinline__ void build_tile_list(int cta, int ncta, const int* s_pos
 #pragma unroll 1
         for (; s < hi && n < V_MAXTL; s += KV_POS) {
             const int cnt = min(KV_POS, hi - s);
-            const int flags = ((s + KV_POS >= hi) ? TL_LAST : 0) | ((live < V_KVST && s_pos[b] >= s && s_pos[b] < s + cnt) ? TL_PATCH : 0);
+            const int flags = ((s + KV_POS >= hi) ? TL_LAST : 0) | (((V_FUSE_X2 || live < V_KVST) && s_pos[b] >= s && s_pos[b] < s + cnt) ? TL_PATCH : 0);
             tl[n++] = make_int4(b | (h << 8) | flags, s, cnt, it);
             live++;
         }
@@ -841,6 +841,11 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                                                 float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos, u32 xphase) {
 #if V_FUSE_X
     u64* xo = reinterpret_cast<u64*>(part);                                    // [head][sequence][V_E] (value, tag): the items' outputs
+#if V_FUSE_X2
+    const u64* xq = xo + (size_t)V_H * V_B * V_E;                              // the same for the queries (fp16 head | remainder << 16),
+    const u64* xk = xq + (size_t)V_H * V_B * V_E;                              // the K rows and the V rows of the current position
+    const u64* xv = xk + (size_t)V_H * V_B * V_E;
+#endif
 #endif
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
@@ -849,6 +854,41 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
     u32 bq[V_E / 16][2], bqn[V_E / 16][2];           // the query of this item and of the next one
 #pragma unroll
     for (int kq = 0; kq < V_E / 16; kq++) { bqn[kq][0] = 0; bqn[kq][1] = 0; }
+#if V_FUSE_X2
+    // No grid barrier between the QKV phase and this one: the query of the item and the K / V rows of the current position
+    // come as tagged values from the CTAs that computed them (x_put in the QKV epilogue); threads 0..63 poll the query
+    // (fp16 head and remainder in one word) and leave it in shared memory in operand order, threads 64..191 poll the K
+    // and V rows and keep their half until the tile that holds the position has landed.
+    u32 kvhalf = 0;
+    {
+        const int4 e = tl[0];
+        const int b = e.x & 255, h = (e.x >> 8) & 255;
+        u16* qs = reinterpret_cast<u16*>(smem + V_SM_RED);
+        if (c.tid < 3 * V_E) {
+            const int part = c.tid / V_E, el = c.tid - part * V_E;
+            const u64* src = (part == 0 ? xq : part == 1 ? xk : xv) + ((size_t)h * V_B + b) * V_E + el;
+            float got = 0.f;
+            const u64 w = x_peek(src);
+            if ((u32)(w >> 32) == xphase) got = __uint_as_float((u32)w);
+            else if (c.dead || !x_get_slow(c.bar, src, xphase, c.cta, got)) { c.dead = true; got = 0.f; }
+            const u32 bits = __float_as_uint(got);
+            if (part == 0) {
+                const int kq = el >> 4, kk = el & 15;
+                u16* q = qs + ((kk & 7) >> 1) * 16 + kq * 4 + (kk >> 3) * 2 + (kk & 1);
+                q[0] = (u16)(bits & 0xffffu); q[64] = (u16)(bits >> 16);
+            } else kvhalf = bits & 0xffffu;
+        }
+        cons_sync();
+        if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
+        uint4 x = make_uint4(0, 0, 0, 0), y = make_uint4(0, 0, 0, 0);
+        if (g < 2) {
+            const uint4* p = reinterpret_cast<const uint4*>(qs + g * 64 + t * 16);
+            x = p[0]; y = p[1];
+        }
+        bq[0][0] = x.x; bq[0][1] = x.y; bq[1][0] = x.z; bq[1][1] = x.w;
+        bq[2][0] = y.x; bq[2][1] = y.y; bq[3][0] = y.z; bq[3][1] = y.w;
+    }
+#else
     {
         const int4 e = tl[0];
         att_load_q(bq, qbuf, e.x & 255, (e.x >> 8) & 255, g, t);        // requested first: its trip to L2 overlaps the copies below
@@ -876,6 +916,7 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         }
         if (any) { cp_wait(); cons_sync(); }
     }
+#endif
     TRACE(44);
 
     float m = -3.0e38f, den = 0.f, o[V_E / 16][4];   // o[mt]: dims mt*16 + g (regs 0+1) and mt*16 + g + 8 (regs 2+3), lanes t == 0
@@ -889,16 +930,28 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
         const int4 e = tl[k];
         const bool last = (e.x & TL_LAST) != 0;
         const int cnt = e.z;
+#if !V_FUSE_X2
         if (last && k + 1 < ntl) {
             const int4 en = tl[k + 1];                  // the next item's query is requested now and used after this tile
             att_load_q(bqn, qbuf, en.x & 255, (en.x >> 8) & 255, g, t);
         }
+#endif
         if (cnt > 0) {
             const u32 stage = c.kvn % V_KVST;
             wait_mbar(c, kv_bar(stage), (c.kvn / V_KVST) & 1u, 0x500u);
             TRACE(45);
             const unsigned char* kt = smem + V_SM_KV + stage * KV_STAGE_BYTES;
             const unsigned char* vt = kt + KV_TILE_BYTES;
+#if V_FUSE_X2
+            if (e.x & TL_PATCH) {
+                // the row of the current position (the tile may have been fetched before the row reached the cache)
+                if (c.tid >= V_E && c.tid < 3 * V_E) {
+                    const int part = c.tid / V_E, el = c.tid - part * V_E, r = s_pos[e.x & 255] - e.y;
+                    *reinterpret_cast<u16*>(smem + V_SM_KV + stage * KV_STAGE_BYTES + (part == 2 ? KV_TILE_BYTES : 0) + kv_off(r, el >> 3) + (el & 7) * 2) = (u16)kvhalf;
+                }
+                cons_sync();
+            }
+#endif
             const int p0 = c.warp * 16;                                 // this warp's positions of the tile
             if (p0 < cnt && !c.dead) {
                 // scores of 16 positions: rows g and g + 8 of the tile slice, in the lanes with t == 0
@@ -1188,9 +1241,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
         cons_sync();
     }
 #if V_FUSE_X
-    if (step == 0 && c.cta == 0) {
-        // the tags of the heads' exchange buffer (a launch counts its attention phases from one; read after the next barrier)
-        for (int i = c.tid; i < V_H * V_B * V_E; i += NCONS) reinterpret_cast<u64*>(part)[i] = 0ull;
+    if (step == 0) {
+        // the tags of the exchange buffers (a launch counts its attention phases from one; read after the next barrier)
+#pragma unroll 1
+        for (int i = gtid; i < (V_FUSE_X2 ? 4 : 1) * V_H * V_B * V_E; i += gthreads) reinterpret_cast<u64*>(part)[i] = 0ull;
     }
 #endif
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
@@ -1239,19 +1293,40 @@ __device__ __forceinline__ void step_body(const Args& a) {
                 if (b < V_B) {
                     // q to scratch, K and V rounded to fp16 into the cache at t
                     const int jx = (p.qkv_j0 + (o >> 7)) * 16 + j_in;
+#if V_FUSE_X2
+                    // query, K and V of the current position as tagged values for the CTA that holds the attention item
+                    // (it does not wait at a grid barrier for them); K and V also go to the cache, for the steps to come
+                    const int prt = jx / V_D, jd = jx - prt * V_D, hh = jd / V_E, el = jd - hh * V_E;
+                    u64* dst = reinterpret_cast<u64*>(part) + (size_t)(1 + prt) * V_H * V_B * V_E + ((size_t)hh * V_B + b) * V_E + el;
+                    if (prt == 0) {
+                        const float vs = V_SCALE_IS_POW2 ? v * (1.0f / V_SCALE) : v;
+                        const u16 hi = f2h(vs);
+                        x_put(dst, __uint_as_float((u32)hi | ((u32)f2h(vs - h2f(hi)) << 16)), (u32)(step * V_L + l + 1));
+                    } else {
+                        const u16 hv = f2h(v);
+                        if (s_pos[b] >= 0) (prt == 1 ? a.keys : a.vals)[((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + jd] = hv;
+                        x_put(dst, __uint_as_float((u32)hv), (u32)(step * V_L + l + 1));
+                    }
+#else
                     if (jx < V_D) q_store(reinterpret_cast<u16*>(qbuf), b, jx, v);
                     else if (s_pos[b] >= 0) {
                         const size_t at = ((size_t)(b * V_L + l) * V_TMAX + s_pos[b]) * V_D + (jx % V_D);
                         if (jx < 2 * V_D) a.keys[at] = f2h(v); else a.vals[at] = f2h(v);
                     }
+#endif
                 }
             }
         }
         TRACE(20);
         TICK(2);
+#if V_FUSE_X2
+        cons_sync();                        // (the partial sums in shared memory have been read: the query is staged there next)
+        TRACE(30);
+#else
         phase_end(c);
         TRACE(30);
         phase_wait(c);
+#endif
         TICK(3);
 
         // ---- attention

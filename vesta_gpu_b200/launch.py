@@ -99,7 +99,7 @@ def compile_cubin(src, arch=ARCH, cache=True):
 
 
 STATUS_WHERE = {0x100: 'grid barrier', 0x200: 'weight stream (producer)', 0x300: 'weight stream (consumer)', 0x400: 'step flag', 0x500: 'K/V tile', 0x600: 'logits operand', 0x700: 'tensor-core tile', 0x800: 'K/V stage (producer)',
-                0x900: 'token or position out of range'}
+                0x900: 'token or position out of range', 0xA00: 'exchange between CTAs (tagged values)'}
 
 
 class Kernel:
