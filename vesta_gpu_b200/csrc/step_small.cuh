@@ -532,6 +532,31 @@ __device__ __forceinline__ u32 gemm_fold_slice(u32 st, u32* bar, int cta, int nu
     }
 }
 
+// Exchange between CTAs without a grid barrier (every CTA holds at most one attention item): the producers write their
+// values to global memory as (value, tag) pairs in one 8-byte store each, the tag being the number of the attention phase
+// since the launch began (the buffer is cleared when a launch begins); a reader polls the pairs it needs until their
+// tags are this phase's (bounded): the data is its own flag, no counter, no fence, no second trip to L2.
+#define BAR_WHERE_HEAD 0xA00u
+__device__ __forceinline__ void x_put(u64* p, float v, u32 tag) {
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" :: "l"(p), "l"(((u64)tag << 32) | (u64)__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ u64 x_peek(const u64* p) {
+    u64 v;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __noinline__ bool x_get_slow(u32* bar, const u64* p, u32 tag, int cta, float& out) {
+    const u64 t0 = now_ns();
+    u32 spins = 0;
+    for (;;) {
+        const u64 v = x_peek(p);
+        if ((u32)(v >> 32) == tag) { out = __uint_as_float((u32)v); return true; }
+        if ((++spins & 63u) == 0) {
+            if (ld_relaxed(bar + BAR_ABORT)) return false;
+            if (now_ns() - t0 > WAIT_NS) { give_up(bar, BAR_WHERE_HEAD, cta); return false; }
+        }
+    }
+}
 #if V_FUSE_PROJ
 // The projection of one attention item (fused mode): the head's 64 outputs (operand at V_SM_GACT, one live row `only`)
 // times the head's 64 rows of the projection, JT_D output tiles x FUSE_US fold tiles, eight output tiles per ring slot.
@@ -584,31 +609,6 @@ __device__ __noinline__ u32 proj_head(u32 st, u32* bar, int cta, zacc* __restric
     return st;
 }
 #if V_FUSE_X
-// Exchange inside a head (every CTA holds at most one item): the V_B CTAs with the items of head h write their 64 outputs
-// to global memory as (value, tag) pairs in one 8-byte store each, the tag being the number of the attention phase
-// since the launch began (the buffer is cleared when a launch begins); a reader polls the pairs it needs until their
-// tags are this phase's (bounded): the data is its own flag, no counter, no fence, no second trip to L2.
-#define BAR_WHERE_HEAD 0xA00u
-__device__ __forceinline__ void x_put(u64* p, float v, u32 tag) {
-    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" :: "l"(p), "l"(((u64)tag << 32) | (u64)__float_as_uint(v)) : "memory");
-}
-__device__ __forceinline__ u64 x_peek(const u64* p) {
-    u64 v;
-    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __noinline__ bool x_get_slow(u32* bar, const u64* p, u32 tag, int cta, float& out) {
-    const u64 t0 = now_ns();
-    u32 spins = 0;
-    for (;;) {
-        const u64 v = x_peek(p);
-        if ((u32)(v >> 32) == tag) { out = __uint_as_float((u32)v); return true; }
-        if ((++spins & 63u) == 0) {
-            if (ld_relaxed(bar + BAR_ABORT)) return false;
-            if (now_ns() - t0 > WAIT_NS) { give_up(bar, BAR_WHERE_HEAD, cta); return false; }
-        }
-    }
-}
 // This CTA's share [j0, j1) of the head's output tiles times the outputs of all V_B sequences (operand at V_SM_GACT, all
 // rows live): eight output tiles per ring slot, one per warp.
 __device__ __noinline__ u32 proj_head_x(u32 st, u32* bar, int cta, zacc* __restrict__ z1, int j0, int j1) {
@@ -838,14 +838,14 @@ __device__ __forceinline__ void q_store(u16* __restrict__ qop16, int b, int jx, 
 }
 
 __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ keys, const u16* __restrict__ vals, const u32* __restrict__ qbuf,
-                                                float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos, u32 xphase) {
+                                                float* __restrict__ part, zacc* __restrict__ z1, int l, const int* s_pos, u32 xphase, u64* __restrict__ xbase) {
 #if V_FUSE_X
-    u64* xo = reinterpret_cast<u64*>(part);                                    // [head][sequence][V_E] (value, tag): the items' outputs
+    u64* xo = xbase;                                                           // [head][sequence][V_E] (value, tag): the items' outputs
+#endif
 #if V_FUSE_X2
-    const u64* xq = xo + (size_t)V_H * V_B * V_E;                              // the same for the queries (fp16 head | remainder << 16),
+    const u64* xq = xbase + (size_t)(V_FUSE_X ? 1 : 0) * V_H * V_B * V_E;      // the same for the queries (fp16 head | remainder << 16),
     const u64* xk = xq + (size_t)V_H * V_B * V_E;                              // the K rows and the V rows of the current position
     const u64* xv = xk + (size_t)V_H * V_B * V_E;
-#endif
 #endif
     const int4* tl = reinterpret_cast<const int4*>(smem + V_SM_MISC + MISC_TL);
     const int ntl = *reinterpret_cast<const volatile int*>(smem + V_SM_MISC + MISC_NTL);
@@ -1240,11 +1240,11 @@ __device__ __forceinline__ void step_body(const Args& a) {
         if (c.tid < V_B) s_pos[c.tid] = __ldcg(a.t + c.tid * V_TSTRIDE);
         cons_sync();
     }
-#if V_FUSE_X
+#if V_FUSE_X || V_FUSE_X2
     if (step == 0) {
         // the tags of the exchange buffers (a launch counts its attention phases from one; read after the next barrier)
 #pragma unroll 1
-        for (int i = gtid; i < (V_FUSE_X2 ? 4 : 1) * V_H * V_B * V_E; i += gthreads) reinterpret_cast<u64*>(part)[i] = 0ull;
+        for (int i = gtid; i < ((V_FUSE_X ? 1 : 0) + (V_FUSE_X2 ? 3 : 0)) * V_H * V_B * V_E; i += gthreads) reinterpret_cast<u64*>(a.S + V_OFF_X)[i] = 0ull;
     }
 #endif
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
@@ -1297,7 +1297,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
                     // query, K and V of the current position as tagged values for the CTA that holds the attention item
                     // (it does not wait at a grid barrier for them); K and V also go to the cache, for the steps to come
                     const int prt = jx / V_D, jd = jx - prt * V_D, hh = jd / V_E, el = jd - hh * V_E;
-                    u64* dst = reinterpret_cast<u64*>(part) + (size_t)(1 + prt) * V_H * V_B * V_E + ((size_t)hh * V_B + b) * V_E + el;
+                    u64* dst = reinterpret_cast<u64*>(a.S + V_OFF_X) + (size_t)((V_FUSE_X ? 1 : 0) + prt) * V_H * V_B * V_E + ((size_t)hh * V_B + b) * V_E + el;
                     if (prt == 0) {
                         const float vs = V_SCALE_IS_POW2 ? v * (1.0f / V_SCALE) : v;
                         const u16 hi = f2h(vs);
@@ -1331,7 +1331,7 @@ __device__ __forceinline__ void step_body(const Args& a) {
 
         // ---- attention
         TRACE(2);
-        attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos, (u32)(step * V_L + l + 1));
+        attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos, (u32)(step * V_L + l + 1), reinterpret_cast<u64*>(a.S + V_OFF_X));
         TRACE(21);
         TICK(4);
         phase_end(c);
