@@ -145,7 +145,8 @@ def test_lowered_fields_match_reference_contract():
     assert low.barriers_per_launch == 1 + 2 * 12          # two per layer (query / K / V and the heads' outputs travel as tagged values between the CTAs that need them); the reference needs 113 at batch 8
     assert lower_for(GPT2_SMALL, 8, 384, tune=dict(qkv_exchange=False)).barriers_per_launch == 1 + 3 * 12
     assert lower_for(GPT2_SMALL, 8, 384, tune=dict(fuse_proj=False, qkv_exchange=False)).barriers_per_launch == 1 + 4 * 12
-    assert lower_for(GPT2_SMALL, 1, 384).barriers_per_launch == 1 + 3 * 12             # one sequence: the pairs are cut into chunks, the projection keeps its phase
+    assert lower_for(GPT2_SMALL, 1, 384).barriers_per_launch == 1 + 2 * 12             # one sequence: the pairs are cut into chunks, the projection keeps its phase but polls the chunks' results
+    assert lower_for(GPT2_SMALL, 1, 384, tune=dict(part_exchange=False)).barriers_per_launch == 1 + 3 * 12
     assert 'vesta_step' in low.src and 'vesta_pack' in low.src and low.counters >= 64
     assert len(low.plan) >= 8 and all(len(p) == 2 for p in low.plan)
     no_fb = lower_for(GPT2_SMALL, 1, 64, feedback=False)

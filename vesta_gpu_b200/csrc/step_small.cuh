@@ -779,7 +779,7 @@ __device__ __noinline__ void ln_to_act(int cta, int ncta, const zacc* __restrict
 
 // Attention output for the fold tiles [k0, k0 + nk) of the projection, merged from the per-chunk partial results
 // (m, sum, unnormalised o[V_E]) of the attention phase, into operand tiles 0 .. nk-1.
-__device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act) {
+__device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ part, int k0, int nk, unsigned char* act, u32 xphase) {
     const int cols = nk * 16;
     const float rcpk = rcp_fast(nk);
 #pragma unroll 1
@@ -788,8 +788,35 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
         const float* p = part + (size_t)((b * V_H + h) * V_NCH) * PART_STRIDE;
         // all loads first (independent, one round trip), then the arithmetic
         float mm[V_NCH], dd[V_NCH], oo[V_NCH], M = -3.0e38f;
+#if V_FUSE_X3
+        // (no grid barrier after the attention phase: the partial results are tagged values, polled until they are this phase's)
+        const u64* p64 = reinterpret_cast<const u64*>(part) + (size_t)((b * V_H + h) * V_NCH) * PART_STRIDE;
+        // all values of a round are requested together (one trip to L2 per round, not per value)
+        u64 raw[V_NCH][3];
+        const u64 t0 = now_ns();
+        u32 spins = 0;
+        for (;;) {
+#pragma unroll
+            for (int ch = 0; ch < V_NCH; ch++) { raw[ch][0] = x_peek(p64 + ch * PART_STRIDE); raw[ch][1] = x_peek(p64 + ch * PART_STRIDE + 1); raw[ch][2] = x_peek(p64 + ch * PART_STRIDE + 2 + e); }
+            bool all = true;
+#pragma unroll
+            for (int ch = 0; ch < V_NCH; ch++) all = all && (u32)(raw[ch][0] >> 32) == xphase && (u32)(raw[ch][1] >> 32) == xphase && (u32)(raw[ch][2] >> 32) == xphase;
+            if (all || c.dead) break;
+            if ((++spins & 63u) == 0) {
+                if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; break; }
+                if (now_ns() - t0 > WAIT_NS) { give_up(c.bar, BAR_WHERE_HEAD, c.cta); c.dead = true; break; }
+            }
+        }
+#pragma unroll
+        for (int ch = 0; ch < V_NCH; ch++) {
+            mm[ch] = c.dead ? -3.0e38f : __uint_as_float((u32)raw[ch][0]);
+            dd[ch] = c.dead ? 0.f : __uint_as_float((u32)raw[ch][1]);
+            oo[ch] = c.dead ? 0.f : __uint_as_float((u32)raw[ch][2]);
+        }
+#else
 #pragma unroll
         for (int ch = 0; ch < V_NCH; ch++) { mm[ch] = __ldcg(p + ch * PART_STRIDE); dd[ch] = __ldcg(p + ch * PART_STRIDE + 1); oo[ch] = __ldcg(p + ch * PART_STRIDE + 2 + e); }
+#endif
 #pragma unroll
         for (int ch = 0; ch < V_NCH; ch++) M = fmaxf(M, mm[ch]);
         float num = 0.f, den = 0.f;
@@ -802,6 +829,9 @@ __device__ __forceinline__ void merge_to_act(Ctx& c, const float* __restrict__ p
         act_store1(act, b, kk, den > 0.f ? __fdividef(num, den) : 0.f);      // a sequence that has not started attends to nothing
     }
     cons_sync();
+#if V_FUSE_X3
+    if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
+#endif
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1041,9 +1071,15 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
 #elif V_FUSE_PROJ
                 act_store1(smem + V_SM_GACT, e.x & 255, c.tid, dd > 0.f ? __fdividef(num, dd) : 0.f);      // a sequence that has not started attends to nothing
 #else
+#if V_FUSE_X3
+                u64* out = reinterpret_cast<u64*>(part) + (size_t)e.w * PART_STRIDE;
+                x_put(out + 2 + c.tid, num, xphase);
+                if (c.tid == 0) { x_put(out, M, xphase); x_put(out + 1, dd, xphase); }
+#else
                 float* out = part + (size_t)e.w * PART_STRIDE;
                 out[2 + c.tid] = num;
                 if (c.tid == 0) { out[0] = M; out[1] = dd; }
+#endif
 #endif
             }
 #if V_FUSE_X
@@ -1245,6 +1281,10 @@ __device__ __forceinline__ void step_body(const Args& a) {
         // the tags of the exchange buffers (a launch counts its attention phases from one; read after the next barrier)
 #pragma unroll 1
         for (int i = gtid; i < ((V_FUSE_X ? 1 : 0) + (V_FUSE_X2 ? 3 : 0)) * V_H * V_B * V_E; i += gthreads) reinterpret_cast<u64*>(a.S + V_OFF_X)[i] = 0ull;
+#if V_FUSE_X3
+#pragma unroll 1
+        for (int i = gtid; i < ATT_ITEMS * PART_STRIDE; i += gthreads) reinterpret_cast<u64*>(part)[i] = 0ull;
+#endif
     }
 #endif
     // Q1: z0 = wte[x] + wpe[t]; the vector the first projection is combined into starts at zero
@@ -1334,24 +1374,31 @@ __device__ __forceinline__ void step_body(const Args& a) {
         attention_phase(c, a.keys, a.vals, qbuf, part, z1, l, s_pos, (u32)(step * V_L + l + 1), reinterpret_cast<u64*>(a.S + V_OFF_X));
         TRACE(21);
         TICK(4);
+#if !V_FUSE_X3
         phase_end(c);
         fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
                      a.fcb + (size_t)l * V_F + p.fc_j0 * 16, p.fc_nj);
         TRACE(31);
         phase_wait(c);
+#endif
         TICK(5);
 
 #if !V_FUSE_PROJ
-        // ---- attention projection + residual
+        // ---- attention projection + residual (V_FUSE_X3: no barrier before it, the partial results of the attention items
+        // are polled as tagged values)
         TRACE(3);
         if (p.proj_nj) {
-            merge_to_act(c, part, p.proj_k0, p.proj_nk, act);
+            merge_to_act(c, part, p.proj_k0, p.proj_nk, act, (u32)(step * V_L + l + 1));
             TRACE(12);
             ctx_set(c, gemm_fold_slice(ctx_state(c), c.bar, c.cta, p.proj_nj, p.proj_nk, p.upc_proj, act, z1 + p.proj_j0 * 16));
         }
         TRACE(22);
         TICK(6);
         phase_end(c);
+#if V_FUSE_X3
+        fetch_params(c, a.ln2w + (size_t)l * V_D, a.ln2b + (size_t)l * V_D, a.pb + (size_t)l * V_D,
+                     a.fcb + (size_t)l * V_F + p.fc_j0 * 16, p.fc_nj);
+#endif
         TRACE(32);
         phase_wait(c);
         TICK(7);

@@ -438,6 +438,8 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     # (also without the fused projection, at one or two sequences, where the pairs are cut into chunks: one item per CTA
     # is all it takes)
     fuse_x2 = bool(tune.get('qkv_exchange', True) and att_items <= grid and (fuse_x or not fuse))
+    # ... and, without the fused projection, from the attention items to the projection phase (their partial results)
+    fuse_x3 = bool(fuse_x2 and not fuse and tune.get('part_exchange', True))
     maxtl = math.ceil(att_items / grid) * math.ceil(math.ceil(tmax / nch) / 128)
     # K/V stages of 32 KB: two tiles in flight where a CTA has several per layer, one (and a deeper weight ring) otherwise
     kvst = int(tune.get('kv_stages', 2 if maxtl > 1 else 1))
@@ -449,7 +451,7 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     off_z = _up(off_next + B)
     off_q = off_z + 3 * _up(B * D) * (2 if fixed_sums else 1)
     off_part = off_q + _up(B * D)
-    off_x = off_part + _up(att_items * (E + 2))                            # exchange buffers of 8-byte (value, tag) pairs:
+    off_x = off_part + _up(att_items * (E + 2) * (2 if fuse_x3 else 1))    # (fuse_x3: the partial results as (value, tag) pairs); exchange buffers of such pairs:
     off_best = off_x + _up(2 * H * B * E * (int(fuse_x) + 3 * int(fuse_x2)))   # the heads' outputs (fuse_x), then query, K and V rows (fuse_x2)
     scratch_floats = off_best + _up(2 * B)
     scratch = {env['$logit']: (off_logit, ('bt', env['$n']), (B, N)), env['$next']: (off_next, ('bt',), (B,))}
@@ -477,7 +479,7 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     defs = dict(V_NW=nw, V_NPROD=2, V_B=B, V_L=L, V_D=D, V_H=H, V_E=E, V_F=F, V_N=N, V_TMAX=tmax, V_CPOS=cpos,
                 V_EPS=_f32(dims['eps']), V_SCALE=_f32(scale), V_SCALE_IS_POW2=int(math.frexp(scale)[0] == 0.5),
                 V_GELU_A=_f32(dims['gelu'][0]), V_GELU_B=_f32(dims['gelu'][1]), V_GELU_C=_f32(dims['gelu'][2]),
-                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_WN=wn, V_FIXED=int(fixed_sums), V_FUSE_PROJ=int(fuse), V_FUSE_X=int(fuse_x), V_FUSE_X2=int(fuse_x2), V_FUSE_BASE=(fuse_base if fuse else 0), V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
+                V_NSLOT=nslot, V_CH=ch, V_KVST=kvst, V_UMAX=umax, V_WN=wn, V_FIXED=int(fixed_sums), V_FUSE_PROJ=int(fuse), V_FUSE_X=int(fuse_x), V_FUSE_X2=int(fuse_x2), V_FUSE_X3=int(fuse_x3), V_FUSE_BASE=(fuse_base if fuse else 0), V_NCH=nch, V_MAXTL=maxtl, V_MAXGRID=grid,
                 V_TSTRIDE=int(t_per_token), V_FEEDBACK=int(bool(fb)), V_TSTEP=int(fb.get(t_name, 0)),
                 V_TIMING=int(timing), V_PLEN=int(prompt_len) if fb else 0,
                 V_OFF_LOGIT=off_logit, V_OFF_NEXT=off_next, V_OFF_Z=off_z, V_OFF_Q=off_q, V_OFF_PART=off_part, V_OFF_X=off_x, V_OFF_BEST=off_best,
@@ -509,10 +511,10 @@ def _lower_small(env, dims, res, roles, fb, B, tmax, cpos, t_per_token, t_name, 
     ]
     sites = ['embed', 'barrier'] + ['qkv', 'barrier', 'attention', 'barrier', 'proj', 'barrier', 'mlp', 'barrier'] + ['logits', 'finish']
     return Lowered(src=src, params=params, scratch=scratch, scratch_floats=scratch_floats, shared_bytes=shared,
-                   barriers_per_launch=1 + (4 - int(fuse) - int(fuse_x2)) * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
+                   barriers_per_launch=1 + (4 - int(fuse) - int(fuse_x2) - int(fuse_x3)) * L, plan=plan, sites=sites, counters=32 + max(grid, 1024),
                    block=(nw + 2) * 32, grid=grid, place=rec, packed_bytes=tiles * 512, pack_params=pack_params,
                    dims=dict(dims, B=B, NB=1, tmax=tmax, notes=notes, WG=WG, chunk_tiles=ch, tc=False, ksplit=False, kernel='small', warps=nw,
-                             nch=nch, kv_stages=kvst, ring_slots=nslot, fuse_proj=fuse, fuse_exchange=fuse_x, qkv_exchange=fuse_x2, fuse_base=(fuse_base if fuse else 0), ordered=fixed_sums), roles=roles)
+                             nch=nch, kv_stages=kvst, ring_slots=nslot, fuse_proj=fuse, fuse_exchange=fuse_x, qkv_exchange=fuse_x2, part_exchange=fuse_x3, fuse_base=(fuse_base if fuse else 0), ordered=fixed_sums), roles=roles)
 
 def lower(text, res, axis_max, batch=1, per_token=(), outputs=(), feedback=None, timing=False,
           grid=DEFAULT_SMS, act_lo=None, prompt_len=0, slab_tiles=None, tune=None, row_seq=False):
