@@ -1088,15 +1088,31 @@ __device__ __forceinline__ void attention_phase(Ctx& c, const u16* __restrict__ 
                 TRACE(48);
                 // the outputs of all V_B sequences for this head as the operand of the projection (this CTA's own come
                 // back the same way): every thread polls the pairs it converts
-#pragma unroll 1
-                for (int i = c.tid; i < V_B * V_E; i += NCONS) {
-                    const int b2 = i / V_E, k = i - b2 * V_E;
-                    const u64* src = xo + ((size_t)xh * V_B + b2) * V_E + k;
-                    float v = 0.f;
-                    const u64 got = x_peek(src);
-                    if ((u32)(got >> 32) == xphase) v = __uint_as_float((u32)got);
-                    else if (c.dead || !x_get_slow(c.bar, src, xphase, c.cta, v)) { c.dead = true; v = 0.f; }
-                    act_store1(smem + V_SM_GACT, b2, k, v);
+                {
+                    constexpr int XN = (V_B * V_E + NCONS - 1) / NCONS;      // pairs per thread, requested together in every round
+                    u64 got[XN];
+                    const u64 t0 = now_ns();
+                    u32 spins = 0;
+                    for (;;) {
+                        bool all = true;
+#pragma unroll
+                        for (int j = 0; j < XN; j++) {
+                            const int i = c.tid + j * NCONS;
+                            got[j] = i < V_B * V_E ? x_peek(xo + (size_t)xh * V_B * V_E + i) : ((u64)xphase << 32);
+                        }
+#pragma unroll
+                        for (int j = 0; j < XN; j++) all = all && (u32)(got[j] >> 32) == xphase;
+                        if (all || c.dead) break;
+                        if ((++spins & 63u) == 0) {
+                            if (ld_relaxed(c.bar + BAR_ABORT)) { c.dead = true; break; }
+                            if (now_ns() - t0 > WAIT_NS) { give_up(c.bar, BAR_WHERE_HEAD, c.cta); c.dead = true; break; }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < XN; j++) {
+                        const int i = c.tid + j * NCONS;
+                        if (i < V_B * V_E) act_store1(smem + V_SM_GACT, i / V_E, i % V_E, c.dead ? 0.f : __uint_as_float((u32)got[j]));
+                    }
                 }
                 cons_sync();
                 if (!c.dead && ld_relaxed(c.bar + BAR_ABORT)) c.dead = true;
