@@ -59,8 +59,8 @@ REF_DIR = os.path.join(ROOT, 'oracle', '_ref')          # an installed copy of t
 # context (attended positions per sequence). A bench launch attends more positions: the K/V part is scaled by the
 # positions, the weights are read once either way. Workloads without a capture report null.
 NCU_CAPTURE = {
-    'cfg2': dict(bytes=292.2e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
-    'cfg1': dict(bytes=257.6e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
+    'cfg2': dict(bytes=291.0e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
+    'cfg1': dict(bytes=256.3e6, positions=131.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b1_b8.md (two steps at contexts 131 and 132) by the K/V bytes of this run\'s contexts'),
     'cfg3': dict(bytes=1484.9e6, positions=513.5, source='scaled from the ncu capture in profiles/vesta_step_gpt2_small_b64.md (two steps at contexts 513 and 514) by the K/V bytes of this run\'s contexts'),
 }
 NCU_SOURCE = 'no capture of this workload for the current kernel: see profiles/'
