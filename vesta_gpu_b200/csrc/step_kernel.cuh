@@ -1435,6 +1435,29 @@ __device__ __forceinline__ void tc_contraction(Ctx& c, int kind, int l, const un
 }
 #endif
 
+// The sums of one output tile of eight sequences (accumulator layout of mma.m16n8k16: lane (g, t) holds outputs g and
+// g + 8 of sequences 2t and 2t + 1) added to zu[b][0..15] with one 16-byte atomic per lane instead of four 4-byte
+// ones: the four lanes g = 4i .. 4i + 3 transpose their 4 x 4 values (four shuffles), after which lane q = g % 4 holds
+// four consecutive outputs of sequence 2t + q % 2 in the tile's half q / 2. Sums of many CTAs into the same rows are
+// bound by the number of atomic operations the L2 has to retire. `rows`: live sequences of the tile.
+__device__ __forceinline__ void red_tile_v4(float* __restrict__ zu, const float (&v)[4], int lane, int rows) {
+    const int g = lane >> 2, t = lane & 3, q = g & 3;
+    const bool odd = q & 1, hi = q & 2;
+    // round 1, partner g ^ 1: even lanes keep registers 0 and 2, odd lanes 1 and 3
+    const float s0 = odd ? v[0] : v[1], s1 = odd ? v[2] : v[3];
+    const float r0 = __shfl_xor_sync(0xffffffffu, s0, 4), r1 = __shfl_xor_sync(0xffffffffu, s1, 4);
+    const float ax = odd ? r0 : v[0], ay = odd ? v[1] : r0;          // register q % 2 of rows (g & ~1), (g & ~1) + 1
+    const float bx = odd ? r1 : v[2], by = odd ? v[3] : r1;          // register 2 + q % 2 of the same rows
+    // round 2, partner g ^ 2: lanes 0, 1 keep the a pair (tile half 0), lanes 2, 3 the b pair (tile half 1)
+    const float t0 = hi ? ax : bx, t1 = hi ? ay : by;
+    const float u0 = __shfl_xor_sync(0xffffffffu, t0, 8), u1 = __shfl_xor_sync(0xffffffffu, t1, 8);
+    const float o0 = hi ? u0 : ax, o1 = hi ? u1 : ay, o2 = hi ? bx : u0, o3 = hi ? by : u1;
+    const int b = 2 * t + (q & 1);
+    if (b < rows)
+        asm volatile("red.relaxed.gpu.global.add.v4.f32 [%0], {%1, %2, %3, %4};"
+                     :: "l"(zu + (size_t)b * V_D + (g & ~3) + (hi ? 8 : 0)), "f"(o0), "f"(o1), "f"(o2), "f"(o3) : "memory");
+}
+
 // ---------------------------------------------------------------------------------------------
 // the step
 // ---------------------------------------------------------------------------------------------
@@ -1757,10 +1780,13 @@ __device__ __forceinline__ void step_body(const Args& a) {
 #pragma unroll
                             for (int nb = 0; nb < V_NB; nb++)
 #pragma unroll
+                                if (kind != PH_LOGITS) red_tile_v4(zt + (size_t)(row0 + nb * 8) * V_D + jt * 16, acc[tw][nb], c.lane, nrows - nb * 8);
+#pragma unroll
+                            for (int nb = 0; nb < V_NB; nb++)
+#pragma unroll
                                 for (int i = 0; i < 4; i++) {
                                     const int jx = jt * 16 + (c.lane >> 2) + ((i & 2) ? 8 : 0), rb = nb * 8 + (c.lane & 3) * 2 + (i & 1), b = row0 + rb;
                                     if (kind != PH_LOGITS) {
-                                        if (rb < nrows) red_add(zt + (size_t)b * V_D + jx, acc[tw][nb][i]);
                                     } else if (rb < nrows && jx < V_N) {
                                         logit[(size_t)b * V_N + jx] = acc[tw][nb][i];
                                         const u64 k = best_key(acc[tw][nb][i], (u32)jx);
