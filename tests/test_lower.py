@@ -354,3 +354,30 @@ def test_small_division_by_reciprocal_is_exact():
         for rr in (lo, r, hi):
             q = ((a.astype(np.float32) + np.float32(0.5)) * rr).astype(np.int32)
             assert np.array_equal(q, a // w), w
+
+
+def test_exchanges_between_ctas_are_chosen_where_every_cta_has_at_most_one_item():
+    """at most eight sequences: where the attention items are no more than the CTAs, the values a phase needs from a few
+    other CTAs travel as tagged 8-byte pairs (no CTA then waits for a value whose producer waits): query / K / V rows to
+    the attention items; the items' outputs inside a head (one chunk per pair) or the chunks' partial results to the
+    projection phase (several chunks); two grid barriers per layer are left. The buffers lie 8-byte aligned in the
+    scratch area, behind the partial results."""
+    for sh, B, tmax in ((GPT2_SMALL, 8, 384), (GPT2_SMALL, 1, 384), (GPT2_SMALL, 2, 384), (GPT2_XL, 1, 384), (TINY, 3, 16)):
+        low = lower_for(sh, B, tmax)
+        d = low.dims
+        assert d['kernel'] == 'small' and d['qkv_exchange']
+        assert d['fuse_exchange'] == bool(d['fuse_proj']) and d['part_exchange'] == (not d['fuse_proj'])
+        assert B * sh.H * d['nch'] <= low.grid
+        assert low.barriers_per_launch == 1 + 2 * sh.L
+        off_x, off_part, off_best = define(low, 'V_OFF_X'), define(low, 'V_OFF_PART'), define(low, 'V_OFF_BEST')
+        assert off_x % 2 == 0 and off_part % 2 == 0
+        pairs = sh.H * B * sh.E * (int(d['fuse_exchange']) + 3)
+        assert off_best - off_x >= 2 * pairs and off_x - off_part >= B * sh.H * d['nch'] * (sh.E + 2) * (2 if d['part_exchange'] else 1)
+        assert low.scratch_floats >= off_best
+    # more items than CTAs (twenty heads x eight sequences): no exchange, the barriers stay
+    from vesta_gpu_b200.shapes import HEADS20
+    low = lower_for(HEADS20, 8, 64)
+    assert not low.dims['qkv_exchange'] and not low.dims['fuse_exchange']
+    # switched off by hand: the reference structure of one barrier per phase
+    low = lower_for(GPT2_SMALL, 8, 384, tune=dict(fuse_proj=False, qkv_exchange=False))
+    assert low.barriers_per_launch == 1 + 4 * 12 and not low.dims['part_exchange']
