@@ -103,7 +103,10 @@ class VestaGPT2:
         """one step for a host-side loop: tokens_host (pinned int32 [batch]) becomes x, the chosen tokens (the
         `next` values, float32 [batch] as in the reference's scratch) land in next_host (pinned); returns when
         they have"""
-        self.k.step_host(self.x, tokens_host, self.next(), next_host)
+        nv = self.__dict__.get('_next_view')
+        if nv is None:
+            nv = self._next_view = self.next()              # (a view of the scratch area: made once, a host loop calls this per step)
+        self.k.step_host(self.x, tokens_host, nv, next_host)
 
     def prefill(self, tokens, lengths=None, rows=None):
         """consume whole prompts as dense passes: all prompt positions of all sequences are cut into launches of `rows`

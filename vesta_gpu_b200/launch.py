@@ -164,6 +164,8 @@ class Kernel:
             n *= s
         return self.S[off:off + max(1, n)].view(*shape) if shape else self.S[off]
 
+    _host_key = None
+
     def bind(self, residue):
         """fix the argument list once (launches then cost one call) and pack the weights"""
         L = lib()
@@ -231,10 +233,19 @@ class Kernel:
     def step_host(self, x_dev, tokens_host, result_dev, result_host):
         """one decode step with host buffers: tokens_host (pinned) -> x_dev, one launch, result_dev -> result_host
         (pinned), stream synchronised on return: a single call into the library (vesta_step_host)"""
-        stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
-        ok(lib().vesta_step_host(self._bound, stream, x_dev.data_ptr(), ctypes.c_void_p(tokens_host.data_ptr()),
-                                 tokens_host.numel() * tokens_host.element_size(), result_dev.data_ptr(),
-                                 ctypes.c_void_p(result_host.data_ptr()), result_host.numel() * result_host.element_size()))
+        # (a host loop calls this once per step: the argument list is kept for the buffers of the last call, the stream
+        # handle comes from torch's raw accessor)
+        key = (x_dev.data_ptr(), tokens_host.data_ptr(), result_dev.data_ptr(), result_host.data_ptr(), tokens_host.numel(), result_host.numel())
+        if self._host_key != key:
+            self._host_key = key
+            self._host_args = (ctypes.c_ulonglong(key[0]), ctypes.c_void_p(key[1]), ctypes.c_size_t(tokens_host.numel() * tokens_host.element_size()),
+                               ctypes.c_ulonglong(key[2]), ctypes.c_void_p(key[3]), ctypes.c_size_t(result_host.numel() * result_host.element_size()))
+            self._host_fn = lib().vesta_step_host
+        raw = getattr(torch._C, '_cuda_getCurrentRawStream', None)
+        stream = raw(self.device.index) if raw else torch.cuda.current_stream(self.device).cuda_stream
+        r = self._host_fn(self._bound, ctypes.c_void_p(stream), *self._host_args)
+        if r:
+            ok(r)
         self.launches += 1
 
     def __call__(self, residue):
